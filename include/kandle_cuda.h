@@ -1,0 +1,181 @@
+/*
+ * kandle_cuda.h -- C ABI of libkandle_cuda.so, the sm_100a compute backend for Kandle.
+ *
+ * This is the boundary a Kandle backend package binds through N-API / FFI / ctypes.  Every entry
+ * point replaces one kernel key (or one storage operation) of the reference's backend contract;
+ * the comment above each declaration names the reference interface it stands in for, by path
+ * inside the reference project.
+ *
+ * Conventions
+ *   - Every function returns 0 on success and a non-zero kd_status otherwise; the message is
+ *     retrieved with kd_last_error().  A binding turns non-zero into a thrown Error, which is how
+ *     the reference reports misuse (synchronous exceptions from dispatch / kernels).
+ *   - All operators only ENQUEUE work on the library's stream of the current device, in program
+ *     order, exactly like the reference's queue.submit model.  kd_download and kd_synchronize are
+ *     the only synchronisation points (the reference's dataAsync()).
+ *   - Tensors are described by value with kd_tensor: storage handle + element offset + dtype +
+ *     shape + strides (strides and offset in ELEMENTS, as in
+ *     packages/backend-webgpu/src/base/tensor.ts:178-183).  Views are metadata only.
+ *   - One process drives one GPU (one rank per GPU); kd_init selects it.
+ *   - There is no CPU fallback: without a usable sm_100 device kd_init fails.
+ */
+#ifndef KANDLE_CUDA_H_
+#define KANDLE_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KD_MAX_DIMS 8
+
+typedef enum kd_status {
+  KD_OK = 0,
+  KD_ERR_INVALID = 1,     /* bad argument: shape/dtype/stride the operator does not accept */
+  KD_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed                           */
+  KD_ERR_OOM = 3,         /* device allocation failed                                      */
+  KD_ERR_NOT_INIT = 4,    /* kd_init has not been called                                   */
+  KD_ERR_UNSUPPORTED = 5, /* valid request outside what this build implements              */
+  KD_ERR_DEVICE = 6       /* a kernel reported an error flag (bounded wait ran out, ...)   */
+} kd_status;
+
+/* Logical dtypes = Kandle's DType (packages/types/src/base.ts:5-20) plus bfloat16. */
+typedef enum kd_dtype {
+  KD_F32 = 0,
+  KD_F16 = 1,
+  KD_BF16 = 2,
+  KD_I32 = 3,
+  KD_I64 = 4,
+  KD_U8 = 5,
+  KD_BOOL = 6
+} kd_dtype;
+
+/* Mirrors ITensorHandle's metadata (packages/types/src/tensor.ts:6-55). */
+typedef struct kd_tensor {
+  uint64_t storage; /* handle returned by kd_storage_alloc */
+  int64_t offset;   /* in elements */
+  int32_t dtype;    /* kd_dtype */
+  int32_t ndim;
+  int64_t shape[KD_MAX_DIMS];
+  int64_t strides[KD_MAX_DIMS]; /* in elements */
+} kd_tensor;
+
+/* ---------------------------------------------------------------------------------------------
+ * Device / context.  Replaces WebGPUBackend.create + WebGPUDeviceManager.init
+ * (packages/backend-webgpu/src/index.ts:73-85, base/device.ts:95-176).
+ * ------------------------------------------------------------------------------------------- */
+int kd_init(int device_ordinal, unsigned flags);
+int kd_shutdown(void);
+int kd_synchronize(void);
+int kd_device_count(int* count);
+/* Thread-local message of the most recent failing call on this thread. */
+int kd_last_error(char* buf, size_t buf_len);
+/* Native stream handle (cudaStream_t) the library enqueues on, for event timing by the host. */
+int kd_stream(void** stream_out);
+/* Number of kernel launches the library has issued since kd_init (or the last reset). */
+int kd_launch_count(uint64_t* count, int reset);
+
+/* ---------------------------------------------------------------------------------------------
+ * Storage.  Replaces WebGPUStorage: refcounted device buffers, new storage zero-initialised on
+ * request, upload / stream-synchronising download
+ * (packages/backend-webgpu/src/base/storage.ts:60-143,191-243; IStorage in
+ * packages/types/src/storage.ts:5-25).
+ * ------------------------------------------------------------------------------------------- */
+int kd_storage_alloc(uint64_t bytes, int zero, uint64_t* storage_out);
+int kd_storage_retain(uint64_t storage);
+int kd_storage_release(uint64_t storage);
+int kd_storage_bytes(uint64_t storage, uint64_t* bytes_out);
+int kd_storage_device_ptr(uint64_t storage, void** ptr_out);
+int kd_upload(uint64_t storage, uint64_t dst_offset_bytes, const void* host, uint64_t bytes);
+int kd_download(uint64_t storage, uint64_t src_offset_bytes, void* host, uint64_t bytes);
+/* Asynchronous variants for pinned host buffers (no implicit synchronisation). */
+int kd_upload_async(uint64_t storage, uint64_t dst_offset_bytes, const void* host, uint64_t bytes);
+int kd_download_async(uint64_t storage, uint64_t src_offset_bytes, void* host, uint64_t bytes);
+int kd_host_alloc_pinned(uint64_t bytes, void** host_out);
+int kd_host_free_pinned(void* host);
+/* Allocator statistics: bytes handed out, bytes cached in free lists, bytes obtained from CUDA. */
+int kd_memory_stats(uint64_t* in_use, uint64_t* cached, uint64_t* reserved);
+int kd_empty_cache(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Operators, one per registry key.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Key `flash_attention` (q,k,v,out,scale,isCausal):
+ * packages/backend-webgpu/src/kernels/attention/executor.ts:41-235 and builder.ts:51-331.
+ * q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D], out [B,Hq,Sq,D]; 3-D means B=1, 2-D means B=Hq=1.
+ * Hq must be a multiple of Hkv (head_kv = head_q / (Hq/Hkv)).  Causal masking is top-left
+ * aligned (column > row is masked).  Unlike the reference kernel, strides are honoured. */
+int kd_flash_attention(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
+                       const kd_tensor* out, float scale, int is_causal);
+
+/* Key `matmul` (cfg, a, b): MatmulDispatchResult,
+ * packages/core/src/dispatch/matmulOps.ts:32-125; executor
+ * packages/backend-webgpu/src/kernels/matrix/executor.ts:47-76,438-598.
+ * out = beta*c + alpha*op(a)*op(b); batch dims broadcast; full strides honoured. */
+typedef struct kd_matmul_cfg {
+  int64_t M, N, K;
+  int32_t transpose_a, transpose_b; /* stored last two dims are [K,M] / [N,K] when set */
+  float alpha, beta;
+  int32_t has_c;
+  int32_t reserved;
+} kd_matmul_cfg;
+int kd_matmul(const kd_matmul_cfg* cfg, const kd_tensor* a, const kd_tensor* b, const kd_tensor* c,
+              const kd_tensor* out);
+
+/* Keys `rms_norm`, `layer_norm`, `softmax` (inputs, params) -> result:
+ * packages/backend-webgpu/src/kernels/normalize/executor.ts:26-183, shaderBuilder.ts:143-415.
+ * Normalise over the last dimension; strided input, contiguous output; weight/bias may be NULL. */
+int kd_rms_norm(const kd_tensor* x, const kd_tensor* weight, float eps, const kd_tensor* out);
+int kd_layer_norm(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* bias, float eps,
+                  const kd_tensor* out);
+int kd_softmax(const kd_tensor* x, const kd_tensor* out);
+
+/* Key `index_select` (self, index, {dim}, output), dim 0 only (the embedding lookup):
+ * packages/backend-webgpu/src/kernels/gather/executor.ts:34-155.  Indices int32 or int64;
+ * an out-of-range index sets the device error flag instead of reading out of bounds. */
+int kd_index_select(const kd_tensor* self, const kd_tensor* index, int dim, const kd_tensor* out);
+
+/* Iterator keys (add, mul, mul_scalar, neg, cos, sin, silu, gelu, abs, div, maximum, tanh,
+ * sigmoid): packages/backend-webgpu/src/kernels/pointwise/executor.ts:60-130 with the expression
+ * table packages/backend-webgpu/src/kernels/pointwise/ops.ts.  Inputs broadcast to out's shape
+ * (stride 0), rank <= 8.  `scalar` is alpha for add, the multiplier for mul_scalar. */
+typedef enum kd_pointwise_op {
+  KD_OP_ADD = 0,
+  KD_OP_MUL = 1,
+  KD_OP_MUL_SCALAR = 2,
+  KD_OP_NEG = 3,
+  KD_OP_COS = 4,
+  KD_OP_SIN = 5,
+  KD_OP_SILU = 6,
+  KD_OP_GELU = 7,
+  KD_OP_ABS = 8,
+  KD_OP_DIV = 9,
+  KD_OP_MAXIMUM = 10,
+  KD_OP_TANH = 11,
+  KD_OP_SIGMOID = 12,
+  KD_OP_SUB = 13
+} kd_pointwise_op;
+int kd_pointwise(int op, const kd_tensor* a, const kd_tensor* b, float scalar, const kd_tensor* out);
+
+/* Keys `copy`, `contiguous`, `copy_`, `cast`, `clone`: strided copy with dtype conversion,
+ * packages/backend-webgpu/src/kernels/copy/index.ts:15-30.  src broadcasts to dst's shape. */
+int kd_copy(const kd_tensor* dst, const kd_tensor* src);
+/* Keys `zeros`, `ones`, `full`, `empty`. */
+int kd_fill(const kd_tensor* dst, double value);
+/* Key `arange` (packages/backend-webgpu/src/kernels/factory/index.ts:27): dst[i] = start+i*step. */
+int kd_arange(const kd_tensor* dst, double start, double step);
+/* Key `argmax` over the last dimension, int32 or int64 output; lowest index wins ties:
+ * packages/backend-webgpu/src/kernels/reduction/argShaderBuilder.ts:29-247. */
+int kd_argmax(const kd_tensor* x, const kd_tensor* out);
+/* Key `conv1d` (cfg, input, weight, bias?) -> [B,Cout,Wout]:
+ * packages/backend-webgpu/src/kernels/window/algorithms/im2col.ts:124-268. */
+int kd_conv1d(const kd_tensor* input, const kd_tensor* weight, const kd_tensor* bias, int stride,
+              int padding, const kd_tensor* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KANDLE_CUDA_H_ */

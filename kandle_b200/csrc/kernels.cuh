@@ -1,0 +1,29 @@
+// Internal entry points shared between translation units.
+#pragma once
+#include "common.cuh"
+
+namespace kd {
+
+struct AttnParams {
+  int B, Hq, Hkv, Sq, Skv, D;
+  int64_t sq[4], sk[4], sv[4], so[4];
+  int dt_q, dt_k, dt_v, dt_o;
+  float scale;
+  int causal;
+};
+
+int matmul_f32_dispatch(const kd_matmul_cfg* cfg, const kd_tensor* a, const kd_tensor* b, const kd_tensor* c,
+                        const kd_tensor* out);
+// Tensor-core GEMM; sets *handled = 1 when it took the call (bf16 operands in a supported layout).
+int matmul_tc_try(const kd_matmul_cfg* cfg, const kd_tensor* a, const kd_tensor* b, const kd_tensor* c,
+                  const kd_tensor* out, int* handled);
+
+int attention_params(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
+                     int is_causal, AttnParams* p);
+int attention_f32_dispatch(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out,
+                           const AttnParams& p);
+// Tensor-core attention; sets *handled = 1 when it took the call.
+int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out,
+                     const AttnParams& p, int* handled);
+
+}  // namespace kd

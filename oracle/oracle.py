@@ -1,0 +1,452 @@
+"""CPU oracle (numpy front end) for the transformer-forward hot path of final-kk/kandle.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by the
+cpu_baseline / reference legs of bench.py.  The shipped package never imports it.
+
+PARITY UNPINNED: the reference ships no golden vectors or runnable tests for this path
+and cannot be executed here; see the header of oracle.cpp.
+
+The arithmetic lives in oracle.cpp (compiled to oracle/_build/liboracle.so by
+`python oracle/build.py`); this module adds the operator sequencing that the reference
+does in TypeScript (model-utils and the composite dispatch handlers).  Citations are
+paths inside the reference project.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+import subprocess
+import sys
+from dataclasses import dataclass
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
+_lib = None
+
+c_f32p = ctypes.POINTER(ctypes.c_float)
+c_i32p = ctypes.POINTER(ctypes.c_int32)
+c_i64p = ctypes.POINTER(ctypes.c_int64)
+
+
+def build(force: bool = False) -> str:
+    """Compile oracle.cpp with g++ (AVX2+FMA, OpenMP)."""
+    src = os.path.join(_HERE, "oracle.cpp")
+    if not force and os.path.exists(_LIB_PATH) and os.path.getmtime(_LIB_PATH) >= os.path.getmtime(src):
+        return _LIB_PATH
+    os.makedirs(os.path.dirname(_LIB_PATH), exist_ok=True)
+    cmd = ["g++", "-O3", "-mavx2", "-mfma", "-fopenmp", "-fno-fast-math", "-shared", "-fPIC",
+           "-std=c++17", "-o", _LIB_PATH, src]
+    subprocess.run(cmd, check=True)
+    return _LIB_PATH
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _lib.orc_num_threads.restype = ctypes.c_int
+    return _lib
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(int(n))
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(c_f32p)
+
+
+# ----------------------------------------------------------------------------- ops
+def linear(x: np.ndarray, w: np.ndarray, bias: np.ndarray | None = None) -> np.ndarray:
+    """`linear` composite: x @ w.T, then a separate bias add
+    (packages/core/src/dispatch/handlers/composite.ts:55-77)."""
+    x = _f32(x)
+    w = _f32(w)
+    K = x.shape[-1]
+    N = w.shape[0]
+    assert w.shape[1] == K
+    x2 = x.reshape(-1, K)
+    out = np.empty((x2.shape[0], N), dtype=np.float32)
+    lib().orc_gemm_nt(_p(x2), ctypes.c_int64(K), _p(w), ctypes.c_int64(K), _p(out), ctypes.c_int64(N),
+                      ctypes.c_int64(x2.shape[0]), ctypes.c_int64(N), ctypes.c_int64(K),
+                      ctypes.c_float(1.0), ctypes.c_float(0.0), None, ctypes.c_int64(0))
+    out = out.reshape(*x.shape[:-1], N)
+    if bias is not None:
+        out = add(out, np.broadcast_to(_f32(bias), out.shape))
+    return out
+
+
+def matmul4d(a: np.ndarray, b: np.ndarray, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0,
+             c: np.ndarray | None = None) -> np.ndarray:
+    """General strided batched matmul (MatmulDispatchResult semantics,
+    packages/core/src/dispatch/matmulOps.ts:32-125).  `a`/`b` may be arbitrary numpy views with
+    up to 4 dims; leading dims broadcast.  The stored last two dims are swapped logically when the
+    matching trans flag is set."""
+    assert a.dtype == np.float32 and b.dtype == np.float32
+    a4 = a.reshape((1,) * (4 - a.ndim) + a.shape) if a.ndim < 4 else a
+    b4 = b.reshape((1,) * (4 - b.ndim) + b.shape) if b.ndim < 4 else b
+    # reshape of a non-contiguous view may copy; rebuild strides explicitly instead
+    def strides4(t):
+        st = [s // 4 for s in t.strides]
+        return [0] * (4 - t.ndim) + st, (1,) * (4 - t.ndim) + t.shape
+    sa, sha = strides4(a)
+    sb, shb = strides4(b)
+    M, K = (sha[3], sha[2]) if trans_a else (sha[2], sha[3])
+    K2, N = (shb[3], shb[2]) if trans_b else (shb[2], shb[3])
+    assert K == K2, (sha, shb)
+    b0 = max(sha[0], shb[0])
+    b1 = max(sha[1], shb[1])
+    for d, bd in ((0, b0), (1, b1)):
+        if sha[d] == 1 and bd > 1:
+            sa[d] = 0
+        if shb[d] == 1 and bd > 1:
+            sb[d] = 0
+    out = np.empty((b0, b1, M, N), dtype=np.float32)
+    sa_c = (ctypes.c_int64 * 4)(*sa)
+    sb_c = (ctypes.c_int64 * 4)(*sb)
+    cp, sc_c = None, (ctypes.c_int64 * 4)(0, 0, 0, 0)
+    if c is not None:
+        cb = np.ascontiguousarray(np.broadcast_to(c, out.shape), dtype=np.float32)
+        cp = _p(cb)
+        sc_c = (ctypes.c_int64 * 4)(*[s // 4 for s in cb.strides])
+    base_a = ctypes.cast(a.ctypes.data, c_f32p)
+    base_b = ctypes.cast(b.ctypes.data, c_f32p)
+    lib().orc_matmul4d(base_a, sa_c, int(trans_a), base_b, sb_c, int(trans_b), cp, sc_c, _p(out),
+                       ctypes.c_int64(b0), ctypes.c_int64(b1), ctypes.c_int64(M), ctypes.c_int64(N),
+                       ctypes.c_int64(K), ctypes.c_float(alpha), ctypes.c_float(beta))
+    nd = max(a.ndim, b.ndim)
+    return out.reshape(out.shape[4 - nd:])
+
+
+def sdpa_tile_config(D: int, Sq: int, Skv: int) -> tuple[int, int]:
+    bq, bkv = ctypes.c_int(0), ctypes.c_int(0)
+    lib().orc_sdpa_tile_config(D, Sq, Skv, ctypes.byref(bq), ctypes.byref(bkv))
+    return bq.value, bkv.value
+
+
+def sdpa(q: np.ndarray, k: np.ndarray, v: np.ndarray, *, scale: float | None = None,
+         is_causal: bool = False, block_kv: int = 0) -> np.ndarray:
+    """Fused attention kernel reached from `scaled_dot_product_attention` when no mask is given
+    (packages/core/src/dispatch/handlers/composite.ts:247-348).  Accepts 2-D, 3-D or 4-D inputs
+    like the executor (packages/backend-webgpu/src/kernels/attention/executor.ts:198-220):
+    3-D [H,S,D] means batch 1."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    shape = q.shape
+    if q.ndim == 2:
+        q, k, v = q[None, None], k[None, None], v[None, None]
+    elif q.ndim == 3:
+        q, k, v = q[None], k[None], v[None]
+    B, Hq, Sq, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)  # composite.ts:272-275
+    out = np.empty_like(q)
+    lib().orc_sdpa(_p(q), _p(k), _p(v), _p(out), B, Hq, Hkv, Sq, Skv, D, ctypes.c_float(scale),
+                   int(bool(is_causal)), int(block_kv))
+    return out.reshape(shape)
+
+
+def rms_norm(x: np.ndarray, w: np.ndarray | None, eps: float = 1e-5) -> np.ndarray:
+    x = _f32(x)
+    n = x.shape[-1]
+    out = np.empty_like(x)
+    wp = _p(_f32(w)) if w is not None else None
+    lib().orc_rms_norm(_p(x), wp, _p(out), ctypes.c_int64(x.size // n), ctypes.c_int64(n), ctypes.c_float(eps))
+    return out
+
+
+def layer_norm(x: np.ndarray, w: np.ndarray | None, b: np.ndarray | None, eps: float = 1e-5) -> np.ndarray:
+    x = _f32(x)
+    n = x.shape[-1]
+    out = np.empty_like(x)
+    wk = _f32(w) if w is not None else None
+    bk = _f32(b) if b is not None else None
+    lib().orc_layer_norm(_p(x), _p(wk) if wk is not None else None, _p(bk) if bk is not None else None,
+                         _p(out), ctypes.c_int64(x.size // n), ctypes.c_int64(n), ctypes.c_float(eps))
+    return out
+
+
+def softmax(x: np.ndarray) -> np.ndarray:
+    """softmax over the last dim."""
+    x = _f32(x)
+    n = x.shape[-1]
+    out = np.empty_like(x)
+    lib().orc_softmax(_p(x), _p(out), ctypes.c_int64(x.size // n), ctypes.c_int64(n))
+    return out
+
+
+_UNARY = {"neg": 0, "cos": 1, "sin": 2, "silu": 3, "gelu": 4, "abs": 5, "tanh": 6, "sigmoid": 7}
+
+
+def unary(op: str, x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib().orc_unary(_UNARY[op], _p(x), _p(out), ctypes.c_int64(x.size))
+    return out
+
+
+def add(a: np.ndarray, b: np.ndarray, alpha: float = 1.0) -> np.ndarray:
+    """a + alpha*b in fp32 (packages/backend-webgpu/src/kernels/pointwise/ops.ts:437-444)."""
+    a = np.asarray(a, dtype=np.float32)
+    b = np.asarray(b, dtype=np.float32)
+    if alpha == 1.0:
+        return (a + b).astype(np.float32)
+    return (a + np.float32(alpha) * b).astype(np.float32)
+
+
+def mul(a: np.ndarray, b) -> np.ndarray:
+    return (np.asarray(a, dtype=np.float32) * np.asarray(b, dtype=np.float32)).astype(np.float32)
+
+
+def embedding(w: np.ndarray, ids: np.ndarray) -> np.ndarray:
+    w = _f32(w)
+    flat = np.ascontiguousarray(ids.reshape(-1), dtype=np.int32)
+    if flat.size and (flat.min() < 0 or flat.max() >= w.shape[0]):
+        raise IndexError("embedding index out of range")
+    out = np.empty((flat.size, w.shape[1]), dtype=np.float32)
+    lib().orc_index_select_rows(_p(w), flat.ctypes.data_as(c_i32p), _p(out), ctypes.c_int64(flat.size),
+                                ctypes.c_int64(w.shape[1]))
+    return out.reshape(*ids.shape, w.shape[1])
+
+
+def argmax_rows(x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    n = x.shape[-1]
+    out = np.empty(x.shape[:-1], dtype=np.int32)
+    lib().orc_argmax_rows(_p(x), out.ctypes.data_as(c_i32p), ctypes.c_int64(x.size // n), ctypes.c_int64(n))
+    return out
+
+
+def conv1d(x: np.ndarray, w: np.ndarray, bias: np.ndarray | None, stride: int = 1, padding: int = 0) -> np.ndarray:
+    x, w = _f32(x), _f32(w)
+    B, Cin, L = x.shape
+    Cout, Cin2, ksz = w.shape
+    assert Cin == Cin2
+    Wout = (L + 2 * padding - ksz) // stride + 1
+    out = np.empty((B, Cout, Wout), dtype=np.float32)
+    bk = _f32(bias) if bias is not None else None
+    lib().orc_conv1d(_p(x), _p(w), _p(bk) if bk is not None else None, _p(out), B, Cin, L, Cout, ksz, stride, padding)
+    return out
+
+
+# ----------------------------------------------------------------------------- RoPE
+def rope_inv_freq(dim: int, base: float) -> np.ndarray:
+    """inv_freq[i] = f32(1 / base**(i/(dim/2))) computed in doubles
+    (packages/model-utils/src/rope.ts:159-171)."""
+    half = dim // 2
+    return np.array([1.0 / math.pow(base, i / half) for i in range(half)], dtype=np.float32)
+
+
+def rope_tables(positions: np.ndarray, dim: int, base: float) -> tuple[np.ndarray, np.ndarray]:
+    """freqs = f32(pos) * inv_freq in fp32; emb = cat(freqs, freqs); cos/sin(emb)
+    (packages/model-utils/src/rope.ts:192-261)."""
+    inv = rope_inv_freq(dim, base)
+    pos = positions.astype(np.float32)
+    freqs = (pos[..., None] * inv).astype(np.float32)
+    emb = np.concatenate([freqs, freqs], axis=-1)
+    return unary("cos", emb), unary("sin", emb)
+
+
+def apply_rope(x: np.ndarray, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """x*cos + rotate_half(x)*sin with rotate_half(x) = cat(-x2, x1)
+    (packages/model-utils/src/rope.ts:546-644).  x [B,H,S,D]; cos/sin [S,D]."""
+    half = x.shape[-1] // 2
+    rot = np.concatenate([-x[..., half:], x[..., :half]], axis=-1)
+    return add(mul(x, cos[None, None]), mul(rot, sin[None, None]))
+
+
+# ----------------------------------------------------------------------------- Qwen3
+@dataclass
+class Qwen3Config:
+    """Field meanings follow Qwen3ModelConfig (packages/model-utils/src/qwen3/model.ts:45-84)."""
+    vocab_size: int = 151936
+    hidden_size: int = 1024
+    intermediate_size: int = 3072
+    num_hidden_layers: int = 28
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+
+
+class StaticKVCacheOracle:
+    """[B,Hkv,maxS,D] zero-initialised per layer; update writes [start,end) and returns the
+    [:end] prefix (packages/model-utils/src/kv-cache.ts:123-130,164-212)."""
+
+    def __init__(self, cfg: Qwen3Config, batch: int, max_seq_len: int):
+        shp = (batch, cfg.num_key_value_heads, max_seq_len, cfg.head_dim)
+        self.k = [np.zeros(shp, np.float32) for _ in range(cfg.num_hidden_layers)]
+        self.v = [np.zeros(shp, np.float32) for _ in range(cfg.num_hidden_layers)]
+        self.max_seq_len = max_seq_len
+
+    def update(self, layer: int, k: np.ndarray, v: np.ndarray, start: int):
+        end = start + k.shape[2]
+        if end > self.max_seq_len:
+            raise ValueError("Cache overflow")
+        self.k[layer][:, :, start:end] = k
+        self.v[layer][:, :, start:end] = v
+        return self.k[layer][:, :, :end], self.v[layer][:, :, :end]
+
+
+class Qwen3Oracle:
+    """Operator sequence of Qwen3ForCausalLM.forward / forwardWithKVCache
+    (packages/model-utils/src/qwen3/for_causal_lm.ts:149-194), Qwen3Model
+    (qwen3/model.ts:265-347), Qwen3DecoderLayer (qwen3/decoder_layer.ts:191-241),
+    GroupedQueryAttention (attention/gqa.ts:246-430) and SwiGLUMLP (mlp/swiglu.ts:119-134).
+
+    `weights` maps HuggingFace-style names to fp32 arrays:
+      model.embed_tokens.weight, model.norm.weight,
+      model.layers.{i}.{input_layernorm,post_attention_layernorm}.weight,
+      model.layers.{i}.self_attn.{q,k,v,o}_proj.weight, .self_attn.{q,k}_norm.weight,
+      model.layers.{i}.mlp.{gate,up,down}_proj.weight.   lm_head is tied to embed_tokens.
+    """
+
+    def __init__(self, cfg: Qwen3Config, weights: dict):
+        self.cfg = cfg
+        self.w = weights
+
+    def _attention(self, li: int, h: np.ndarray, cos, sin, cache, pos: int, hooks=None) -> np.ndarray:
+        c, w = self.cfg, self.w
+        pre = f"model.layers.{li}.self_attn."
+        B, S, _ = h.shape
+        q = linear(h, w[pre + "q_proj.weight"]).reshape(B, S, c.num_attention_heads, c.head_dim)
+        k = linear(h, w[pre + "k_proj.weight"]).reshape(B, S, c.num_key_value_heads, c.head_dim)
+        v = linear(h, w[pre + "v_proj.weight"]).reshape(B, S, c.num_key_value_heads, c.head_dim)
+        q = rms_norm(q, w[pre + "q_norm.weight"], c.rms_norm_eps)      # gqa.ts:279-286
+        k = rms_norm(k, w[pre + "k_norm.weight"], c.rms_norm_eps)
+        q = np.ascontiguousarray(q.transpose(0, 2, 1, 3))             # gqa.ts:297-299
+        k = np.ascontiguousarray(k.transpose(0, 2, 1, 3))
+        v = np.ascontiguousarray(v.transpose(0, 2, 1, 3))
+        q = apply_rope(q, cos, sin)                                   # gqa.ts:306-310
+        k = apply_rope(k, cos, sin)
+        causal = True
+        if cache is not None:
+            k, v = cache.update(li, k, v, pos)                        # gqa.ts:319-322
+            if S == 1 and k.shape[2] > 1:
+                causal = False                                        # gqa.ts:333-336
+        # The reference materialises K/V repeated to Hq heads (gqa.ts:494-519) and calls the
+        # kernel with ratio 1; the grouped call below reads the same rows.
+        o = sdpa(q, k, v, is_causal=causal)
+        if hooks is not None:
+            hooks.setdefault(f"attn{li}", o)
+        o = np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(B, S, -1)
+        return linear(o, w[pre + "o_proj.weight"])
+
+    def _mlp(self, li: int, h: np.ndarray) -> np.ndarray:
+        pre = f"model.layers.{li}.mlp."
+        g = unary("silu", linear(h, self.w[pre + "gate_proj.weight"]))
+        u = linear(h, self.w[pre + "up_proj.weight"])
+        return linear(mul(g, u), self.w[pre + "down_proj.weight"])
+
+    def hidden(self, ids: np.ndarray, cache=None, pos: int = 0, num_layers: int | None = None, hooks=None) -> np.ndarray:
+        c, w = self.cfg, self.w
+        B, S = ids.shape
+        h = embedding(w["model.embed_tokens.weight"], ids)
+        positions = np.arange(pos, pos + S, dtype=np.int32)            # rope.ts:270-272
+        cos, sin = rope_tables(positions, c.head_dim, c.rope_theta)
+        L = c.num_hidden_layers if num_layers is None else num_layers
+        for li in range(L):
+            pre = f"model.layers.{li}."
+            x = rms_norm(h, w[pre + "input_layernorm.weight"], c.rms_norm_eps)
+            h = add(h, self._attention(li, x, cos, sin, cache, pos, hooks))
+            x = rms_norm(h, w[pre + "post_attention_layernorm.weight"], c.rms_norm_eps)
+            h = add(h, self._mlp(li, x))
+            if hooks is not None:
+                hooks[f"layer{li}"] = h
+        return rms_norm(h, w["model.norm.weight"], c.rms_norm_eps)
+
+    def logits(self, ids: np.ndarray, cache=None, pos: int = 0, last_only: bool = False,
+               num_layers: int | None = None) -> np.ndarray:
+        """Tied lm_head: matmul(h, embed^T) (for_causal_lm.ts:184-185).  The reference computes
+        every position; last_only selects position S-1 before the matmul (same rows)."""
+        h = self.hidden(ids, cache, pos, num_layers)
+        if last_only:
+            h = h[:, -1:, :]
+        return linear(h, self.w["model.embed_tokens.weight"])
+
+    def greedy_generate(self, ids: np.ndarray, steps: int, max_seq_len: int | None = None) -> np.ndarray:
+        """Prefill, then `steps` greedy tokens: select last position, argmax, feed back
+        (for_causal_lm.ts:475-508, batch-capable form)."""
+        B, S = ids.shape
+        cache = StaticKVCacheOracle(self.cfg, B, max_seq_len or (S + steps))
+        out = np.empty((B, steps), dtype=np.int32)
+        lg = self.logits(ids, cache, 0, last_only=True)
+        tok = argmax_rows(lg[:, -1, :])
+        out[:, 0] = tok
+        for t in range(1, steps):
+            lg = self.logits(tok.reshape(B, 1), cache, S + t - 1, last_only=True)
+            tok = argmax_rows(lg[:, -1, :])
+            out[:, t] = tok
+        return out
+
+
+# ----------------------------------------------------------------------------- Whisper encoder
+@dataclass
+class WhisperEncoderConfig:
+    """packages/model-utils/src/whisper/config.ts:33-69 (encoder fields)."""
+    n_mels: int = 80
+    n_audio_ctx: int = 1500
+    n_audio_state: int = 768
+    n_audio_head: int = 12
+    n_audio_layer: int = 12
+    ln_eps: float = 1e-5
+
+
+class WhisperEncoderOracle:
+    """WhisperAudioEncoder.forward (packages/model-utils/src/whisper/encoder.ts:202-250) with
+    ResidualAttentionBlock (whisper/block.ts:150-200) and nn.MultiheadAttention
+    (packages/core/src/nn/modules/attention/MultiheadAttention.ts:280-437).
+
+    weights: conv1.{weight,bias}, conv2.{weight,bias}, embed_positions.weight,
+      layers.{i}.self_attn_layer_norm.{weight,bias}, layers.{i}.self_attn.in_proj_{weight,bias},
+      layers.{i}.self_attn.out_proj.{weight,bias}, layers.{i}.final_layer_norm.{weight,bias},
+      layers.{i}.fc1.{weight,bias}, layers.{i}.fc2.{weight,bias}, layer_norm.{weight,bias}
+    """
+
+    def __init__(self, cfg: WhisperEncoderConfig, weights: dict):
+        self.cfg, self.w = cfg, weights
+
+    def forward(self, mel: np.ndarray, num_layers: int | None = None) -> np.ndarray:
+        c, w = self.cfg, self.w
+        x = unary("gelu", conv1d(mel, w["conv1.weight"], w["conv1.bias"], 1, 1))
+        x = unary("gelu", conv1d(x, w["conv2.weight"], w["conv2.bias"], 2, 1))
+        x = x.transpose(0, 2, 1)                                       # [B,T,C]
+        T = x.shape[1]
+        x = add(x, w["embed_positions.weight"][:T][None])
+        B, E, H = x.shape[0], c.n_audio_state, c.n_audio_head
+        D = E // H
+        L = c.n_audio_layer if num_layers is None else num_layers
+        for li in range(L):
+            p = f"layers.{li}."
+            y = layer_norm(x, w[p + "self_attn_layer_norm.weight"], w[p + "self_attn_layer_norm.bias"], c.ln_eps)
+            W_in, b_in = w[p + "self_attn.in_proj_weight"], w[p + "self_attn.in_proj_bias"]
+            q = linear(y, W_in[0:E], b_in[0:E])
+            k = linear(y, W_in[E:2 * E], b_in[E:2 * E])
+            v = linear(y, W_in[2 * E:], b_in[2 * E:])
+            def heads(t):
+                return np.ascontiguousarray(t.reshape(B, T, H, D).transpose(0, 2, 1, 3)).reshape(B * H, T, D)
+            o = sdpa(heads(q), heads(k), heads(v), is_causal=False)     # 3-D path: batch 1, heads B*H
+            o = np.ascontiguousarray(o.reshape(B, H, T, D).transpose(0, 2, 1, 3)).reshape(B, T, E)
+            x = add(x, linear(o, w[p + "self_attn.out_proj.weight"], w[p + "self_attn.out_proj.bias"]))
+            y = layer_norm(x, w[p + "final_layer_norm.weight"], w[p + "final_layer_norm.bias"], c.ln_eps)
+            y = unary("gelu", linear(y, w[p + "fc1.weight"], w[p + "fc1.bias"]))
+            x = add(x, linear(y, w[p + "fc2.weight"], w[p + "fc2.bias"]))
+        return layer_norm(x, w["layer_norm.weight"], w["layer_norm.bias"], c.ln_eps)
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))

@@ -1,0 +1,241 @@
+"""GPU parity of every operator key against the CPU oracle, called through the C ABI (via the
+CudaBackend mirror).  fp32 bound: max-abs <= 1e-4 * max|reference| (the bound the north star
+states); bf16 storage is checked with a bound that allows one rounding of the output."""
+import math
+
+import numpy as np
+import pytest
+
+import kandle_b200
+from kandle_b200 import core, lib, synth
+from kandle_b200.core import Tensor
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, ref, rel=1e-4):
+    ref = np.asarray(ref)
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    tol = rel * max(np.abs(ref).max(), 1e-30)
+    err = np.abs(got.astype(np.float64) - ref.astype(np.float64)).max() if ref.size else 0.0
+    assert err <= tol, f"max-abs error {err:.3e} > {tol:.3e}"
+
+
+# ------------------------------------------------------------------ config 1 (the first slice)
+def test_config1_sdpa_fp32_causal_gqa(backend, oracle):
+    """B=1, Hq=16, Hkv=8, S=128, D=128, N(0,1), default scale, causal."""
+    q, k, v = synth.normal("c1.q", (1, 16, 128, 128)), synth.normal("c1.k", (1, 8, 128, 128)), synth.normal("c1.v", (1, 8, 128, 128))
+    out = core.scaledDotProductAttention(Tensor(q), Tensor(k), Tensor(v), None, 0.0, True)
+    close(out.dataAsync(), oracle.sdpa(q, k, v, is_causal=True))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("b,hq,hkv,sq,skv,d", [
+    (2, 4, 4, 33, 33, 64), (1, 8, 2, 1, 77, 128), (2, 2, 1, 17, 40, 32), (1, 4, 1, 127, 127, 128),
+    (1, 2, 2, 129, 129, 64), (1, 3, 3, 300, 300, 64), (1, 2, 1, 5, 260, 256)])
+def test_sdpa_shapes_and_tails(backend, oracle, causal, b, hq, hkv, sq, skv, d):
+    q, k, v = synth.normal("q", (b, hq, sq, d)), synth.normal("k", (b, hkv, skv, d)), synth.normal("v", (b, hkv, skv, d))
+    out = core.scaledDotProductAttention(Tensor(q), Tensor(k), Tensor(v), None, 0.0, causal)
+    close(out.dataAsync(), oracle.sdpa(q, k, v, is_causal=causal))
+
+
+def test_sdpa_3d_and_strided_inputs(backend, oracle):
+    q, k, v = synth.normal("q", (6, 20, 64)), synth.normal("k", (6, 20, 64)), synth.normal("v", (6, 20, 64))
+    out = core.scaledDotProductAttention(Tensor(q), Tensor(k), Tensor(v))
+    close(out.dataAsync(), oracle.sdpa(q, k, v))
+    # K/V as prefix views of a longer cache (non-contiguous across heads), Q as a permuted view
+    kc, vc = synth.normal("kc", (2, 2, 64, 128)), synth.normal("vc", (2, 2, 64, 128))
+    qb = synth.normal("qb", (2, 9, 4, 128))                       # [B,S,H,D]
+    tq = Tensor(qb).permute([0, 2, 1, 3])
+    tk, tv = Tensor(kc).slice(":, :, :37, :"), Tensor(vc).slice(":, :, :37, :")
+    out = core.scaledDotProductAttention(tq, tk, tv, None, 0.0, False)
+    close(out.dataAsync(), oracle.sdpa(qb.transpose(0, 2, 1, 3), kc[:, :, :37], vc[:, :, :37]))
+
+
+def test_sdpa_mask_path_uses_naive_composite(backend, oracle):
+    q, k, v = synth.normal("q", (1, 2, 8, 32)), synth.normal("k", (1, 2, 8, 32)), synth.normal("v", (1, 2, 8, 32))
+    mask = np.where(np.arange(8)[None, :] > np.arange(8)[:, None], -np.inf, 0.0).astype(np.float32)
+    out = core.scaledDotProductAttention(Tensor(q), Tensor(k), Tensor(v), Tensor(mask.reshape(1, 1, 8, 8)))
+    close(out.dataAsync(), oracle.sdpa(q, k, v, is_causal=True), 2e-4)
+    with pytest.raises(ValueError):
+        core.scaledDotProductAttention(Tensor(q), Tensor(k), Tensor(v), Tensor(mask), 0.0, True)
+
+
+def test_sdpa_rejects_bad_shapes(backend):
+    q, k = Tensor(synth.normal("q", (1, 3, 4, 32))), Tensor(synth.normal("k", (1, 2, 4, 32)))
+    with pytest.raises(lib.KandleCudaError):
+        core.scaledDotProductAttention(q, k, k)
+
+
+# ------------------------------------------------------------------ matmul / linear
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (5, 7, 3), (128, 128, 16), (130, 257, 100), (512, 1024, 1024), (1, 3072, 1024)])
+def test_linear(backend, oracle, m, n, k):
+    x, w = synth.normal("x", (m, k)), synth.normal("w", (n, k), 0.05)
+    close(core.linear(Tensor(x), Tensor(w)).dataAsync(), oracle.linear(x, w))
+
+
+def test_linear_batched_with_bias_and_1d(backend, oracle):
+    x, w, b = synth.normal("x", (3, 11, 40)), synth.normal("w", (24, 40)), synth.normal("b", (24,))
+    close(core.linear(Tensor(x), Tensor(w), Tensor(b)).dataAsync(), oracle.linear(x, w, b))
+    close(core.linear(Tensor(x[0, 0]), Tensor(w)).dataAsync(), oracle.linear(x[0, 0], w))
+    with pytest.raises(ValueError):
+        core.linear(Tensor(x), Tensor(synth.normal("w2", (24, 41))))
+
+
+def test_matmul_dispatch_cases(backend, oracle):
+    # lm_head: B operand is a transposed (strided) view with both transpose flags false
+    h, e = synth.normal("h", (2, 5, 64)), synth.normal("e", (300, 64))
+    et = Tensor(e).transpose(0, 1)
+    close(core.matmul(Tensor(h), et).dataAsync(), h @ e.T)
+    # 4-D bmm with broadcast batch and alpha (naive attention's QK^T)
+    q, k = synth.normal("q", (2, 3, 9, 16)), synth.normal("k", (1, 3, 11, 16))
+    close(core.matmul(Tensor(q), Tensor(k), transposeB=True, alpha=0.25).dataAsync(), 0.25 * (q @ k.transpose(0, 1, 3, 2)))
+    # Whisper MHA: transposed batch-first activations, weight row-slice with non-zero offset
+    x, w = synth.normal("x", (4, 6, 32)), synth.normal("w", (96, 32))
+    xt = Tensor(x).transpose(0, 1)
+    ws = Tensor(w).slice([slice(32, 64), slice(None)])
+    close(core.linear(xt, ws).dataAsync(), oracle.linear(x.transpose(1, 0, 2), w[32:64]))
+    # beta * C epilogue and transposeA
+    a, b, c = synth.normal("a", (20, 12)), synth.normal("b", (20, 8)), synth.normal("c", (12, 8))
+    got = core.matmul(Tensor(a), Tensor(b), transposeA=True, alpha=2.0, beta=0.5, inputC=Tensor(c)).dataAsync()
+    close(got, oracle.matmul4d(a, b, trans_a=True, alpha=2.0, beta=0.5, c=c))
+    # vectors
+    close(core.matmul(Tensor(a[:, 0]), Tensor(b)).dataAsync(), a[:, 0] @ b)
+    with pytest.raises(ValueError):
+        core.matmul(Tensor(a), Tensor(c))
+
+
+# ------------------------------------------------------------------ normalisation
+@pytest.mark.parametrize("rows,n", [(1, 1), (7, 128), (5, 1024), (3, 2560), (2, 9000), (33, 100)])
+def test_rms_norm(backend, oracle, rows, n):
+    x, w = synth.normal("x", (rows, n), 2.0), synth.normal("w", (n,), 0.1, 1.0)
+    close(core.rmsNorm(Tensor(x), (n,), Tensor(w), 1e-6).dataAsync(), oracle.rms_norm(x, w, 1e-6))
+    close(core.rmsNorm(Tensor(x), (n,), None, 1e-5).dataAsync(), oracle.rms_norm(x, None, 1e-5))
+
+
+def test_rms_norm_on_strided_view(backend, oracle):
+    """q/k-norm runs on [B,S,H,D] views of a projection output; also a permuted view."""
+    x = synth.normal("x", (2, 5, 4, 128))
+    w = synth.normal("w", (128,), 0.1, 1.0)
+    t = Tensor(x).permute([0, 2, 1, 3])
+    close(core.rmsNorm(t, (128,), Tensor(w), 1e-6).dataAsync(), oracle.rms_norm(x.transpose(0, 2, 1, 3), w, 1e-6))
+    t2 = Tensor(x).slice("..., :64")
+    close(core.rmsNorm(t2, (64,), None, 1e-6).dataAsync(), oracle.rms_norm(x[..., :64], None, 1e-6))
+
+
+@pytest.mark.parametrize("rows,n", [(4, 768), (3, 33), (2, 3072)])
+def test_layer_norm(backend, oracle, rows, n):
+    x, w, b = synth.normal("x", (rows, n), 3.0, 0.7), synth.normal("w", (n,), 0.1, 1.0), synth.normal("b", (n,))
+    close(core.layerNorm(Tensor(x), (n,), Tensor(w), Tensor(b), 1e-5).dataAsync(), oracle.layer_norm(x, w, b, 1e-5))
+
+
+@pytest.mark.parametrize("rows,n", [(9, 333), (2, 151936), (64, 77)])
+def test_softmax(backend, oracle, rows, n):
+    x = synth.normal("x", (rows, n), 4.0)
+    close(core.softmax(Tensor(x), -1).dataAsync(), oracle.softmax(x))
+
+
+# ------------------------------------------------------------------ pointwise / copy
+@pytest.mark.parametrize("op", ["neg", "cos", "sin", "silu", "gelu", "abs", "tanh", "sigmoid"])
+def test_unary(backend, oracle, op):
+    x = synth.normal("x", (7, 1001), 6.0)
+    x[0, :6] = [-1000, -88, 0, 88, 1000, 25]
+    got = getattr(core, op)(Tensor(x)).dataAsync()
+    ref = oracle.unary(op, x)
+    assert np.abs(got - ref).max() <= 2e-6 * max(1.0, np.abs(ref).max())
+
+
+def test_rope_angles_need_accurate_sincos(backend, oracle):
+    ang = (np.arange(0, 4400, dtype=np.float32) * np.float32(1.0)).reshape(44, 100)
+    for op in ("cos", "sin"):
+        assert np.abs(getattr(core, op)(Tensor(ang)).dataAsync() - oracle.unary(op, ang)).max() < 1e-6
+
+
+def test_binary_broadcast_and_alpha(backend, oracle):
+    a, b = synth.normal("a", (4, 1, 6, 8)), synth.normal("b", (5, 1, 8))
+    assert np.array_equal(core.add(Tensor(a), Tensor(b)).dataAsync(), a + b)
+    close(core.add(Tensor(a), Tensor(b), 0.5).dataAsync(), oracle.add(a, b, 0.5), 1e-6)
+    assert np.array_equal(core.mul(Tensor(a), Tensor(b)).dataAsync(), a * b)
+    assert np.array_equal(core.mul(Tensor(a), 0.25).dataAsync(), a * np.float32(0.25))
+    assert np.array_equal(core.maximum(Tensor(a), Tensor(b)).dataAsync(), np.maximum(a, b))
+    c = synth.normal("c", (1024, 1024))
+    assert np.array_equal(core.add(Tensor(c), Tensor(c.T.copy())).dataAsync(), c + c.T)
+    ids = np.arange(12, dtype=np.int32)
+    assert np.array_equal(core.mul(Tensor(ids).unsqueeze(-1).expand((12, 3)), Tensor(np.array([0.5, 1, 2], np.float32)).unsqueeze(0).expand((12, 3))).dataAsync(),
+                          ids[:, None].astype(np.float32) * np.array([0.5, 1, 2], np.float32))
+    with pytest.raises(ValueError):
+        core.add(Tensor(a), Tensor(synth.normal("z", (7,))))
+
+
+def test_views_copy_cat_cast(backend):
+    x = synth.normal("x", (2, 3, 4, 6))
+    t = Tensor(x)
+    assert np.array_equal(t.permute([0, 2, 1, 3]).contiguous().dataAsync(), x.transpose(0, 2, 1, 3))
+    assert np.array_equal(t.slice("..., 2:5").dataAsync(), x[..., 2:5])
+    assert np.array_equal(t.select(1, 2).dataAsync(), x[:, 2])
+    assert np.array_equal(t.unsqueeze(2).expand((2, 3, 5, 4, 6)).contiguous().dataAsync(), np.broadcast_to(x[:, :, None], (2, 3, 5, 4, 6)))
+    assert np.array_equal(core.cat([t.slice("..., 3:"), t.slice("..., :3")], -1).dataAsync(), np.concatenate([x[..., 3:], x[..., :3]], -1))
+    # copy_ into a slice of a zero tensor (KV-cache write)
+    cache = core.zeros((2, 3, 10, 6))
+    v = cache.slice(":, :, 4:8, :")
+    core.copy_(v, t)
+    ref = np.zeros((2, 3, 10, 6), np.float32)
+    ref[:, :, 4:8] = x
+    assert np.array_equal(cache.dataAsync(), ref)
+    # casts
+    b16 = core.cast(t, "bfloat16")
+    assert b16.dtype == "bfloat16" and np.array_equal(b16.dataAsync(), lib.round_to_bf16(x))
+    assert np.array_equal(core.cast(b16, "float32").dataAsync(), lib.round_to_bf16(x))
+    i64 = Tensor(np.array([[1, 2 ** 40, -5]], dtype=np.int64))
+    assert np.array_equal(core.cast(i64.permute([1, 0]), "int64").dataAsync(), np.array([[1], [2 ** 40], [-5]]))
+    assert np.array_equal(core.cast(Tensor(np.array([3, 150000], np.int64)), "int32").dataAsync(), np.array([3, 150000], np.int32))
+    assert np.array_equal(core.arange(5, 12).dataAsync(), np.arange(5, 12, dtype=np.int32))
+    assert np.array_equal(core.full((3, 2), 1.5).dataAsync(), np.full((3, 2), 1.5, np.float32))
+    assert np.array_equal(core.ones((4,), "bfloat16").dataAsync(), np.ones(4, np.float32))
+
+
+def test_embedding_and_argmax(backend, oracle):
+    w = synth.normal("e", (500, 48))
+    ids = synth.token_ids("ids", (3, 17), 500)
+    assert np.array_equal(core.embedding(Tensor(ids), Tensor(w)).dataAsync(), w[ids])
+    assert np.array_equal(core.embedding(Tensor(ids.astype(np.int64)), Tensor(w)).dataAsync(), w[ids])
+    x = synth.normal("x", (4, 151936))
+    x[2, 10] = x[2, 150000] = 99.0
+    got = core.argmax(Tensor(x), 1).dataAsync()
+    assert got.dtype == np.int64 and np.array_equal(got, oracle.argmax_rows(x)) and got[2] == 10
+    xb = lib.round_to_bf16(x)
+    assert np.array_equal(core.argmax(Tensor(xb, dtype="bfloat16"), -1).dataAsync(), oracle.argmax_rows(xb))
+    y = synth.normal("y", (6, 5, 7))
+    assert np.array_equal(core.argmax(Tensor(y), 1).dataAsync(), np.argmax(y, 1))
+
+
+def test_embedding_out_of_range_sets_error_flag(backend):
+    w = Tensor(synth.normal("e", (10, 8)))
+    out = core.embedding(Tensor(np.array([1, 12], np.int32)), w)
+    with pytest.raises(lib.KandleCudaError) as e:
+        out.dataAsync()
+    assert e.value.status == 6
+    backend.synchronize()   # flag was cleared; the context stays usable
+    assert np.array_equal(core.add(w, w).dataAsync(), 2 * w.dataAsync())
+
+
+def test_conv1d(backend, oracle):
+    x, w, b = synth.normal("x", (2, 5, 31)), synth.normal("w", (7, 5, 3)), synth.normal("b", (7,))
+    for stride in (1, 2):
+        close(core.conv1d(Tensor(x), Tensor(w), Tensor(b), stride, 1).dataAsync(), oracle.conv1d(x, w, b, stride, 1))
+
+
+def test_storage_refcount_and_allocator_reuse(backend):
+    s0 = backend.memory_stats()
+    t = core.zeros((1024, 1024))
+    v = t.slice("10:20, :")
+    t.dispose()
+    assert np.array_equal(v.dataAsync(), np.zeros((10, 1024), np.float32))   # view keeps storage alive
+    v.dispose()
+    with pytest.raises(RuntimeError):
+        v.dataAsync()
+    s1 = backend.memory_stats()
+    assert s1["in_use"] == s0["in_use"]
+    t2 = core.zeros((1024, 1024))
+    assert backend.memory_stats()["reserved"] == s1["reserved"]            # block came from the cache
+    t2.dispose()
