@@ -175,6 +175,32 @@ int kd_argmax(const kd_tensor* x, const kd_tensor* out);
 int kd_conv1d(const kd_tensor* input, const kd_tensor* weight, const kd_tensor* bias, int stride,
               int padding, const kd_tensor* out);
 
+/* ---------------------------------------------------------------------------------------------
+ * Timing.  CUDA events recorded on the library's stream (the reference only has host-side
+ * performance.now() around dataAsync(), playground-node/src/qwen3/index.ts:161,253).
+ * ------------------------------------------------------------------------------------------- */
+int kd_event_create(uint64_t* event_out);
+int kd_event_record(uint64_t event);
+int kd_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms_out); /* synchronises on `stop` */
+int kd_event_destroy(uint64_t event);
+
+/* ---------------------------------------------------------------------------------------------
+ * Fused bf16 fast paths.  Each one computes what a run of the reference's eager operator calls
+ * computes; the comment names that run.  They exist because one decoder layer is ~41 separate
+ * kernel submissions on the eager path (packages/model-utils/src/attention/gqa.ts:246-430,
+ * mlp/swiglu.ts:119-134, qwen3/decoder_layer.ts:191-241).
+ * ------------------------------------------------------------------------------------------- */
+typedef enum kd_epilogue {
+  KD_EPI_NONE = 0,
+  KD_EPI_RESIDUAL = 1, /* out = residual + x W^T : `linear` followed by the residual `add`     */
+  KD_EPI_SWIGLU = 2    /* out = silu(x Wg^T) * (x Wu^T) : gate/up `linear`, `silu`, `mul`;
+                          weight rows interleave 128 gate rows / 128 up rows per 256-row block */
+} kd_epilogue;
+/* `linear` on the tensor cores (tcgen05): x [tokens,K] bf16, weight [N,K] bf16 (K-major, as
+ * composite.ts:62-70 passes it), out [tokens,N] (or [tokens,N/2] for SWIGLU) bf16 or fp32. */
+int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* residual, int epilogue,
+                   const kd_tensor* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -268,3 +268,21 @@ class CudaBackend:
         a, b, c = ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_uint64(0)
         lib.call("kd_memory_stats", ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
         return {"in_use": a.value, "cached": b.value, "reserved": c.value}
+
+
+class CudaEvent:
+    """CUDA event on the library's stream, for device-side timing."""
+
+    def __init__(self):
+        h = ctypes.c_uint64(0)
+        lib.call("kd_event_create", ctypes.byref(h))
+        self.handle = h.value
+
+    def record(self) -> "CudaEvent":
+        lib.call("kd_event_record", ctypes.c_uint64(self.handle))
+        return self
+
+    def elapsed_ms(self, stop: "CudaEvent") -> float:
+        ms = ctypes.c_float(0)
+        lib.call("kd_event_elapsed_ms", ctypes.c_uint64(self.handle), ctypes.c_uint64(stop.handle), ctypes.byref(ms))
+        return float(ms.value)

@@ -3,7 +3,9 @@
 The shared library links the CUDA runtime statically and resolves the driver API at run time, so
 it loads (and its symbols can be listed) on a machine without a GPU driver.  Usage:
 
-    python -m kandle_b200.build [--force] [--verbose]
+    python kandle_b200/build.py [--force] [--verbose]
+
+(run it as a script: importing the package needs the library this script produces)
 """
 from __future__ import annotations
 

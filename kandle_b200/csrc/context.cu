@@ -392,3 +392,29 @@ KD_API int kd_empty_cache(void) {
   g_alloc.release_cached();
   return KD_OK;
 }
+
+KD_API int kd_event_create(uint64_t* event_out) {
+  KD_TRY(require_init());
+  if (!event_out) return fail(KD_ERR_INVALID, "null argument");
+  cudaEvent_t e;
+  KD_CUDA_CHECK(cudaEventCreate(&e));
+  *event_out = reinterpret_cast<uint64_t>(e);
+  return KD_OK;
+}
+KD_API int kd_event_record(uint64_t event) {
+  KD_TRY(require_init());
+  KD_CUDA_CHECK(cudaEventRecord(reinterpret_cast<cudaEvent_t>(event), ctx().stream));
+  return KD_OK;
+}
+KD_API int kd_event_elapsed_ms(uint64_t start, uint64_t stop, float* ms_out) {
+  KD_TRY(require_init());
+  if (!ms_out) return fail(KD_ERR_INVALID, "null argument");
+  KD_CUDA_CHECK(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(stop)));
+  KD_CUDA_CHECK(cudaEventElapsedTime(ms_out, reinterpret_cast<cudaEvent_t>(start), reinterpret_cast<cudaEvent_t>(stop)));
+  return KD_OK;
+}
+KD_API int kd_event_destroy(uint64_t event) {
+  KD_TRY(require_init());
+  KD_CUDA_CHECK(cudaEventDestroy(reinterpret_cast<cudaEvent_t>(event)));
+  return KD_OK;
+}

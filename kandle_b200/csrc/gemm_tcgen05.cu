@@ -1,6 +1,408 @@
+// bf16 GEMM on the 5th-generation tensor cores: out[M,N] = A[M,K] * W[N,K]^T (+ epilogue).
+//
+// This is the `linear` hot op of the prefill (the reference computes it with a 32x32 scalar-FMA
+// WGSL tile, packages/backend-webgpu/src/kernels/matrix/builder.ts:837-1066).  Both operands are
+// K-major, which is exactly what `linear` passes: activations [tokens, K] and the weight stored
+// [N, K] (packages/core/src/dispatch/handlers/composite.ts:62-70).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: 128x64 A tile + BLOCK_Nx64 W tile per stage, 128-byte swizzle,
+//               mbarrier complete_tx; loads are plain tiled loads (no cluster multicast).
+//   warp 1      one elected thread issues tcgen05.mma (M=128, N=BLOCK_N, K=16 x4 per stage) into a
+//               TMEM accumulator; tcgen05.commit releases the smem stage / publishes the tile.
+//   warps 2-5   epilogue: tcgen05.ld the 128xBLOCK_N fp32 tile (one row per thread), apply the
+//               fused epilogue, convert and store.  Two TMEM accumulators let the epilogue of tile
+//               i overlap the mainloop of tile i+1.
+// Fused epilogues: residual add (o_proj / down_proj) and SiLU(gate)*up for a weight whose rows
+// interleave 128 gate rows with 128 up rows per 256-row block.
+//
+// Roofline: tensor-core bound; 2*M*N*K flops per call.
 #include "common.cuh"
 #include "kernels.cuh"
+#include "sm100.cuh"
+
 namespace kd {
-int matmul_tc_try(const kd_matmul_cfg*, const kd_tensor*, const kd_tensor*, const kd_tensor*, const kd_tensor*, int* handled) { *handled = 0; return KD_OK; }
-int attention_tc_try(const kd_tensor*, const kd_tensor*, const kd_tensor*, const kd_tensor*, const AttnParams&, int* handled) { *handled = 0; return KD_OK; }
+
+using namespace sm100;
+
+// ----------------------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
 }
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                      uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(KD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  KD_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base address must be 16-byte aligned");
+  KD_REQUIRE((row_stride * 2) % 16 == 0, "TMA row stride must be a multiple of 16 bytes (got %llu elements)",
+             (unsigned long long)row_stride);
+  KD_REQUIRE(box_cols * 2 <= 128 && box_rows <= 256, "TMA box [%u,%u] too large for 128-byte swizzle", box_rows, box_cols);
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {row_stride * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(KD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return KD_OK;
+}
+
+int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t d2, uint64_t rows, uint64_t cols, uint64_t stride2,
+                      uint64_t row_stride, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(KD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  KD_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base address must be 16-byte aligned");
+  KD_REQUIRE((row_stride * 2) % 16 == 0 && (stride2 * 2) % 16 == 0, "TMA strides must be multiples of 16 bytes");
+  KD_REQUIRE(box_cols * 2 <= 128 && box_rows <= 256, "TMA box [%u,%u] too large for 128-byte swizzle", box_rows, box_cols);
+  cuuint64_t gdim[3] = {cols, rows, d2};
+  cuuint64_t gstr[2] = {row_stride * 2, stride2 * 2};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(KD_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with code %d", (int)r);
+  return KD_OK;
+}
+
+// ----------------------------------------------------------------------------- kernel
+struct GemmParams {
+  int M, N, K;            // N = rows of W (for EPI_SWIGLU the output is N/2 wide)
+  void* out;
+  int64_t ldo;
+  int out_f32;            // 0: bf16 output, 1: fp32 output
+  const __nv_bfloat16* resid;
+  int64_t ldr;
+  int epi;
+  int num_m_tiles, num_n_tiles;
+  int* err;
+};
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ float silu_f(float x) {
+  return x / (1.0f + __expf(-fminf(fmaxf(x, -88.f), 88.f)));
+}
+
+template <int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+  constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  constexpr int B_BYTES = BLOCK_N * GEMM_BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N < 32 ? 32 : 2 * BLOCK_N;
+  constexpr uint32_t IDESC = make_idesc_bf16(GEMM_BM, BLOCK_N, 0, 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_k_blocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int total_tiles = p.num_m_tiles * p.num_n_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int m_tile = tile / p.num_n_tiles, n_tile = tile - m_tile * p.num_n_tiles;
+        for (int kb = 0; kb < num_k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.err, 201)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &full[stage], kb * GEMM_BK, m_tile * GEMM_BM);
+          tma_load_2d(sa + A_BYTES, &tmap_b, &full[stage], kb * GEMM_BK, n_tile * BLOCK_N);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, 202)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+        for (int kb = 0; kb < num_k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.err, 203)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            umma_ss(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int m_tile = tile / p.num_n_tiles, n_tile = tile - m_tile * p.num_n_tiles;
+      bool ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.err, 204);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_tile * GEMM_BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N);
+      if (p.epi == 2) {
+        // SiLU(gate) * up: columns [0,BLOCK_N/2) are gate, [BLOCK_N/2,BLOCK_N) the matching up columns
+        constexpr int HALF = BLOCK_N / 2;
+        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + (int64_t)n_tile * HALF;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HALF; c0 += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c0, g);
+          tmem_ld_32x32(t_row + HALF + c0, u);
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int col = n_tile * HALF + c0 + j * 8;
+              if (col + 8 <= p.N / 2) {
+                uint4 v;
+                uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float a0 = silu_f(__uint_as_float(g[j * 8 + 2 * e])) * __uint_as_float(u[j * 8 + 2 * e]);
+                  const float a1 = silu_f(__uint_as_float(g[j * 8 + 2 * e + 1])) * __uint_as_float(u[j * 8 + 2 * e + 1]);
+                  vv[e] = pack_bf16(a0, a1);
+                }
+                *reinterpret_cast<uint4*>(orow + c0 + j * 8) = v;
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c0, r);
+          tmem_wait_ld();
+          if (row_ok) {
+            const int col0 = n_tile * BLOCK_N + c0;
+            if (p.epi == 1) {
+              const __nv_bfloat16* rrow = p.resid + (int64_t)row * p.ldr + col0;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col0 + j * 8 + 8 <= p.N) {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(rrow + j * 8);
+                  const uint32_t* rr = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    r[j * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e]) + bf16_lo(rr[e]));
+                    r[j * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e + 1]) + bf16_hi(rr[e]));
+                  }
+                }
+              }
+            }
+            if (p.out_f32) {
+              float* orow = static_cast<float*>(p.out) + (int64_t)row * p.ldo + col0;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (col0 + j * 4 + 4 <= p.N)
+                  *reinterpret_cast<float4*>(orow + j * 4) =
+                      make_float4(__uint_as_float(r[j * 4]), __uint_as_float(r[j * 4 + 1]), __uint_as_float(r[j * 4 + 2]),
+                                  __uint_as_float(r[j * 4 + 3]));
+              }
+            } else {
+              __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + col0;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col0 + j * 8 + 8 <= p.N) {
+                  uint4 v;
+                  v.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+                  v.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+                  v.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+                  v.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+                  *reinterpret_cast<uint4*>(orow + j * 8) = v;
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // teardown: every role falls through to here, also after an aborted wait
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BLOCK_N, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p) {
+  constexpr int STAGE_BYTES = GEMM_BM * GEMM_BK * 2 + BLOCK_N * GEMM_BK * 2;
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    KD_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BLOCK_N, STAGES>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured = true;
+  }
+  p.num_m_tiles = (p.M + GEMM_BM - 1) / GEMM_BM;
+  p.num_n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int total = p.num_m_tiles * p.num_n_tiles;
+  const int grid = total < ctx().sm_count ? total : ctx().sm_count;
+  gemm_bf16_tcgen05_kernel<BLOCK_N, STAGES><<<grid, GEMM_THREADS, SMEM, ctx().stream>>>(ta, tb, p);
+  return after_launch("gemm_bf16_tcgen05_kernel");
+}
+
+// out[M, N or N/2] = epilogue(A[M,K] * W[N,K]^T).  Pointers are device pointers; ld* in elements.
+int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out, int64_t ldo, int out_f32,
+              const void* resid, int64_t ldr, int M, int N, int K, int epi) {
+  KD_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem");
+  KD_REQUIRE(K % 8 == 0, "gemm: K=%d must be a multiple of 8 for the tensor-core path", K);
+  const int n_out = epi == 2 ? N / 2 : N;
+  KD_REQUIRE(n_out % 8 == 0 && ldo % (out_f32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+             "gemm: output width / leading dimension / address not 16-byte aligned");
+  if (epi == 1)
+    KD_REQUIRE(resid != nullptr && ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0,
+               "gemm: residual operand must be 16-byte aligned");
+  if (epi == 2) KD_REQUIRE(N % 256 == 0 && !out_f32, "gemm: SwiGLU epilogue needs N %% 256 == 0 and a bf16 output");
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
+  p.resid = static_cast<const __nv_bfloat16*>(resid); p.ldr = ldr;
+  p.epi = epi;
+  p.err = ctx().error_flag;
+  CUtensorMap ta, tb;
+  KD_TRY(make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GEMM_BM, GEMM_BK));
+  if (N >= 256 || epi == 2) {
+    KD_TRY(make_tmap_bf16_2d(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 256, GEMM_BK));
+    return launch_gemm<256, 4>(ta, tb, p);
+  }
+  if (N > 64) {
+    KD_TRY(make_tmap_bf16_2d(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, GEMM_BK));
+    return launch_gemm<128, 6>(ta, tb, p);
+  }
+  KD_TRY(make_tmap_bf16_2d(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 64, GEMM_BK));
+  return launch_gemm<64, 8>(ta, tb, p);
+}
+
+// ----------------------------------------------------------------------------- dispatch from kd_matmul
+int matmul_tc_try(const kd_matmul_cfg* cfg, const kd_tensor* a, const kd_tensor* b, const kd_tensor* c,
+                  const kd_tensor* out, int* handled) {
+  *handled = 0;
+  if (a->dtype != KD_BF16 || b->dtype != KD_BF16) return KD_OK;
+  if (out->dtype != KD_BF16 && out->dtype != KD_F32) return KD_OK;
+  if (cfg->alpha != 1.0f) return KD_OK;
+  if (a->ndim < 2 || b->ndim != 2 || !is_contiguous(out)) return KD_OK;
+  // A must be logically [rows..., K] with unit K stride and collapsible leading dims.
+  if (cfg->transpose_a) return KD_OK;
+  if (a->strides[a->ndim - 1] != 1 && a->shape[a->ndim - 1] != 1) return KD_OK;
+  int64_t lda = a->strides[a->ndim - 2];
+  int64_t rows = a->shape[a->ndim - 2];
+  for (int d = a->ndim - 3; d >= 0; --d) {
+    if (a->shape[d] != 1 && a->strides[d] != lda * rows) return KD_OK;
+    rows *= a->shape[d];
+  }
+  // W must be K-major: stored [N,K] with transposeB, or a [K,N] view with strides [1, ld].
+  int64_t ldw;
+  if (cfg->transpose_b) {
+    if (b->strides[1] != 1) return KD_OK;
+    ldw = b->strides[0];
+  } else {
+    if (b->strides[0] != 1) return KD_OK;
+    ldw = b->strides[1];
+  }
+  const int64_t M = rows, N = cfg->N, K = cfg->K;
+  if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffff) return KD_OK;
+  if (K % 8 || N % 8 || lda % 8 || ldw % 8) return KD_OK;
+  int epi = 0;
+  void* pc = nullptr;
+  if (cfg->has_c && c != nullptr && cfg->beta != 0.f) {
+    if (cfg->beta != 1.0f || c->dtype != KD_BF16 || !is_contiguous(c) || numel(c) != M * N) return KD_OK;
+    KD_TRY(tensor_ptr(c, &pc));
+    epi = 1;
+  }
+  void *pa = nullptr, *pb = nullptr, *po = nullptr;
+  KD_TRY(tensor_ptr(a, &pa));
+  KD_TRY(tensor_ptr(b, &pb));
+  KD_TRY(tensor_ptr(out, &po));
+  if ((reinterpret_cast<uintptr_t>(pa) | reinterpret_cast<uintptr_t>(pb) | reinterpret_cast<uintptr_t>(po)) & 15) return KD_OK;
+  if (pc && (reinterpret_cast<uintptr_t>(pc) & 15)) return KD_OK;
+  KD_TRY(gemm_bf16(pa, lda, pb, ldw, po, N, out->dtype == KD_F32, pc, N, (int)M, (int)N, (int)K, epi));
+  *handled = 1;
+  return KD_OK;
+}
+
+int attention_tc_try(const kd_tensor*, const kd_tensor*, const kd_tensor*, const kd_tensor*, const AttnParams&,
+                     int* handled) {
+  *handled = 0;
+  return KD_OK;
+}
+
+}  // namespace kd

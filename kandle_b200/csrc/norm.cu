@@ -87,7 +87,8 @@ __global__ void __launch_bounds__(THREADS) norm_kernel(const void* __restrict__ 
     float a0 = 0.f, a1 = 0.f;
     if (MODE == NORM_SOFTMAX) a0 = -1e38f;
     // pass 1
-    if (dt_x == KD_F32 && last == 1 && ((base & 3) == 0) && ((n & 3) == 0)) {
+    if (dt_x == KD_F32 && last == 1 && ((n & 3) == 0) &&
+        ((reinterpret_cast<uintptr_t>(static_cast<const float*>(x) + base) & 15) == 0)) {
       const float4* xv = reinterpret_cast<const float4*>(static_cast<const float*>(x) + base);
       for (int64_t i = tid; i < cnt / 4; i += G) {
         const float4 v = xv[i];
@@ -202,7 +203,8 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const void* __restrict_
     const int64_t base = ridx.row_offset(row);
     float best = -3.402823466e38f;
     int64_t bi = 0x7fffffffffffffffLL;
-    if (dt_x == KD_BF16 && ridx.last == 1 && ((base & 7) == 0)) {
+    if (dt_x == KD_BF16 && ridx.last == 1 &&
+        ((reinterpret_cast<uintptr_t>(static_cast<const __nv_bfloat16*>(x) + base) & 15) == 0)) {
       const uint4* xv = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + base);
       for (int64_t i = threadIdx.x; i < n / 8; i += THREADS) {
         const uint4 u = xv[i];
@@ -217,7 +219,8 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const void* __restrict_
         const float v = load_float(x, dt_x, base + i);
         if (v > best) { best = v; bi = i; }
       }
-    } else if (dt_x == KD_F32 && ridx.last == 1 && ((base & 3) == 0)) {
+    } else if (dt_x == KD_F32 && ridx.last == 1 &&
+               ((reinterpret_cast<uintptr_t>(static_cast<const float*>(x) + base) & 15) == 0)) {
       const float4* xv = reinterpret_cast<const float4*>(static_cast<const float*>(x) + base);
       for (int64_t i = threadIdx.x; i < n / 4; i += THREADS) {
         const float4 u = xv[i];

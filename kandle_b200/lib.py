@@ -85,7 +85,7 @@ def round_to_bf16(a: np.ndarray) -> np.ndarray:
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m kandle_b200.build` (needs nvcc). "
+        f"{LIB_PATH} is missing: build it with `python kandle_b200/build.py` (needs nvcc). "
         "kandle_b200 has no CPU fallback.")
 
 _lib = ctypes.CDLL(LIB_PATH)
@@ -125,6 +125,11 @@ _SIGNATURES = {
     "kd_arange": [_T, ctypes.c_double, ctypes.c_double],
     "kd_argmax": [_T, _T],
     "kd_conv1d": [_T, _T, _T, ctypes.c_int, ctypes.c_int, _T],
+    "kd_event_create": [ctypes.POINTER(_u64)],
+    "kd_event_record": [_u64],
+    "kd_event_elapsed_ms": [_u64, _u64, ctypes.POINTER(ctypes.c_float)],
+    "kd_event_destroy": [_u64],
+    "kd_linear_bf16": [_T, _T, _T, ctypes.c_int, _T],
 }
 
 

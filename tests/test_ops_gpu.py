@@ -102,7 +102,7 @@ def test_matmul_dispatch_cases(backend, oracle):
     # vectors
     close(core.matmul(Tensor(a[:, 0]), Tensor(b)).dataAsync(), a[:, 0] @ b)
     with pytest.raises(ValueError):
-        core.matmul(Tensor(a), Tensor(c))
+        core.matmul(Tensor(a), Tensor(b))
 
 
 # ------------------------------------------------------------------ normalisation
@@ -132,7 +132,13 @@ def test_layer_norm(backend, oracle, rows, n):
 @pytest.mark.parametrize("rows,n", [(9, 333), (2, 151936), (64, 77)])
 def test_softmax(backend, oracle, rows, n):
     x = synth.normal("x", (rows, n), 4.0)
-    close(core.softmax(Tensor(x), -1).dataAsync(), oracle.softmax(x))
+    got = core.softmax(Tensor(x), -1).dataAsync()
+    xd = x.astype(np.float64)
+    e = np.exp(xd - xd.max(-1, keepdims=True))
+    close(got, e / e.sum(-1, keepdims=True), 1e-5)
+    # The oracle keeps the reference's strictly serial fp32 sum, whose own rounding noise over a
+    # 151 936-long row is ~2e-4 relative; the kernel's tree reduction sits closer to float64.
+    close(got, oracle.softmax(x), 1e-4 if n < 10000 else 5e-4)
 
 
 # ------------------------------------------------------------------ pointwise / copy
@@ -205,6 +211,8 @@ def test_embedding_and_argmax(backend, oracle):
     assert got.dtype == np.int64 and np.array_equal(got, oracle.argmax_rows(x)) and got[2] == 10
     xb = lib.round_to_bf16(x)
     assert np.array_equal(core.argmax(Tensor(xb, dtype="bfloat16"), -1).dataAsync(), oracle.argmax_rows(xb))
+    sel = Tensor(x).slice(":, 3:")                                   # rows start at unaligned addresses
+    assert np.array_equal(sel.dataAsync(), x[:, 3:]) and np.array_equal(core.argmax(sel, 1).dataAsync(), np.argmax(x[:, 3:], 1))
     y = synth.normal("y", (6, 5, 7))
     assert np.array_equal(core.argmax(Tensor(y), 1).dataAsync(), np.argmax(y, 1))
 
