@@ -399,10 +399,4 @@ int matmul_tc_try(const kd_matmul_cfg* cfg, const kd_tensor* a, const kd_tensor*
   return KD_OK;
 }
 
-int attention_tc_try(const kd_tensor*, const kd_tensor*, const kd_tensor*, const kd_tensor*, const AttnParams&,
-                     int* handled) {
-  *handled = 0;
-  return KD_OK;
-}
-
 }  // namespace kd
