@@ -201,6 +201,25 @@ typedef enum kd_epilogue {
 int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* residual, int epilogue,
                    const kd_tensor* out);
 
+/* Decode attention: one new query position per sequence against a KV cache.  Computes what the
+ * reference computes with `_repeatKv` (materialised GQA expansion) + `flash_attention` with
+ * isCausal=false on the cache prefix views (packages/model-utils/src/attention/gqa.ts:325-336,
+ * 407-414; cache layout packages/model-utils/src/kv-cache.ts:123-130,197-211), without the copies.
+ * q/out [B,Hq,1,D]; k_cache/v_cache [B,Hkv,maxS,D]; keys [0, ctx) are attended.  ctx comes from
+ * `ctx_len` (device int32 scalar, so a captured graph can be replayed as the sequence grows) or,
+ * when that is NULL, from ctx_len_host.  splits = 0 picks the split-KV factor automatically.
+ * Scratch for the split partials is library-owned and grows on demand (the first call at a larger
+ * size allocates, so make that call before capturing a graph). */
+int kd_attention_decode(const kd_tensor* q, const kd_tensor* k_cache, const kd_tensor* v_cache,
+                        const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
+                        const kd_tensor* out);
+/* Paged variant (no counterpart in the reference, which only has the contiguous static cache):
+ * k_pool/v_pool [pages,Hkv,128,D]; block_table [B,max_pages] int32 names the page of each
+ * 128-key tile of each sequence. */
+int kd_attention_decode_paged(const kd_tensor* q, const kd_tensor* k_pool, const kd_tensor* v_pool,
+                              const kd_tensor* block_table, const kd_tensor* ctx_len, int ctx_len_host,
+                              float scale, int splits, const kd_tensor* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,6 +21,17 @@
 // beyond Skv in the last block are masked.  Heavy (late) query tiles are scheduled first.
 //
 // Roofline: tensor-core bound, 4*B*Hq*D*P flops (P = number of unmasked (q,k) pairs).
+//
+// DECODE mode (one new token per sequence against a KV cache) reuses the same pipeline with the
+// query tile holding the Hq/Hkv query heads that share one KV head (the other rows of the 128-row
+// MMA tile are zero padding, which costs nothing: the kernel is HBM-bound).  The key range of a
+// (batch, kv-head) pair is split across CTAs (split-KV); each CTA writes an un-normalised partial
+// output plus its (max, sum) statistics to scratch and a second kernel combines the splits.  The
+// context length is read from device memory so that a captured CUDA graph can be replayed while
+// the sequence grows.  The cache is either contiguous [B,Hkv,maxS,D] (the reference's
+// StaticKVCache layout, packages/model-utils/src/kv-cache.ts:123-130) or paged: a pool
+// [pages,Hkv,128,D] addressed through a per-sequence block table (one page = one key tile).
+// Roofline for decode: HBM, 2*B*Hkv*ctx*D*2 bytes.
 #include "common.cuh"
 #include "kernels.cuh"
 #include "sm100.cuh"
@@ -72,6 +83,14 @@ struct FaParams {
   int64_t so_b, so_h, so_s;
   int num_q_tiles;
   int* err;
+  // decode mode
+  const int* ctx_ptr;          // device scalar: number of valid keys (NULL: use Skv)
+  const int* block_table;      // paged cache: [B, max_pages] page indices (NULL: contiguous cache)
+  int max_pages;
+  int splits;
+  int group;                   // query heads per KV head (valid rows of the tile)
+  float* part_o;               // [B, Hkv, splits, group, D] un-normalised partial outputs
+  float* part_ml;              // [B, Hkv, splits, group, 2] (running max in the log2 domain, sum)
 };
 
 constexpr int FA_BQ = 128;
@@ -79,16 +98,20 @@ constexpr int FA_BKV = 128;
 constexpr int FA_THREADS = 192;
 constexpr int FA_STAGES = 2;
 
-template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+template <int D, bool DECODE>
+__global__ void __launch_bounds__(FA_THREADS, DECODE ? 2 : 1)
 flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                const __grid_constant__ CUtensorMap tmap_v, FaParams p) {
   constexpr int SLABS = D / 64;                     // 64-wide head-dim slabs (one swizzle atom each)
   constexpr int Q_BYTES = FA_BQ * D * 2;
   constexpr int KV_BYTES = FA_BKV * D * 2;
   constexpr int SLAB_BYTES = FA_BKV * 128;          // 128 rows x 128 B
-  constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t S_COL0 = 0, O_COL0 = 256;      // S buffers at columns 0 and 128, O at 256
+  // prefill: two S buffers (columns 0 and 128) + O at 256; decode: one S buffer + O at 128, one
+  // smem stage per operand, so that two CTAs fit on an SM and overlap each other's latencies
+  constexpr int NSBUF = DECODE ? 1 : 2;
+  constexpr int STAGES = DECODE ? 1 : FA_STAGES;
+  constexpr uint32_t TMEM_COLS = DECODE ? 256 : 512;
+  constexpr uint32_t S_COL0 = 0, O_COL0 = DECODE ? 128 : 256;
   constexpr uint32_t IDESC_QK = make_idesc_bf16(FA_BQ, FA_BKV, 0, 0);
   constexpr uint32_t IDESC_PV = make_idesc_bf16(FA_BQ, D, 0, 1);
 
@@ -96,8 +119,8 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;
   uint8_t* k_smem = q_smem + Q_BYTES;                       // [STAGES][KV_BYTES]
-  uint8_t* v_smem = k_smem + FA_STAGES * KV_BYTES;          // [STAGES][KV_BYTES]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + FA_STAGES * KV_BYTES);
+  uint8_t* v_smem = k_smem + STAGES * KV_BYTES;          // [STAGES][KV_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + STAGES * KV_BYTES);
   uint64_t* q_full = bars;                 // 1
   uint64_t* k_full = bars + 1;             // 2
   uint64_t* k_empty = bars + 3;            // 2
@@ -110,21 +133,47 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = p.num_q_tiles - 1 - (int)blockIdx.x;   // heavy causal tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.Hq / p.Hkv);
-  const int q0 = q_tile * FA_BQ;
-  int kv_end = p.Skv;
-  if (p.causal) kv_end = min(p.Skv, q0 + FA_BQ);
-  const int n_blocks = (kv_end + FA_BKV - 1) / FA_BKV;
+  const int b = blockIdx.z;
+  int h, hk, q0, kv_len, j_begin, j_end, kv_end;
+  if (DECODE) {
+    hk = blockIdx.y;
+    h = hk;                     // Q tensor map is indexed by (row-in-group, kv head, batch)
+    q0 = 0;
+    kv_len = p.ctx_ptr ? *p.ctx_ptr : p.Skv;
+    kv_len = max(0, min(kv_len, p.Skv));
+    kv_end = kv_len;
+    const int n_total = (kv_len + FA_BKV - 1) / FA_BKV;
+    const int per_split = (n_total + p.splits - 1) / p.splits;
+    j_begin = (int)blockIdx.x * per_split;
+    j_end = min(n_total, j_begin + per_split);
+    if (j_begin >= j_end) {     // nothing for this split: publish an empty partial and leave
+      if ((int)threadIdx.x < p.group) {
+        const int64_t slot = (((int64_t)b * p.Hkv + hk) * p.splits + blockIdx.x) * p.group + threadIdx.x;
+        p.part_ml[slot * 2] = -1e30f;
+        p.part_ml[slot * 2 + 1] = 0.f;
+      }
+      return;
+    }
+  } else {
+    const int q_tile = p.num_q_tiles - 1 - (int)blockIdx.x;   // heavy causal tiles first
+    h = blockIdx.y;
+    hk = h / (p.Hq / p.Hkv);
+    q0 = q_tile * FA_BQ;
+    kv_len = p.Skv;
+    kv_end = p.Skv;
+    if (p.causal) kv_end = min(p.Skv, q0 + FA_BQ);
+    j_begin = 0;
+    j_end = (kv_end + FA_BKV - 1) / FA_BKV;
+  }
+  const int n_blocks = j_end - j_begin;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < FA_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4); }
+    for (int s = 0; s < NSBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4); }
     mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -148,31 +197,37 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * SLAB_BYTES, &tmap_q, q_full, s * 64, q0, h, b);
       int stage = 0;
       uint32_t phase = 0;
-      for (int j = 0; j < n_blocks; ++j) {
+      for (int jj = 0; jj < n_blocks; ++jj) {
+        // key-tile coordinates: rows j*128.. of sequence b, or row 0 of the page the block table names
+        int row = (j_begin + jj) * FA_BKV, outer = b;
+        if (DECODE && p.block_table) {
+          outer = p.block_table[(int64_t)b * p.max_pages + (j_begin + jj)];
+          row = 0;
+        }
         if (!mbar_wait(&k_empty[stage], phase ^ 1, abort_flag, p.err, 301)) break;
         mbar_arrive_expect_tx(&k_full[stage], KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(k_smem + stage * KV_BYTES + s * SLAB_BYTES, &tmap_k, &k_full[stage], s * 64, j * FA_BKV, hk, b);
+          tma_load_4d(k_smem + stage * KV_BYTES + s * SLAB_BYTES, &tmap_k, &k_full[stage], s * 64, row, hk, outer);
         if (!mbar_wait(&v_empty[stage], phase ^ 1, abort_flag, p.err, 302)) break;
         mbar_arrive_expect_tx(&v_full[stage], KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(v_smem + stage * KV_BYTES + s * SLAB_BYTES, &tmap_v, &v_full[stage], s * 64, j * FA_BKV, hk, b);
-        if (++stage == FA_STAGES) { stage = 0; phase ^= 1; }
+          tma_load_4d(v_smem + stage * KV_BYTES + s * SLAB_BYTES, &tmap_v, &v_full[stage], s * 64, row, hk, outer);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, 303);
       const uint32_t q_addr = smem_u32(q_smem);
-      // S(j) = Q K(j)^T into S buffer j&1
+      // S(j) = Q K(j)^T into S buffer j % NSBUF   (j counts this CTA's key tiles from 0)
       auto issue_qk = [&](int j) -> bool {
-        const int stage = j % FA_STAGES;
-        if (!mbar_wait(&k_full[stage], (uint32_t)((j / FA_STAGES) & 1), abort_flag, p.err, 304)) return false;
+        const int stage = j % STAGES;
+        if (!mbar_wait(&k_full[stage], (uint32_t)((j / STAGES) & 1), abort_flag, p.err, 304)) return false;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(k_smem + stage * KV_BYTES);
-        const uint32_t d_tmem = tmem_base + S_COL0 + (uint32_t)((j & 1) * FA_BKV);
+        const uint32_t d_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (uint32_t)((k / 4) * SLAB_BYTES + (k % 4) * 32);
@@ -180,20 +235,21 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
                   IDESC_QK, k != 0 ? 1u : 0u);
         }
         umma_commit(&k_empty[stage]);
-        umma_commit(&s_full[j & 1]);
+        umma_commit(&s_full[j % NSBUF]);
         return true;
       };
       if (ok) ok = issue_qk(0);
       for (int j = 0; ok && j < n_blocks; ++j) {
-        if (j + 1 < n_blocks) {
+        // with two S buffers the next QK^T is issued before this block's softmax has finished
+        if (NSBUF == 2 && j + 1 < n_blocks) {
           if (!issue_qk(j + 1)) break;
         }
-        const int stage = j % FA_STAGES;
-        if (!mbar_wait(&p_ready[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, p.err, 305)) break;
-        if (!mbar_wait(&v_full[stage], (uint32_t)((j / FA_STAGES) & 1), abort_flag, p.err, 306)) break;
+        const int stage = j % STAGES;
+        if (!mbar_wait(&p_ready[j % NSBUF], (uint32_t)((j / NSBUF) & 1), abort_flag, p.err, 305)) break;
+        if (!mbar_wait(&v_full[stage], (uint32_t)((j / STAGES) & 1), abort_flag, p.err, 306)) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(v_smem + stage * KV_BYTES);
-        const uint32_t p_tmem = tmem_base + S_COL0 + (uint32_t)((j & 1) * FA_BKV);
+        const uint32_t p_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
         const uint32_t o_tmem = tmem_base + O_COL0;
 #pragma unroll
         for (int k = 0; k < FA_BKV / 16; ++k) {
@@ -203,6 +259,10 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         }
         umma_commit(&v_empty[stage]);
         umma_commit(o_done);
+        // one S buffer: the next QK^T overwrites P, so it is issued after PV (in-order pipe)
+        if (NSBUF == 1 && j + 1 < n_blocks) {
+          if (!issue_qk(j + 1)) break;
+        }
       }
     }
   } else {
@@ -213,16 +273,16 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     float m_used = -1e30f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      ok = mbar_wait(&s_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, p.err, 307);
+      ok = mbar_wait(&s_full[j % NSBUF], (uint32_t)((j / NSBUF) & 1), abort_flag, p.err, 307);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + S_COL0 + (uint32_t)((j & 1) * FA_BKV);
+      const uint32_t s_addr = lane_addr + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
       uint32_t sr[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sr[c]);
       tmem_wait_ld();
-      const int kv0 = j * FA_BKV;
+      const int kv0 = (j_begin + j) * FA_BKV;
       // Only the diagonal block of a causal tile and the last (ragged) key block need masking;
       // the test is hoisted so that the common path carries no per-element predicates.
       if ((kv0 + FA_BKV > kv_end) || (p.causal && kv0 + FA_BKV - 1 > q0)) {
@@ -231,7 +291,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = kv0 + c * 32 + i;
-            if (col >= p.Skv || (p.causal && col > row)) sr[c][i] = __float_as_uint(-1e30f);
+            if (col >= kv_len || (p.causal && col > row)) sr[c][i] = __float_as_uint(-1e30f);
           }
       }
       float mx0 = -1e30f, mx1 = -1e30f;
@@ -292,7 +352,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
+      if (lane == 0) mbar_arrive(&p_ready[j % NSBUF]);
     }
     if (ok) {
       ok = mbar_wait(o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, p.err, 309);
@@ -300,25 +360,49 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     }
     if (ok) {
       tc_fence_after();
-      const float inv_l = 1.0f / l;
-      __nv_bfloat16* orow = p.o + (int64_t)b * p.so_b + (int64_t)h * p.so_h + (int64_t)row * p.so_s;
+      if (DECODE) {
+        // un-normalised partial output + statistics; only the first `group` rows are real queries
+        const int64_t slot = (((int64_t)b * p.Hkv + hk) * p.splits + blockIdx.x) * p.group + row_in_tile;
+        const bool valid = row_in_tile < p.group;
+        if (valid) {
+          p.part_ml[slot * 2] = m_used;
+          p.part_ml[slot * 2 + 1] = l;
+        }
+        float* prow = p.part_o + slot * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t orr[32];
-        tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
-        tmem_wait_ld();
-        if (row < p.Sq) {
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orr[32];
+          tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
+          tmem_wait_ld();
+          if (valid) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 v;
-            uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+            for (int g = 0; g < 8; ++g)
+              *reinterpret_cast<float4*>(prow + c * 32 + g * 4) =
+                  make_float4(__uint_as_float(orr[g * 4]), __uint_as_float(orr[g * 4 + 1]), __uint_as_float(orr[g * 4 + 2]),
+                              __uint_as_float(orr[g * 4 + 3]));
+          }
+        }
+      } else {
+        const float inv_l = 1.0f / l;
+        __nv_bfloat16* orow = p.o + (int64_t)b * p.so_b + (int64_t)h * p.so_h + (int64_t)row * p.so_s;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orr[32];
+          tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
+          tmem_wait_ld();
+          if (row < p.Sq) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(orr[g * 8 + 2 * e]) * inv_l,
-                                                       __uint_as_float(orr[g * 8 + 2 * e + 1]) * inv_l);
-              vv[e] = *reinterpret_cast<uint32_t*>(&t);
+            for (int g = 0; g < 4; ++g) {
+              uint4 v;
+              uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(orr[g * 8 + 2 * e]) * inv_l,
+                                                         __uint_as_float(orr[g * 8 + 2 * e + 1]) * inv_l);
+                vv[e] = *reinterpret_cast<uint32_t*>(&t);
+              }
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
             }
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
           }
         }
       }
@@ -334,17 +418,18 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   }
 }
 
-template <int D>
-static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p) {
-  constexpr int SMEM = FA_BQ * D * 2 + 2 * FA_STAGES * FA_BKV * D * 2 + 1024 + 256;
+template <int D, bool DECODE>
+static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid) {
+  constexpr int STAGES = DECODE ? 1 : FA_STAGES;
+  constexpr int SMEM = FA_BQ * D * 2 + 2 * STAGES * FA_BKV * D * 2 + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    KD_CUDA_CHECK(cudaFuncSetAttribute(flash_attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    KD_CUDA_CHECK(cudaFuncSetAttribute(flash_attention_tcgen05_kernel<D, DECODE>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured = true;
   }
-  dim3 grid(p.num_q_tiles, p.Hq, p.B);
-  flash_attention_tcgen05_kernel<D><<<grid, FA_THREADS, SMEM, ctx().stream>>>(tq, tk, tv, p);
-  return after_launch("flash_attention_tcgen05_kernel");
+  flash_attention_tcgen05_kernel<D, DECODE><<<grid, FA_THREADS, SMEM, ctx().stream>>>(tq, tk, tv, p);
+  return after_launch(DECODE ? "flash_attention_tcgen05_kernel<decode>" : "flash_attention_tcgen05_kernel");
 }
 
 int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out,
@@ -353,7 +438,7 @@ int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   if (a.dt_q != KD_BF16 || a.dt_k != KD_BF16 || a.dt_v != KD_BF16 || a.dt_o != KD_BF16) return KD_OK;
   if (a.D != 64 && a.D != 128) return KD_OK;
   if (!(a.scale > 0.f)) return KD_OK;  // the kernel takes the row max before scaling
-  if (a.Sq < 16) return KD_OK;  // single-row (decode) shapes are bandwidth-bound: CUDA-core / split-KV kernels
+  if (a.Sq < 16) return KD_OK;  // single-row (decode) shapes go through kd_attention_decode or the CUDA-core kernel
   if (a.B == 0 || a.Hq == 0 || a.Skv == 0) return KD_OK;
   if (a.Hq > 65535 || a.B > 65535) return KD_OK;
   if (a.sq[3] != 1 || a.sk[3] != 1 || a.sv[3] != 1 || a.so[3] != 1) return KD_OK;
@@ -381,10 +466,127 @@ int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   p.so_b = a.so[0]; p.so_h = a.so[1]; p.so_s = a.so[2];
   p.num_q_tiles = (a.Sq + FA_BQ - 1) / FA_BQ;
   p.err = ctx().error_flag;
-  if (a.D == 128) KD_TRY(launch_fa<128>(tq, tk, tv, p));
-  else KD_TRY(launch_fa<64>(tq, tk, tv, p));
+  dim3 grid(p.num_q_tiles, p.Hq, p.B);
+  if (a.D == 128) KD_TRY((launch_fa<128, false>(tq, tk, tv, p, grid)));
+  else KD_TRY((launch_fa<64, false>(tq, tk, tv, p, grid)));
   *handled = 1;
   return KD_OK;
+}
+
+// ----------------------------------------------------------------------------- split-KV combine
+// out[b, h, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s,  M = max_s m_s.
+// One warp per (batch, query head); lanes stride over the head dimension.
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      __nv_bfloat16* __restrict__ out, int64_t so_b, int64_t so_h, int B, int Hkv,
+                                      int group, int splits, int D) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int Hq = Hkv * group;
+  if (warp >= B * Hq) return;
+  const int b = warp / Hq, h = warp - b * Hq;
+  const int hk = h / group, r = h - hk * group;
+  const int64_t base = ((int64_t)b * Hkv + hk) * splits;
+  float M = -1e30f;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[((base + s) * group + r) * 2]);
+  float denom = 0.f;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const int64_t slot = (base + s) * group + r;
+    const float l = part_ml[slot * 2 + 1];
+    if (l == 0.f) continue;  // empty split: its output row was never written
+    const float w = exp2f(part_ml[slot * 2] - M);
+    denom += w * l;
+    const float* po = part_o + slot * D;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) acc[i] += w * po[d];
+    }
+  }
+  const float inv = 1.0f / denom;
+  __nv_bfloat16* orow = out + (int64_t)b * so_b + (int64_t)h * so_h;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) orow[d] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+// Scratch needed by attention_decode for a given problem (bytes).
+size_t attention_decode_scratch_bytes(int B, int Hkv, int group, int splits, int D) {
+  return (size_t)B * Hkv * splits * group * (D + 2) * sizeof(float);
+}
+
+// q [B,Hq,1,D] (any strides, unit d stride), cache k/v [B,Hkv,maxS,D] or pool [pages,Hkv,128,D]
+// with block_table [B,max_pages]; out [B,Hq,1,D].  `scratch` holds the split partials.
+int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
+                     const int* ctx_dev, int ctx_host, const int* block_table, int max_pages, int splits,
+                     void* scratch, size_t scratch_bytes) {
+  KD_REQUIRE(q->ndim == 4 && k->ndim == 4 && v->ndim == 4 && out->ndim == 4, "attention_decode: operands must be 4-D");
+  KD_REQUIRE(q->dtype == KD_BF16 && k->dtype == KD_BF16 && v->dtype == KD_BF16 && out->dtype == KD_BF16,
+             "attention_decode: bf16 tensors required");
+  const int B = (int)q->shape[0], Hq = (int)q->shape[1], D = (int)q->shape[3];
+  const int Hkv = (int)k->shape[1];
+  KD_REQUIRE(q->shape[2] == 1 && out->shape[2] == 1, "attention_decode: exactly one query position per sequence");
+  KD_REQUIRE(D == 64 || D == 128, "attention_decode: head_dim must be 64 or 128");
+  KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 128, "attention_decode: bad head counts %d / %d", Hq, Hkv);
+  KD_REQUIRE(v->shape[1] == Hkv && v->shape[2] == k->shape[2] && v->shape[3] == D && k->shape[3] == D,
+             "attention_decode: K and V cache shapes differ");
+  KD_REQUIRE(scale > 0.f, "attention_decode: scale must be positive");
+  KD_REQUIRE(splits >= 1 && splits <= 1024, "attention_decode: splits out of range");
+  const int group = Hq / Hkv;
+  int Skv;
+  if (block_table) {
+    KD_REQUIRE(k->shape[2] == FA_BKV, "attention_decode: paged cache needs pages of %d rows", FA_BKV);
+    Skv = max_pages * FA_BKV;
+  } else {
+    KD_REQUIRE(k->shape[0] == B, "attention_decode: cache batch differs from the query batch");
+    Skv = (int)k->shape[2];
+  }
+  if (!ctx_dev) KD_REQUIRE(ctx_host >= 1 && ctx_host <= Skv, "attention_decode: context length %d outside [1,%d]", ctx_host, Skv);
+  KD_REQUIRE(q->strides[3] == 1 && k->strides[3] == 1 && v->strides[3] == 1 && out->strides[3] == 1,
+             "attention_decode: unit stride along head_dim required");
+  for (int i = 0; i < 3; ++i)
+    KD_REQUIRE(q->strides[i] % 8 == 0 && k->strides[i] % 8 == 0 && v->strides[i] % 8 == 0,
+               "attention_decode: strides must be multiples of 8 elements");
+  KD_REQUIRE(scratch_bytes >= attention_decode_scratch_bytes(B, Hkv, group, splits, D), "attention_decode: scratch too small");
+  void *pq = nullptr, *pk = nullptr, *pv = nullptr, *po = nullptr;
+  KD_TRY(tensor_ptr(q, &pq));
+  KD_TRY(tensor_ptr(k, &pk));
+  KD_TRY(tensor_ptr(v, &pv));
+  KD_TRY(tensor_ptr(out, &po));
+  KD_REQUIRE(((reinterpret_cast<uintptr_t>(pq) | reinterpret_cast<uintptr_t>(pk) | reinterpret_cast<uintptr_t>(pv)) & 15) == 0,
+             "attention_decode: operands must be 16-byte aligned");
+  if (B == 0) return KD_OK;
+  // Q viewed as [B, Hkv, group, D]: the tile's rows are the query heads of one KV group.
+  const int64_t eq[4] = {B, Hkv, group, D};
+  const int64_t sq[3] = {q->strides[0], q->strides[1] * group, q->strides[1]};
+  const int64_t ek[4] = {k->shape[0], Hkv, k->shape[2], D};
+  CUtensorMap tq, tk, tv;
+  KD_TRY(make_tmap_bhsd(&tq, pq, eq, sq, FA_BQ));
+  KD_TRY(make_tmap_bhsd(&tk, pk, ek, k->strides, FA_BKV));
+  KD_TRY(make_tmap_bhsd(&tv, pv, ek, v->strides, FA_BKV));
+  FaParams p{};
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = group; p.Skv = ctx_dev ? Skv : ctx_host;
+  p.causal = 0;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = ctx().error_flag;
+  p.ctx_ptr = ctx_dev;
+  p.block_table = block_table;
+  p.max_pages = max_pages;
+  p.splits = splits;
+  p.group = group;
+  p.part_o = static_cast<float*>(scratch);
+  p.part_ml = p.part_o + (size_t)B * Hkv * splits * group * D;
+  dim3 grid(splits, Hkv, B);
+  if (D == 128) KD_TRY((launch_fa<128, true>(tq, tk, tv, p, grid)));
+  else KD_TRY((launch_fa<64, true>(tq, tk, tv, p, grid)));
+  const int warps = B * Hq;
+  decode_combine_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx().stream>>>(p.part_o, p.part_ml, static_cast<__nv_bfloat16*>(po),
+                                                                         out->strides[0], out->strides[1], B, Hkv, group,
+                                                                         splits, D);
+  return after_launch("decode_combine_kernel");
 }
 
 }  // namespace kd

@@ -55,3 +55,56 @@ KD_API int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_
   }
   return gemm_bf16(px, K, pw, weight->strides[0], po, n_out, out->dtype == KD_F32, pr, N, (int)M, (int)N, (int)K, epilogue);
 }
+
+static int decode_common(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* block_table,
+                         const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits, const kd_tensor* out) {
+  KD_TRY(require_init());
+  KD_REQUIRE(q && k && v && out, "null tensor");
+  KD_REQUIRE(q->ndim == 4 && k->ndim == 4, "decode attention operands must be 4-D");
+  const int* ctx_dev = nullptr;
+  if (ctx_len) {
+    KD_REQUIRE(ctx_len->dtype == KD_I32 && numel(ctx_len) == 1, "ctx_len must be a device int32 scalar");
+    void* pc = nullptr;
+    KD_TRY(tensor_ptr(ctx_len, &pc));
+    ctx_dev = static_cast<const int*>(pc);
+  }
+  const int* table = nullptr;
+  int max_pages = 0;
+  if (block_table) {
+    KD_REQUIRE(block_table->dtype == KD_I32 && block_table->ndim == 2 && is_contiguous(block_table) &&
+                   block_table->shape[0] == q->shape[0],
+               "block_table must be a contiguous int32 [B, max_pages] tensor");
+    void* pt = nullptr;
+    KD_TRY(tensor_ptr(block_table, &pt));
+    table = static_cast<const int*>(pt);
+    max_pages = (int)block_table->shape[1];
+  }
+  const int B = (int)q->shape[0], Hq = (int)q->shape[1], Hkv = (int)k->shape[1], D = (int)q->shape[3];
+  KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "bad head counts");
+  const int max_keys = table ? max_pages * 128 : (int)k->shape[2];
+  const int max_blocks = (max_keys + 127) / 128;
+  if (splits <= 0) {
+    // aim at ~4 CTAs per SM worth of work items, never more splits than key tiles
+    const int pairs = B * Hkv > 0 ? B * Hkv : 1;
+    splits = (4 * ctx().sm_count + pairs - 1) / pairs;
+    if (splits > max_blocks) splits = max_blocks;
+    if (splits < 1) splits = 1;
+  }
+  const size_t need = attention_decode_scratch_bytes(B, Hkv, Hq / Hkv, splits, D);
+  void* scratch = nullptr;
+  KD_TRY(get_workspace(need, &scratch));
+  return attention_decode(q, k, v, out, scale, ctx_dev, ctx_len_host, table, max_pages, splits, scratch, need);
+}
+
+KD_API int kd_attention_decode(const kd_tensor* q, const kd_tensor* k_cache, const kd_tensor* v_cache,
+                               const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
+                               const kd_tensor* out) {
+  return decode_common(q, k_cache, v_cache, nullptr, ctx_len, ctx_len_host, scale, splits, out);
+}
+
+KD_API int kd_attention_decode_paged(const kd_tensor* q, const kd_tensor* k_pool, const kd_tensor* v_pool,
+                                     const kd_tensor* block_table, const kd_tensor* ctx_len, int ctx_len_host,
+                                     float scale, int splits, const kd_tensor* out) {
+  KD_REQUIRE(block_table != nullptr, "kd_attention_decode_paged needs a block table");
+  return decode_common(q, k_pool, v_pool, block_table, ctx_len, ctx_len_host, scale, splits, out);
+}

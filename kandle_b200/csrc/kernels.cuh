@@ -29,4 +29,9 @@ int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out,
 int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out,
                      const AttnParams& p, int* handled);
 
+size_t attention_decode_scratch_bytes(int B, int Hkv, int group, int splits, int D);
+int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
+                     const int* ctx_dev, int ctx_host, const int* block_table, int max_pages, int splits,
+                     void* scratch, size_t scratch_bytes);
+
 }  // namespace kd

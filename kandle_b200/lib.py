@@ -130,6 +130,8 @@ _SIGNATURES = {
     "kd_event_elapsed_ms": [_u64, _u64, ctypes.POINTER(ctypes.c_float)],
     "kd_event_destroy": [_u64],
     "kd_linear_bf16": [_T, _T, _T, ctypes.c_int, _T],
+    "kd_attention_decode": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
+    "kd_attention_decode_paged": [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
 }
 
 
