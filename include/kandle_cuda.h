@@ -192,14 +192,55 @@ int kd_event_destroy(uint64_t event);
  * ------------------------------------------------------------------------------------------- */
 typedef enum kd_epilogue {
   KD_EPI_NONE = 0,
-  KD_EPI_RESIDUAL = 1, /* out = residual + x W^T : `linear` followed by the residual `add`     */
+  KD_EPI_RESIDUAL = 1, /* out = residual + x W^T : `linear` followed by the residual `add`;
+                          residual has the output's dtype (bf16, or fp32 residual stream) */
   KD_EPI_SWIGLU = 2    /* out = silu(x Wg^T) * (x Wu^T) : gate/up `linear`, `silu`, `mul`;
-                          weight rows interleave 128 gate rows / 128 up rows per 256-row block */
+                          weight rows interleave 16 gate rows / 16 up rows per 32-row block      */
 } kd_epilogue;
 /* `linear` on the tensor cores (tcgen05): x [tokens,K] bf16, weight [N,K] bf16 (K-major, as
  * composite.ts:62-70 passes it), out [tokens,N] (or [tokens,N/2] for SWIGLU) bf16 or fp32. */
 int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* residual, int epilogue,
                    const kd_tensor* out);
+
+/* `linear` for 1..128 activation rows (decode): weights are streamed once from HBM with the
+ * operands swapped so that weight rows fill the MMA's M dimension.  out is either bf16 [rows,N]
+ * or fp32 [splits,rows,N] split-K partial sums that the consumers below add up (splits is taken
+ * from out's leading extent; the `splits` argument only matters for choosing that extent: 0 asks
+ * the library, see kd_linear_bf16_skinny_splits). */
+int kd_linear_bf16_skinny(const kd_tensor* x, const kd_tensor* weight, int splits, const kd_tensor* out);
+int kd_linear_bf16_skinny_splits(int64_t N, int64_t K, int* splits_out);
+
+/* cos/sin tables [seq_len, D/2] fp32 for positions start..start+seq_len-1: arange -> mul(inv_freq)
+ * -> cos / sin of packages/model-utils/src/rope.ts:192-261.  `pos` (device int32 scalar) overrides
+ * start_pos when given. */
+int kd_rope_table(const kd_tensor* inv_freq, const kd_tensor* pos, int start_pos, int seq_len,
+                  const kd_tensor* cos_out, const kd_tensor* sin_out);
+/* q/k RMSNorm over head_dim + RoPE + [B,S,H,D] layout + KV-cache write in one pass
+ * (packages/model-utils/src/attention/gqa.ts:274-322, rope.ts:546-644, kv-cache.ts:180-188).
+ * qkv: bf16 [B,S,(Hq+2Hkv)*D] (q heads, then k heads, then v heads) or fp32 split-K partials
+ * [splits,B*S,(Hq+2Hkv)*D].  Writes q_out bf16 [B,S,Hq,D] and rows [pos, pos+S) of the caches
+ * [B,Hkv,maxS,D].  A write position outside the cache sets the device error flag. */
+int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_norm_weight,
+                                const kd_tensor* k_norm_weight, float eps, const kd_tensor* cos,
+                                const kd_tensor* sin, const kd_tensor* k_cache, const kd_tensor* v_cache,
+                                const kd_tensor* pos, int start_pos, const kd_tensor* q_out);
+/* silu(gate) * up (packages/model-utils/src/mlp/swiglu.ts:121-131) from a bf16 [rows,2I] matrix or
+ * fp32 partials [splits,rows,2I] whose columns interleave 16 gate / 16 up values. */
+int kd_swiglu(const kd_tensor* gate_up, const kd_tensor* out);
+/* (residual + x) -> bf16 sum_out, then RMSNorm(sum) * weight -> norm_out
+ * (packages/model-utils/src/qwen3/decoder_layer.ts:224-232).  x: bf16 [rows,n] or fp32 partials
+ * [splits,rows,n] (a plain fp32 matrix is the splits = 1 case); residual and sum_out may be NULL
+ * (plain RMSNorm) and are bf16 or fp32 (an fp32 residual stream is summed without rounding). */
+int kd_add_rmsnorm(const kd_tensor* x, const kd_tensor* residual, const kd_tensor* weight, float eps,
+                   const kd_tensor* sum_out, const kd_tensor* norm_out);
+int kd_increment_i32(const kd_tensor* scalar, int delta);
+
+/* CUDA-graph capture of everything enqueued between begin and end (no counterpart in the
+ * reference, whose per-op host overhead is what this removes). */
+int kd_graph_begin(void);
+int kd_graph_end(uint64_t* graph_out);
+int kd_graph_launch(uint64_t graph);
+int kd_graph_destroy(uint64_t graph);
 
 /* Decode attention: one new query position per sequence against a KV cache.  Computes what the
  * reference computes with `_repeatKv` (materialised GQA expansion) + `flash_attention` with

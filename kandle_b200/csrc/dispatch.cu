@@ -49,8 +49,8 @@ KD_API int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_
   KD_TRY(tensor_ptr(weight, &pw));
   KD_TRY(tensor_ptr(out, &po));
   if (epilogue == KD_EPI_RESIDUAL) {
-    KD_REQUIRE(residual && residual->dtype == KD_BF16 && is_contiguous(residual) && numel(residual) == M * N,
-               "residual must be a contiguous bf16 tensor of the output's shape");
+    KD_REQUIRE(residual && residual->dtype == out->dtype && is_contiguous(residual) && numel(residual) == M * N,
+               "residual must be contiguous, of the output's shape and dtype");
     KD_TRY(tensor_ptr(residual, &pr));
   }
   return gemm_bf16(px, K, pw, weight->strides[0], po, n_out, out->dtype == KD_F32, pr, N, (int)M, (int)N, (int)K, epilogue);

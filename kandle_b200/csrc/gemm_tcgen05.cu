@@ -14,7 +14,7 @@
 //               fused epilogue, convert and store.  Two TMEM accumulators let the epilogue of tile
 //               i overlap the mainloop of tile i+1.
 // Fused epilogues: residual add (o_proj / down_proj) and SiLU(gate)*up for a weight whose rows
-// interleave 128 gate rows with 128 up rows per 256-row block.
+// interleave 16 gate rows with the 16 matching up rows per 32-row block.
 //
 // Roofline: tensor-core bound; 2*M*N*K flops per call.
 #include "common.cuh"
@@ -85,7 +85,7 @@ struct GemmParams {
   void* out;
   int64_t ldo;
   int out_f32;            // 0: bf16 output, 1: fp32 output
-  const __nv_bfloat16* resid;
+  const void* resid;      // bf16 when the output is bf16, fp32 when the output is fp32
   int64_t ldr;
   int epi;
   int num_m_tiles, num_n_tiles;
@@ -208,31 +208,25 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N);
       if (p.epi == 2) {
-        // SiLU(gate) * up: columns [0,BLOCK_N/2) are gate, [BLOCK_N/2,BLOCK_N) the matching up columns
-        constexpr int HALF = BLOCK_N / 2;
-        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + (int64_t)n_tile * HALF;
+        // SiLU(gate) * up.  Weight rows interleave 16 gate rows with the 16 matching up rows, so each
+        // 32-column chunk of the accumulator holds 16 (gate, up) pairs and yields 16 outputs.
+        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + (int64_t)n_tile * (BLOCK_N / 2);
 #pragma unroll 1
-        for (int c0 = 0; c0 < HALF; c0 += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(t_row + c0, g);
-          tmem_ld_32x32(t_row + HALF + c0, u);
+        for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c0, r);
           tmem_wait_ld();
-          if (row_ok) {
+          const int col = n_tile * (BLOCK_N / 2) + c0 / 2;
+          if (row_ok && col + 16 <= p.N / 2) {
+            uint32_t o[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int col = n_tile * HALF + c0 + j * 8;
-              if (col + 8 <= p.N / 2) {
-                uint4 v;
-                uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float a0 = silu_f(__uint_as_float(g[j * 8 + 2 * e])) * __uint_as_float(u[j * 8 + 2 * e]);
-                  const float a1 = silu_f(__uint_as_float(g[j * 8 + 2 * e + 1])) * __uint_as_float(u[j * 8 + 2 * e + 1]);
-                  vv[e] = pack_bf16(a0, a1);
-                }
-                *reinterpret_cast<uint4*>(orow + c0 + j * 8) = v;
-              }
+            for (int e = 0; e < 8; ++e) {
+              const float a0 = silu_f(__uint_as_float(r[2 * e])) * __uint_as_float(r[16 + 2 * e]);
+              const float a1 = silu_f(__uint_as_float(r[2 * e + 1])) * __uint_as_float(r[16 + 2 * e + 1]);
+              o[e] = pack_bf16(a0, a1);
             }
+            *reinterpret_cast<uint4*>(orow + c0 / 2) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(orow + c0 / 2 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
           }
         }
       } else {
@@ -244,16 +238,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           if (row_ok) {
             const int col0 = n_tile * BLOCK_N + c0;
             if (p.epi == 1) {
-              const __nv_bfloat16* rrow = p.resid + (int64_t)row * p.ldr + col0;
+              if (p.out_f32) {
+                const float* rrow = static_cast<const float*>(p.resid) + (int64_t)row * p.ldr + col0;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (col0 + j * 8 + 8 <= p.N) {
-                  const uint4 rv = *reinterpret_cast<const uint4*>(rrow + j * 8);
-                  const uint32_t* rr = reinterpret_cast<const uint32_t*>(&rv);
+                for (int j = 0; j < 8; ++j) {
+                  if (col0 + j * 4 + 4 <= p.N) {
+                    const float4 rv = *reinterpret_cast<const float4*>(rrow + j * 4);
+                    r[j * 4 + 0] = __float_as_uint(__uint_as_float(r[j * 4 + 0]) + rv.x);
+                    r[j * 4 + 1] = __float_as_uint(__uint_as_float(r[j * 4 + 1]) + rv.y);
+                    r[j * 4 + 2] = __float_as_uint(__uint_as_float(r[j * 4 + 2]) + rv.z);
+                    r[j * 4 + 3] = __float_as_uint(__uint_as_float(r[j * 4 + 3]) + rv.w);
+                  }
+                }
+              } else {
+                const __nv_bfloat16* rrow = static_cast<const __nv_bfloat16*>(p.resid) + (int64_t)row * p.ldr + col0;
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    r[j * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e]) + bf16_lo(rr[e]));
-                    r[j * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e + 1]) + bf16_hi(rr[e]));
+                for (int j = 0; j < 4; ++j) {
+                  if (col0 + j * 8 + 8 <= p.N) {
+                    const uint4 rv = *reinterpret_cast<const uint4*>(rrow + j * 8);
+                    const uint32_t* rr = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      r[j * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e]) + bf16_lo(rr[e]));
+                      r[j * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e + 1]) + bf16_hi(rr[e]));
+                    }
                   }
                 }
               }
@@ -329,13 +337,13 @@ int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out,
   KD_REQUIRE(n_out % 8 == 0 && ldo % (out_f32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
              "gemm: output width / leading dimension / address not 16-byte aligned");
   if (epi == 1)
-    KD_REQUIRE(resid != nullptr && ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0,
+    KD_REQUIRE(resid != nullptr && ldr % (out_f32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0,
                "gemm: residual operand must be 16-byte aligned");
-  if (epi == 2) KD_REQUIRE(N % 256 == 0 && !out_f32, "gemm: SwiGLU epilogue needs N %% 256 == 0 and a bf16 output");
+  if (epi == 2) KD_REQUIRE(N % 32 == 0 && !out_f32, "gemm: SwiGLU epilogue needs N %% 32 == 0 and a bf16 output");
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
-  p.resid = static_cast<const __nv_bfloat16*>(resid); p.ldr = ldr;
+  p.resid = resid; p.ldr = ldr;
   p.epi = epi;
   p.err = ctx().error_flag;
   CUtensorMap ta, tb;
@@ -350,6 +358,195 @@ int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out,
   }
   KD_TRY(make_tmap_bf16_2d(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 64, GEMM_BK));
   return launch_gemm<64, 8>(ta, tb, p);
+}
+
+// ----------------------------------------------------------------------------- skinny (decode) GEMM
+// y[m, n] = sum_k x[m, k] W[n, k] for a handful of rows m (one per sequence being decoded).  The
+// reference runs this through its "skinny" tile of the generic shader
+// (packages/backend-webgpu/src/kernels/matrix/tileSelector.ts:57-66,169-203); there is no GEMV path.
+//
+// The problem is HBM-bound (every weight byte is used once per step), so the kernel is organised
+// around streaming W: the operands are swapped, W rows become the M dimension of the MMA (128 rows
+// per CTA, all of them useful) and the few activation rows become the N dimension (16..128).  Each
+// stage then carries 16 KB of weights and only a few KB of activations, and a deep TMA ring keeps
+// ~100+ KB of weight traffic in flight per SM.  When N/128 gives too few CTAs the K range is split
+// across CTAs; every split writes fp32 partial sums [split][m][n], which the consumer kernels
+// (norm+RoPE, SwiGLU, residual+RMSNorm) add up while they do their own work.
+// Roofline: HBM, N*K*2 bytes of weights per call.
+struct SkinnyParams {
+  int Mb, N, K;
+  int mb_pad;             // MMA N extent: multiple of 16 covering Mb
+  int x_box;              // rows of the activation TMA box (smem rows per stage)
+  int splits, kblocks_per_split, stages;
+  uint32_t tmem_cols;
+  float* out_f32;         // [splits][Mb][N]
+  __nv_bfloat16* out_bf16;  // [Mb][N], only with splits == 1
+  int* err;
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                           SkinnyParams p) {
+  constexpr int W_BYTES = 128 * GEMM_BK * 2;
+  const int x_bytes = p.x_box * GEMM_BK * 2;
+  const int stage_bytes = W_BYTES + x_bytes;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_full = empty + p.stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, split = blockIdx.y;
+  const int total_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int kb_begin = split * p.kblocks_per_split;
+  const int kb_end = min(total_kb, kb_begin + p.kblocks_per_split);
+  const int n_kb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_w);
+    prefetch_tmap(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < n_kb; ++i) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.err, 211)) break;
+        uint8_t* sw = smem + stage * stage_bytes;
+        mbar_arrive_expect_tx(&full[stage], (uint32_t)stage_bytes);
+        tma_load_2d(sw, &tmap_w, &full[stage], (kb_begin + i) * GEMM_BK, n_tile * 128);
+        tma_load_2d(sw + W_BYTES, &tmap_x, &full[stage], (kb_begin + i) * GEMM_BK, 0);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(128, p.mb_pad, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < n_kb; ++i) {
+        if (!mbar_wait(&full[stage], phase, abort_flag, p.err, 212)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t w_addr = smem_u32(smem + stage * stage_bytes);
+        const uint32_t x_addr = w_addr + W_BYTES;
+#pragma unroll
+        for (int k = 0; k < GEMM_BK / 16; ++k)
+          umma_ss(tmem_base, make_smem_desc_sw128(w_addr + k * 32, 16, 1024), make_smem_desc_sw128(x_addr + k * 32, 16, 1024),
+                  idesc, (i | k) != 0 ? 1u : 0u);
+        umma_commit(&empty[stage]);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    const int q = warp & 3;
+    bool ok = true;
+    if (n_kb > 0) {
+      ok = mbar_wait(acc_full, 0, abort_flag, p.err, 213);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int n = n_tile * 128 + q * 32 + lane;
+      const bool n_ok = n < p.N;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+      for (int c0 = 0; c0 < p.mb_pad; c0 += 16) {
+        uint32_t r[16];
+        if (n_kb > 0) {
+          tmem_ld_32x16(t_row + c0, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = 0u;
+        }
+        if (n_ok) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c0 + i;
+            if (m < p.Mb) {
+              if (p.out_bf16) p.out_bf16[(int64_t)m * p.N + n] = __float2bfloat16_rn(__uint_as_float(r[i]));
+              else p.out_f32[((int64_t)split * p.Mb + m) * p.N + n] = __uint_as_float(r[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+}
+
+// Picks the split-K factor for a skinny GEMM: enough CTAs to cover the SMs about twice, at least
+// two k-blocks per split.
+int gemm_skinny_auto_splits(int N, int K) {
+  const int tiles = (N + 127) / 128;
+  const int total_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  int splits = (2 * ctx().sm_count + tiles - 1) / tiles;
+  if (splits > total_kb / 2) splits = total_kb / 2;
+  if (splits < 1) splits = 1;
+  if (splits > 32) splits = 32;
+  return splits;
+}
+
+// x [Mb<=128, K] bf16, W [N, K] bf16 -> fp32 partials [splits][Mb][N] (or bf16 [Mb][N] when
+// out_bf16 != NULL and splits == 1).
+int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int Mb, int N, int K, int splits,
+                     float* out_f32, void* out_bf16) {
+  KD_REQUIRE(Mb >= 1 && Mb <= 128, "skinny gemm: %d rows; this path handles 1..128", Mb);
+  KD_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "skinny gemm: K=%d must be a positive multiple of 8", K);
+  KD_REQUIRE(splits >= 1, "skinny gemm: splits must be >= 1");
+  KD_REQUIRE(out_bf16 == nullptr || splits == 1, "skinny gemm: bf16 output needs splits == 1");
+  SkinnyParams p{};
+  p.Mb = Mb; p.N = N; p.K = K;
+  p.mb_pad = (Mb + 15) / 16 * 16;
+  p.x_box = p.mb_pad <= 32 ? 32 : (p.mb_pad <= 64 ? 64 : 128);
+  const int total_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  if (splits > total_kb) splits = total_kb;
+  p.kblocks_per_split = (total_kb + splits - 1) / splits;
+  p.splits = splits;
+  const int stage_bytes = 128 * GEMM_BK * 2 + p.x_box * GEMM_BK * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 10) stages = 10;
+  if (stages > p.kblocks_per_split) stages = p.kblocks_per_split < 2 ? 2 : p.kblocks_per_split;
+  p.stages = stages;
+  p.tmem_cols = p.mb_pad <= 32 ? 32 : (p.mb_pad <= 64 ? 64 : 128);
+  p.out_f32 = out_f32;
+  p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16);
+  p.err = ctx().error_flag;
+  CUtensorMap tw, tx;
+  KD_TRY(make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, GEMM_BK));
+  KD_TRY(make_tmap_bf16_2d(&tx, x, (uint64_t)Mb, (uint64_t)K, (uint64_t)ldx, (uint32_t)p.x_box, GEMM_BK));
+  const int smem = stages * stage_bytes + 1024 + 256;
+  static int configured = 0;
+  if (configured < smem) {
+    KD_CUDA_CHECK(cudaFuncSetAttribute(gemm_skinny_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+    configured = 210 * 1024;
+  }
+  dim3 grid((N + 127) / 128, splits);
+  gemm_skinny_tcgen05_kernel<<<grid, GEMM_THREADS, smem, ctx().stream>>>(tw, tx, p);
+  return after_launch("gemm_skinny_tcgen05_kernel");
 }
 
 // ----------------------------------------------------------------------------- dispatch from kd_matmul
@@ -384,7 +581,7 @@ int matmul_tc_try(const kd_matmul_cfg* cfg, const kd_tensor* a, const kd_tensor*
   int epi = 0;
   void* pc = nullptr;
   if (cfg->has_c && c != nullptr && cfg->beta != 0.f) {
-    if (cfg->beta != 1.0f || c->dtype != KD_BF16 || !is_contiguous(c) || numel(c) != M * N) return KD_OK;
+    if (cfg->beta != 1.0f || c->dtype != out->dtype || !is_contiguous(c) || numel(c) != M * N) return KD_OK;
     KD_TRY(tensor_ptr(c, &pc));
     epi = 1;
   }

@@ -1,0 +1,296 @@
+"""Fused bf16 fast path for Qwen3-architecture decoders: tensor-core GEMMs with fused epilogues,
+tcgen05 flash attention, split-KV decode attention and a CUDA-graph decode step.
+
+It computes what `Qwen3ForCausalLM.forwardWithKVCache` + greedy argmax compute on the eager path
+(packages/model-utils/src/qwen3/for_causal_lm.ts:170-194,475-508), with the ~41 backend calls per
+layer collapsed into 8 (prefill) / 10 (decode) kernels and no intermediate copies:
+
+  prefill, per layer     rms_norm -> QKV GEMM -> q/k-norm+RoPE+cache write -> flash attention ->
+                         o_proj GEMM (+residual) -> rms_norm -> gate/up GEMM (SiLU*up epilogue) ->
+                         down GEMM (+residual)
+  decode step, per layer skinny QKV GEMM (split-K partials) -> norm+RoPE+cache write (sums the
+                         partials) -> split-KV attention + combine -> skinny o_proj -> residual+rms_norm
+                         -> skinny gate/up -> SiLU*up -> skinny down -> residual+rms_norm
+  The decode step reads the write position / context length from device memory, so one captured
+  graph is replayed for every step.
+
+Numerics: weights and GEMM / attention operands are bf16, every accumulation is fp32, and the
+residual stream and the logits are kept in fp32 (bf16 rounding of the residual at every layer is
+the largest avoidable error source; it costs 2 extra bytes per hidden element per layer).
+
+All activations live in buffers allocated once per (batch, sequence) shape; 180 GB of HBM makes a
+static workspace the simple choice.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import numpy as np
+
+from . import core, lib
+from .core import Tensor
+from .model_utils.qwen3 import Qwen3Config
+
+
+def _r(t):
+    return ctypes.byref(t._handle.c()) if t is not None else None
+
+
+def interleave_gate_up(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """[I,K] gate and up weights -> [2I,K] with 16 gate rows followed by the 16 matching up rows,
+    the row order the SiLU*up GEMM epilogue and kd_swiglu expect."""
+    I, K = gate.shape
+    assert I % 16 == 0 and up.shape == gate.shape
+    return np.stack([gate.reshape(I // 16, 16, K), up.reshape(I // 16, 16, K)], axis=1).reshape(2 * I, K)
+
+
+class Qwen3Engine:
+    def __init__(self, cfg: Qwen3Config, weights: dict, max_batch: int, max_seq_len: int):
+        """weights: HuggingFace-style names -> float32 arrays (rounded to bf16 on upload)."""
+        self.cfg = cfg
+        self.B, self.max_seq_len = max_batch, max_seq_len
+        c = cfg
+        self.H, self.D, self.Hq, self.Hkv, self.I, self.V, self.L = (c.hiddenSize, c.headDim, c.numAttentionHeads,
+                                                                     c.numKeyValueHeads, c.intermediateSize, c.vocabSize,
+                                                                     c.numHiddenLayers)
+        if self.D not in (64, 128):
+            raise ValueError("the fused engine supports head_dim 64 or 128")
+        self.nqkv = (self.Hq + 2 * self.Hkv) * self.D
+        bf = lambda a: Tensor(np.ascontiguousarray(a, dtype=np.float32), dtype="bfloat16")  # noqa: E731
+        self.embed = bf(weights["model.embed_tokens.weight"])
+        self.final_norm = bf(weights["model.norm.weight"])
+        self.layers = []
+        for i in range(self.L):
+            p = f"model.layers.{i}."
+            self.layers.append({
+                "in_norm": bf(weights[p + "input_layernorm.weight"]),
+                "post_norm": bf(weights[p + "post_attention_layernorm.weight"]),
+                "wqkv": bf(np.concatenate([weights[p + "self_attn.q_proj.weight"], weights[p + "self_attn.k_proj.weight"],
+                                           weights[p + "self_attn.v_proj.weight"]], axis=0)),
+                "q_norm": bf(weights[p + "self_attn.q_norm.weight"]),
+                "k_norm": bf(weights[p + "self_attn.k_norm.weight"]),
+                "wo": bf(weights[p + "self_attn.o_proj.weight"]),
+                "wgu": bf(interleave_gate_up(weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"])),
+                "wdown": bf(weights[p + "mlp.down_proj.weight"]),
+            })
+        half = self.D // 2
+        inv = np.array([1.0 / math.pow(c.ropeTheta, i / half) for i in range(half)], dtype=np.float32)  # rope.ts:159-171
+        self.inv_freq = Tensor(inv, dtype="float32")
+        # KV cache [B,Hkv,maxS,D] per layer, zero-initialised (kv-cache.ts:123-130)
+        self.k_cache = [core.zeros((self.B, self.Hkv, max_seq_len, self.D), "bfloat16") for _ in range(self.L)]
+        self.v_cache = [core.zeros((self.B, self.Hkv, max_seq_len, self.D), "bfloat16") for _ in range(self.L)]
+        self.scale = 1.0 / math.sqrt(self.D)
+        self._prefill_bufs = {}
+        self._decode = None
+        self.pos = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _linear(self, x, w, out, resid=None, epi=0):
+        lib.call("kd_linear_bf16", _r(x), _r(w), _r(resid), epi, _r(out))
+
+    def _norm(self, x, w, out, resid=None, sum_out=None):
+        lib.call("kd_add_rmsnorm", _r(x), _r(resid), _r(w), ctypes.c_float(self.cfg.rmsNormEps), _r(sum_out), _r(out))
+
+    def kv_bytes_per_token(self) -> int:
+        return 2 * self.L * self.Hkv * self.D * 2
+
+    # ------------------------------------------------------------------ prefill
+    def _bufs(self, B: int, S: int) -> dict:
+        key = (B, S)
+        if key not in self._prefill_bufs:
+            T = B * S
+            e = lambda *shape: core.empty(shape, "bfloat16")  # noqa: E731
+            self._prefill_bufs = {key: {
+                "ids": core.empty((T,), "int32"), "emb": e(T, self.H), "h": core.empty((T, self.H), "float32"),
+                "h1": core.empty((T, self.H), "float32"), "x": e(T, self.H),
+                "qkv": e(T, self.nqkv), "q": e(B, S, self.Hq, self.D), "attn": e(B, S, self.Hq, self.D),
+                "act": e(T, self.I), "cos": core.empty((S, self.D // 2), "float32"),
+                "sin": core.empty((S, self.D // 2), "float32"), "last": core.empty((B, self.H), "float32"), "xl": e(B, self.H),
+                "logits": core.empty((1, B, self.V), "float32"), "tok": core.empty((B,), "int64"),
+            }}
+        return self._prefill_bufs[key]
+
+    def prefill(self, ids, all_logits: bool = False):
+        """ids: host int32 array [B,S] (uploaded here) or an int32 device Tensor [B,S].  Fills the KV
+        cache for positions [0,S) and returns the greedy next token per sequence as a device int64
+        Tensor [B] (plus fp32 logits for every position when all_logits is set, which is what the
+        unmodified model code computes)."""
+        if isinstance(ids, Tensor):
+            B, S = ids.shape
+            ids_t = ids.view(B * S)
+        else:
+            ids = np.ascontiguousarray(ids, dtype=np.int32)
+            B, S = ids.shape
+            ids_t = None
+        if B > self.B or S > self.max_seq_len:
+            raise ValueError(f"prefill of {B}x{S} exceeds the engine's {self.B}x{self.max_seq_len}")
+        w = self._bufs(B, S)
+        if ids_t is None:
+            core._backend().upload(w["ids"]._handle, ids.reshape(-1))
+            ids_t = w["ids"]
+        c = self.cfg
+        T = B * S
+        core._kernel("index_select")(self.embed._handle, ids_t._handle, {"dim": 0}, w["emb"]._handle)
+        core.copy_(w["h"], w["emb"])                       # bf16 embedding rows -> fp32 residual stream
+        lib.call("kd_rope_table", _r(self.inv_freq), None, 0, S, _r(w["cos"]), _r(w["sin"]))
+        q_bhsd = w["q"].permute([0, 2, 1, 3])
+        o_bhsd = w["attn"].permute([0, 2, 1, 3])
+        attn2d = w["attn"].view(T, self.Hq * self.D)
+        h, h1 = w["h"], w["h1"]
+        for li, lw in enumerate(self.layers):
+            kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
+            vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
+            self._norm(h, lw["in_norm"], w["x"])
+            self._linear(w["x"], lw["wqkv"], w["qkv"])
+            lib.call("kd_qkv_norm_rope_cachewrite", _r(w["qkv"]), _r(lw["q_norm"]), _r(lw["k_norm"]),
+                     ctypes.c_float(c.rmsNormEps), _r(w["cos"]), _r(w["sin"]), _r(kc), _r(vc), None, 0, _r(w["q"]))
+            kp, vp = kc.slice(f":, :, :{S}, :"), vc.slice(f":, :, :{S}, :")
+            lib.call("kd_flash_attention", _r(q_bhsd), _r(kp), _r(vp), _r(o_bhsd), ctypes.c_float(self.scale), 1)
+            self._linear(attn2d, lw["wo"], h1, resid=h, epi=1)
+            self._norm(h1, lw["post_norm"], w["x"])
+            self._linear(w["x"], lw["wgu"], w["act"], epi=2)
+            self._linear(w["act"], lw["wdown"], h, resid=h1, epi=1)
+            for t in (kc, vc, kp, vp):
+                t.dispose()
+        # tied lm_head on the last position of every sequence (select commutes with the row-wise matmul)
+        h3 = h.view(B, S, self.H)
+        last = h3.select(1, S - 1)
+        core.copy_(w["last"], last)
+        self._norm(w["last"], self.final_norm, w["xl"])
+        lib.call("kd_linear_bf16_skinny", _r(w["xl"]), _r(self.embed), 1, _r(w["logits"]))
+        lg = w["logits"].view(B, self.V)
+        lib.call("kd_argmax", _r(lg), _r(w["tok"]))
+        lg.dispose()
+        full = None
+        if all_logits:
+            xa = core.empty((T, self.H), "bfloat16")
+            self._norm(h, self.final_norm, xa)
+            full = core.empty((B, S, self.V), "float32")
+            self._linear(xa, self.embed, full)
+            xa.dispose()
+        for t in (q_bhsd, o_bhsd, attn2d, h3, last):
+            t.dispose()
+        self.pos = S
+        self.cur_B = B
+        return (w["tok"], full) if all_logits else w["tok"]
+
+    # ------------------------------------------------------------------ decode
+    def _decode_state(self, B: int) -> dict:
+        if self._decode is not None and self._decode["B"] == B:
+            return self._decode
+        def splits(n, k):
+            s = ctypes.c_int(0)
+            lib.call("kd_linear_bf16_skinny_splits", ctypes.c_int64(n), ctypes.c_int64(k), ctypes.byref(s))
+            return s.value
+        e = lambda *shape: core.empty(shape, "bfloat16")  # noqa: E731
+        f = lambda *shape: core.empty(shape, "float32")  # noqa: E731
+        d = {
+            "B": B, "graph": None,
+            "scalars": core.zeros((2,), "int32"),           # [write position, context length]
+            "ids": core.zeros((B,), "int64"), "emb": e(B, self.H), "h": f(B, self.H), "h1": f(B, self.H), "x": e(B, self.H),
+            "qkv_p": f(splits(self.nqkv, self.H), B, self.nqkv), "q": e(B, 1, self.Hq, self.D),
+            "attn": e(B, 1, self.Hq, self.D), "o_p": f(splits(self.H, self.Hq * self.D), B, self.H),
+            "gu_p": f(splits(2 * self.I, self.H), B, 2 * self.I), "act": e(B, self.I),
+            "down_p": f(splits(self.H, self.I), B, self.H), "logits": f(1, B, self.V),
+            "cos": f(1, self.D // 2), "sin": f(1, self.D // 2),
+        }
+        d["pos"] = d["scalars"].slice([slice(0, 1)])
+        d["ctx"] = d["scalars"].slice([slice(1, 2)])
+        self._decode = d
+        return d
+
+    def _enqueue_decode_step(self, d: dict) -> None:
+        """One decode step for d['ids'] at device position d['pos']; leaves the next ids in d['ids']."""
+        c, B = self.cfg, d["B"]
+        eps = ctypes.c_float(c.rmsNormEps)
+        core._kernel("index_select")(self.embed._handle, d["ids"]._handle, {"dim": 0}, d["emb"]._handle)
+        core.copy_(d["h"], d["emb"])
+        lib.call("kd_rope_table", _r(self.inv_freq), _r(d["pos"]), 0, 1, _r(d["cos"]), _r(d["sin"]))
+        q_bh1d = d["q"].permute([0, 2, 1, 3])
+        o_bh1d = d["attn"].permute([0, 2, 1, 3])
+        attn2d = d["attn"].view(B, self.Hq * self.D)
+        h, h1 = d["h"], d["h1"]
+        self._norm(h, self.layers[0]["in_norm"], d["x"])
+        for li, lw in enumerate(self.layers):
+            kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
+            vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
+            lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wqkv"]), 0, _r(d["qkv_p"]))
+            lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
+                     _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
+            lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
+            lib.call("kd_linear_bf16_skinny", _r(attn2d), _r(lw["wo"]), 0, _r(d["o_p"]))
+            self._norm(d["o_p"], lw["post_norm"], d["x"], resid=h, sum_out=h1)
+            lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wgu"]), 0, _r(d["gu_p"]))
+            lib.call("kd_swiglu", _r(d["gu_p"]), _r(d["act"]))
+            lib.call("kd_linear_bf16_skinny", _r(d["act"]), _r(lw["wdown"]), 0, _r(d["down_p"]))
+            nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
+            self._norm(d["down_p"], nxt, d["x"], resid=h1, sum_out=h)
+            kc.dispose()
+            vc.dispose()
+        lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(self.embed), 1, _r(d["logits"]))
+        lg = d["logits"].view(B, self.V)
+        lib.call("kd_argmax", _r(lg), _r(d["ids"]))
+        lg.dispose()
+        lib.call("kd_increment_i32", _r(d["pos"]), 1)
+        lib.call("kd_increment_i32", _r(d["ctx"]), 1)
+        for t in (q_bh1d, o_bh1d, attn2d):
+            t.dispose()
+
+    def start_decode(self, first_tokens: Tensor, use_graph: bool = True) -> dict:
+        """Prepares the decode state after a prefill: next input ids = first_tokens (device int64 [B]),
+        write position = prompt length.  With use_graph the step is captured once (after one eager
+        warm-up step on a scratch position) and replayed by decode_step()."""
+        B = first_tokens.shape[0]
+        d = self._decode_state(B)
+        if self.pos + 1 > self.max_seq_len:
+            raise ValueError("Cache overflow: no room left for decode steps")
+        be = core._backend()
+        if use_graph and d["graph"] is None:
+            # warm-up at the current position: sizes the library's scratch and the allocator's caches
+            # (nothing may allocate while capturing); the cache row it writes is overwritten by the
+            # first real step, which runs at the same position.
+            core.copy_(d["ids"], first_tokens)
+            be.upload(d["scalars"]._handle, np.array([self.pos, self.pos + 1], np.int32))
+            self._enqueue_decode_step(d)
+            lib.call("kd_graph_begin")
+            try:
+                self._enqueue_decode_step(d)
+            finally:
+                g = ctypes.c_uint64(0)
+                lib.call("kd_graph_end", ctypes.byref(g))
+            d["graph"] = g.value
+        core.copy_(d["ids"], first_tokens)
+        be.upload(d["scalars"]._handle, np.array([self.pos, self.pos + 1], np.int32))
+        d["use_graph"] = use_graph
+        return d
+
+    def decode_step(self) -> Tensor:
+        """Runs one step; returns the device int64 [B] tensor holding the tokens just produced."""
+        d = self._decode
+        if self.pos + 1 > self.max_seq_len:
+            raise ValueError(f"Cache overflow: position {self.pos} but maxSeqLen is {self.max_seq_len}")
+        if d["use_graph"]:
+            lib.call("kd_graph_launch", ctypes.c_uint64(d["graph"]))
+        else:
+            self._enqueue_decode_step(d)
+        self.pos += 1
+        return d["ids"]
+
+    def generate(self, ids, steps: int, use_graph: bool = True) -> np.ndarray:
+        """Greedy generation: prefill + `steps` tokens (the first comes from the prefill).  Returns
+        int64 [B, steps] on the host; every step's ids are read back, as the reference does."""
+        tok = self.prefill(ids)
+        B = tok.shape[0]
+        out = np.empty((B, steps), dtype=np.int64)
+        out[:, 0] = tok.dataAsync()
+        if steps > 1:
+            self.start_decode(tok, use_graph)
+            for t in range(1, steps):
+                out[:, t] = self.decode_step().dataAsync()
+        return out
+
+    def dispose(self) -> None:
+        if self._decode is not None and self._decode.get("graph"):
+            lib.call("kd_graph_destroy", ctypes.c_uint64(self._decode["graph"]))
+        self._decode = None

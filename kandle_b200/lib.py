@@ -130,6 +130,17 @@ _SIGNATURES = {
     "kd_event_elapsed_ms": [_u64, _u64, ctypes.POINTER(ctypes.c_float)],
     "kd_event_destroy": [_u64],
     "kd_linear_bf16": [_T, _T, _T, ctypes.c_int, _T],
+    "kd_linear_bf16_skinny": [_T, _T, ctypes.c_int, _T],
+    "kd_linear_bf16_skinny_splits": [ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)],
+    "kd_rope_table": [_T, _T, ctypes.c_int, ctypes.c_int, _T, _T],
+    "kd_qkv_norm_rope_cachewrite": [_T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, ctypes.c_int, _T],
+    "kd_swiglu": [_T, _T],
+    "kd_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
+    "kd_increment_i32": [_T, ctypes.c_int],
+    "kd_graph_begin": [],
+    "kd_graph_end": [ctypes.POINTER(_u64)],
+    "kd_graph_launch": [_u64],
+    "kd_graph_destroy": [_u64],
     "kd_attention_decode": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_paged": [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
 }

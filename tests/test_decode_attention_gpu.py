@@ -86,5 +86,5 @@ def test_decode_attention_rejects_bad_arguments(backend):
     with pytest.raises(lib.KandleCudaError):      # context longer than the cache
         lib.call("kd_attention_decode", _ref(q), _ref(kc), _ref(kc), None, 65, ctypes.c_float(0.1), 0, _ref(out))
     with pytest.raises(lib.KandleCudaError):      # fp32 query
-        lib.call("kd_attention_decode", _ref(Tensor(synth.normal("q", (1, 4, 1, 128)))), _ref(kc), _ref(kc), None, 8,
-                 ctypes.c_float(0.1), 0, _ref(out))
+        q32 = Tensor(synth.normal("q", (1, 4, 1, 128)))
+        lib.call("kd_attention_decode", _ref(q32), _ref(kc), _ref(kc), None, 8, ctypes.c_float(0.1), 0, _ref(out))

@@ -49,11 +49,11 @@ def test_linear_bf16_residual_epilogue(backend, oracle):
 
 
 def test_linear_bf16_swiglu_epilogue(backend, oracle):
-    """Fused gate/up weight: per 256-row block, 128 gate rows then the 128 matching up rows."""
+    """Fused gate/up weight: per 32-row block, 16 gate rows then the 16 matching up rows."""
     K, I = 1024, 768
     x = lib.round_to_bf16(synth.normal("x", (150, K)))
     wg, wu = lib.round_to_bf16(synth.normal("wg", (I, K), 0.03)), lib.round_to_bf16(synth.normal("wu", (I, K), 0.03))
-    fused = np.concatenate([np.concatenate([wg[i:i + 128], wu[i:i + 128]]) for i in range(0, I, 128)])
+    fused = np.concatenate([np.concatenate([wg[i:i + 16], wu[i:i + 16]]) for i in range(0, I, 16)])
     ref = oracle.mul(oracle.unary("silu", oracle.linear(x, wg)), oracle.linear(x, wu))
     bf16_close(_linear_bf16(x, fused, None, 2), ref, 2e-3)
 
