@@ -30,8 +30,6 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int*
 // Replaces, per layer: view -> rms_norm(q), rms_norm(k) over head_dim -> permute+contiguous x3 ->
 // applyRotaryPosEmbDirect (16 pointwise/copy calls) -> StaticKVCache.update (2 copy_ calls)
 // (packages/model-utils/src/attention/gqa.ts:274-322, rope.ts:546-644, kv-cache.ts:180-188).
-// One warp per (token, head); a lane holds D/32 elements arranged so that both members of every
-// rotation pair (i, i + D/2) live in the same lane.
 struct QkvRopeParams {
   int tokens, S, Hq, Hkv;
   int splits;            // 0: bf16 source; >0: fp32 partials [splits][tokens][Ntot]
@@ -41,55 +39,101 @@ struct QkvRopeParams {
   int pos_host;
 };
 
+template <int V>
+struct VecF { float v[V]; };
+
+// Loads V consecutive elements starting at element index `e` of a bf16 row or of the sum of fp32
+// partial rows (rows are `stride` elements apart in the partial case).
+template <int V>
+__device__ __forceinline__ VecF<V> load_src(const void* src, int splits, int64_t row_off, int64_t split_stride, int e) {
+  VecF<V> r;
+  if (splits == 0) {
+    const __nv_bfloat16* s = static_cast<const __nv_bfloat16*>(src) + row_off + e;
+    if (V == 4) {
+      const uint2 u = *reinterpret_cast<const uint2*>(s);
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+      for (int i = 0; i < V; ++i) r.v[i] = __bfloat162float(h[i]);
+    } else {
+      const uint32_t u = *reinterpret_cast<const uint32_t*>(s);
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+      for (int i = 0; i < V; ++i) r.v[i] = __bfloat162float(h[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) r.v[i] = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float* s = static_cast<const float*>(src) + sp * split_stride + row_off + e;
+      if (V == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(s);
+        r.v[0] += f.x; r.v[1] += f.y; r.v[2] += f.z; r.v[3] += f.w;
+      } else {
+        const float2 f = *reinterpret_cast<const float2*>(s);
+        r.v[0] += f.x; r.v[1] += f.y;
+      }
+    }
+  }
+  return r;
+}
+
+template <int V>
+__device__ __forceinline__ void store_bf16(__nv_bfloat16* dst, const float* v) {
+  if (V == 4) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(dst) = u;
+  } else {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<uint32_t*>(&a);
+  }
+}
+
+// Half a warp (16 lanes) per (token, head).  Lane l holds V = D/32 consecutive elements of the
+// first half of the head, [V*l, V*l+V), and the V elements D/2 further on, i.e. both members of
+// each rotation pair (i, i + D/2); every access is one 4- or 8-byte (bf16) / 8- or 16-byte (fp32) vector.
 template <int D>
 __global__ void qkv_norm_rope_kernel(const void* __restrict__ src, const void* __restrict__ qw, int dt_qw,
                                      const void* __restrict__ kw, int dt_kw, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q_out,
                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                      const int* __restrict__ pos_dev, QkvRopeParams p, int* __restrict__ err) {
-  constexpr int EPL = D / 32;       // elements per lane
+  constexpr int V = D / 32;
   constexpr int HALF = D / 2;
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int l16 = threadIdx.x & 15;
+  const int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
   const int heads = p.Hq + 2 * p.Hkv;
-  if (warp >= (int64_t)p.tokens * heads) return;
-  const int token = (int)(warp / heads), head = (int)(warp - (int64_t)token * heads);
+  const bool live = item < (int64_t)p.tokens * heads;
+  const int token = live ? (int)(item / heads) : 0, head = live ? (int)(item - (int64_t)token * heads) : 0;
   const int64_t ntot = (int64_t)heads * D;
-  float x[EPL];
-  if (p.splits == 0) {
-    const __nv_bfloat16* s = static_cast<const __nv_bfloat16*>(src) + (int64_t)token * ntot + (int64_t)head * D;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) x[j] = __bfloat162float(s[lane + 32 * j]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) x[j] = 0.f;
-    for (int sp = 0; sp < p.splits; ++sp) {
-      const float* s = static_cast<const float*>(src) + ((int64_t)sp * p.tokens + token) * ntot + (int64_t)head * D;
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) x[j] += s[lane + 32 * j];
-    }
-  }
+  const int64_t row_off = (int64_t)token * ntot + (int64_t)head * D;
+  const int64_t split_stride = (int64_t)p.tokens * ntot;
+  const int e0 = V * l16;
+  VecF<V> x1 = load_src<V>(src, p.splits, row_off, split_stride, e0);
+  VecF<V> x2 = load_src<V>(src, p.splits, row_off, split_stride, HALF + e0);
   const int b = token / p.S, s_idx = token - b * p.S;
   const bool is_q = head < p.Hq, is_k = !is_q && head < p.Hq + p.Hkv;
-  if (is_q || is_k) {
-    // RMSNorm over head_dim: y = (x * (1/sqrt(mean(x^2)+eps))) * w   (normalize/shaderBuilder.ts:343-415)
-    float ss = 0.f;
+  // RMSNorm over head_dim: y = (x * (1/sqrt(mean(x^2)+eps))) * w   (normalize/shaderBuilder.ts:343-415)
+  float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) ss += x[j] * x[j];
-    ss = warp_sum(ss);
+  for (int i = 0; i < V; ++i) ss += x1.v[i] * x1.v[i] + x2.v[i] * x2.v[i];
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // stays inside the 16-lane half
+  if (!live) return;
+  if (is_q || is_k) {
     const float sc = 1.0f / sqrtf(ss / (float)D + p.eps);
     const void* w = is_q ? qw : kw;
     const int dtw = is_q ? dt_qw : dt_kw;
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) x[j] = (x[j] * sc) * load_float(w, dtw, lane + 32 * j);
-    // rotate: out[i] = y[i] cos - y[i+D/2] sin ; out[i+D/2] = y[i+D/2] cos + y[i] sin
-#pragma unroll
-    for (int j = 0; j < EPL / 2; ++j) {
-      const int e = lane + 32 * j;  // < HALF
-      const float c = cos_t[(int64_t)s_idx * HALF + e], sn = sin_t[(int64_t)s_idx * HALF + e];
-      const float y1 = x[j], y2 = x[j + EPL / 2];
-      x[j] = y1 * c - y2 * sn;
-      x[j + EPL / 2] = y2 * c + y1 * sn;
+    for (int i = 0; i < V; ++i) {
+      const float y1 = (x1.v[i] * sc) * load_float(w, dtw, e0 + i);
+      const float y2 = (x2.v[i] * sc) * load_float(w, dtw, HALF + e0 + i);
+      // rotate: out[i] = y[i] cos - y[i+D/2] sin ; out[i+D/2] = y[i+D/2] cos + y[i] sin
+      const float c = cos_t[(int64_t)s_idx * HALF + e0 + i], sn = sin_t[(int64_t)s_idx * HALF + e0 + i];
+      x1.v[i] = y1 * c - y2 * sn;
+      x2.v[i] = y2 * c + y1 * sn;
     }
   }
   __nv_bfloat16* dst;
@@ -99,14 +143,14 @@ __global__ void qkv_norm_rope_kernel(const void* __restrict__ src, const void* _
     const int pos0 = pos_dev ? *pos_dev : p.pos_host;
     const int pos = pos0 + s_idx;
     if (pos < 0 || pos >= p.max_s) {  // never write outside the cache; report instead
-      if (lane == 0 && atomicCAS(err, 0, 102) == 0) { err[1] = pos; err[2] = p.max_s; }
+      if (l16 == 0 && atomicCAS(err, 0, 102) == 0) { err[1] = pos; err[2] = p.max_s; }
       return;
     }
     const int hk = is_k ? head - p.Hq : head - p.Hq - p.Hkv;
     dst = (is_k ? k_cache : v_cache) + (int64_t)b * p.kc_b + (int64_t)hk * p.kc_h + (int64_t)pos * p.kc_s;
   }
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(x[j]);
+  store_bf16<V>(dst + e0, x1.v);
+  store_bf16<V>(dst + HALF + e0, x2.v);
 }
 
 // ----------------------------------------------------------------------------- SiLU(gate) * up
@@ -225,6 +269,78 @@ __global__ void __launch_bounds__(ARN_THREADS) add_rmsnorm_kernel(const void* __
   }
 }
 
+// Many-row variant (prefill): one warp per row, 8 rows per CTA, no shared memory.  Same arithmetic.
+constexpr int RWN_MAXV = 16;  // vectors of 8 per lane: rows up to 4096 wide
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const void* __restrict__ src, int src_f32,
+                                                            const void* __restrict__ resid, int resid_f32,
+                                                            const void* __restrict__ w, int dt_w, float eps,
+                                                            void* __restrict__ sum_out, int sum_f32, int round_sum,
+                                                            __nv_bfloat16* __restrict__ norm_out, int64_t rows, int n) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const int nvec = n / 8;
+  float v[RWN_MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int t = 0; t < RWN_MAXV; ++t) {
+    const int vi = lane + t * 32;
+    if (vi < nvec) {
+      if (src_f32) {
+        const float4* sp = reinterpret_cast<const float4*>(static_cast<const float*>(src) + row * n) + vi * 2;
+        const float4 a = sp[0], b = sp[1];
+        v[t][0] = a.x; v[t][1] = a.y; v[t][2] = a.z; v[t][3] = a.w; v[t][4] = b.x; v[t][5] = b.y; v[t][6] = b.z; v[t][7] = b.w;
+      } else {
+        const uint4 u = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + row * n)[vi];
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[t][e] = __bfloat162float(h[e]);
+      }
+      if (resid) {
+        if (resid_f32) {
+          const float4* rp = reinterpret_cast<const float4*>(static_cast<const float*>(resid) + row * n) + vi * 2;
+          const float4 a = rp[0], b = rp[1];
+          v[t][0] += a.x; v[t][1] += a.y; v[t][2] += a.z; v[t][3] += a.w; v[t][4] += b.x; v[t][5] += b.y; v[t][6] += b.z; v[t][7] += b.w;
+        } else {
+          const uint4 u = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(resid) + row * n)[vi];
+          const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[t][e] += __bfloat162float(h[e]);
+        }
+      }
+      if (sum_out && sum_f32) {
+        float4* sp = reinterpret_cast<float4*>(static_cast<float*>(sum_out) + row * n) + vi * 2;
+        sp[0] = make_float4(v[t][0], v[t][1], v[t][2], v[t][3]);
+        sp[1] = make_float4(v[t][4], v[t][5], v[t][6], v[t][7]);
+      } else if (round_sum) {
+        uint4 o;
+        __nv_bfloat16* ho = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          ho[e] = __float2bfloat16_rn(v[t][e]);
+          v[t][e] = __bfloat162float(ho[e]);
+        }
+        if (sum_out) reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sum_out) + row * n)[vi] = o;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[t][e] * v[t][e];
+    }
+  }
+  ss = warp_sum(ss);
+  const float sc = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+  for (int t = 0; t < RWN_MAXV; ++t) {
+    const int vi = lane + t * 32;
+    if (vi < nvec) {
+      uint4 o;
+      __nv_bfloat16* ho = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16_rn((v[t][e] * sc) * load_float(w, dt_w, vi * 8 + e));
+      reinterpret_cast<uint4*>(norm_out + row * n)[vi] = o;
+    }
+  }
+}
+
 __global__ void increment_i32_kernel(int* p, int delta) { *p += delta; }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -316,9 +432,14 @@ KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_
   p.kc_b = k_cache->strides[0]; p.kc_h = k_cache->strides[1]; p.kc_s = k_cache->strides[2];
   p.max_s = (int)k_cache->shape[2];
   p.pos_host = start_pos;
-  const int64_t warps = tokens * (Hq + 2 * Hkv);
+  const int64_t items = tokens * (Hq + 2 * Hkv);   // 16 lanes each
   const int threads = 256;
-  const int64_t blocks = (warps * 32 + threads - 1) / threads;
+  const int64_t blocks = (items * 16 + threads - 1) / threads;
+  KD_REQUIRE(k_cache->strides[0] % 4 == 0 && k_cache->strides[1] % 4 == 0 && k_cache->strides[2] % 4 == 0,
+             "cache strides must be multiples of 4 elements");
+  KD_REQUIRE((reinterpret_cast<uintptr_t>(psrc) & 15) == 0 && (reinterpret_cast<uintptr_t>(pkc) & 7) == 0 &&
+                 (reinterpret_cast<uintptr_t>(pvc) & 7) == 0 && (reinterpret_cast<uintptr_t>(pqo) & 7) == 0,
+             "qkv / cache / q_out must be 16- / 8-byte aligned");
   KD_REQUIRE(blocks <= 0x7fffffff, "too many tokens for one launch");
   if (D == 128)
     qkv_norm_rope_kernel<128><<<(unsigned)blocks, threads, 0, ctx().stream>>>(
@@ -386,6 +507,13 @@ KD_API int kd_add_rmsnorm(const kd_tensor* x, const kd_tensor* residual, const k
   if (residual) KD_TRY(tensor_ptr(residual, &pr));
   if (sum_out) KD_TRY(tensor_ptr(sum_out, &ps));
   KD_REQUIRE(aligned16(px) && aligned16(pn) && (!pr || aligned16(pr)) && (!ps || aligned16(ps)), "operands must be 16-byte aligned");
+  if (rows >= 1024 && splits <= 1 && n <= 8 * 32 * RWN_MAXV) {
+    const int round_sum = ((splits != 0 || residual) && !(sum_out == nullptr && sum_f32)) ? 1 : 0;
+    rmsnorm_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx().stream>>>(
+        px, splits == 1, pr, residual ? residual->dtype == KD_F32 : 0, pw, weight->dtype, eps, ps, sum_f32, round_sum,
+        (__nv_bfloat16*)pn, rows, (int)n);
+    return after_launch("rmsnorm_rows_kernel");
+  }
   add_rmsnorm_kernel<<<(unsigned)rows, ARN_THREADS, 0, ctx().stream>>>(px, splits, pr, residual ? residual->dtype == KD_F32 : 0, pw,
                                                                      weight->dtype, eps, ps, sum_f32, (__nv_bfloat16*)pn,
                                                                      (int)rows, (int)n);
