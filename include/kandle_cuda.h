@@ -254,6 +254,23 @@ int kd_graph_destroy(uint64_t graph);
 int kd_attention_decode(const kd_tensor* q, const kd_tensor* k_cache, const kd_tensor* v_cache,
                         const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
                         const kd_tensor* out);
+/* Same computation as kd_attention_decode for callers that are not allowed to allocate device
+ * memory while they run: a serving loop that has handed the whole GPU to its own pool, code running
+ * inside a memory-budgeted plugin host, or a latency path where a cudaMalloc (which can synchronise
+ * the device) is unacceptable.  It has no counterpart in the reference.  The split-KV partials go to
+ * an 8 MiB buffer built into the library image instead of the growing workspace, and the call makes
+ * no cudaMalloc / cudaFree and uses no allocating library routine.  Limits and rules:
+ *   - B * Hkv * splits * (Hq/Hkv) * (D + 2) * 4 bytes must fit in 8 MiB, otherwise the call fails
+ *     with KD_ERR_INVALID and a message that names both sizes (pass a smaller `splits`);
+ *   - the first call on a device looks up the buffer's device address; make that call before any
+ *     stream capture begins;
+ *   - all calls share the one buffer, which keeps whatever the previous call left in it (nothing in
+ *     it needs clearing: every slot a call reads was written by that same call), so two calls that
+ *     overlap on the GPU race with each other; keep them on one stream;
+ *   - every GPU that loads the library holds the 8 MiB until the process exits. */
+int kd_attention_decode_noalloc(const kd_tensor* q, const kd_tensor* k_cache, const kd_tensor* v_cache,
+                                const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
+                                const kd_tensor* out);
 /* Paged variant (no counterpart in the reference, which only has the contiguous static cache):
  * k_pool/v_pool [pages,Hkv,128,D]; block_table [B,max_pages] int32 names the page of each
  * 128-key tile of each sequence. */

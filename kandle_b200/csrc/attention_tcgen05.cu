@@ -589,4 +589,45 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   return after_launch("decode_combine_kernel");
 }
 
+// ----------------------------------------------------------------------------- decode attention without allocation
+// Scratch for the entry point that must not allocate: it lives in the library image, so every
+// GPU that loads the library carries these 8 MiB until the process exits.
+constexpr size_t STATIC_SCRATCH_BYTES = 8u << 20;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[STATIC_SCRATCH_BYTES];
+
+int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
+                            const int* ctx_dev, int ctx_host, int splits) {
+  // In host code the array's name is only a handle for the symbol, not a device address: the
+  // address the kernels may use has to be asked for, once per device, with that device current.
+  static void* scratch_ptr[64] = {nullptr};
+  const int dev = ctx().device;
+  KD_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+  if (scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return fail(KD_ERR_CUDA, "cudaGetSymbolAddress for the static decode scratch failed: %s", cudaGetErrorString(e));
+    }
+    scratch_ptr[dev] = p;
+  }
+  KD_REQUIRE(q && k && q->ndim == 4 && k->ndim == 4, "decode attention operands must be 4-D");
+  const int B = (int)q->shape[0], Hq = (int)q->shape[1], Hkv = (int)k->shape[1], D = (int)q->shape[3];
+  KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "bad head counts");
+  const int max_blocks = (int)((k->shape[2] + FA_BKV - 1) / FA_BKV);
+  if (splits <= 0) {
+    const int pairs = B * Hkv > 0 ? B * Hkv : 1;
+    splits = (4 * ctx().sm_count + pairs - 1) / pairs;
+    if (splits > max_blocks) splits = max_blocks;
+    if (splits < 1) splits = 1;
+  }
+  const size_t need = attention_decode_scratch_bytes(B, Hkv, Hq / Hkv, splits, D);
+  if (need > STATIC_SCRATCH_BYTES)
+    return fail(KD_ERR_INVALID,
+                "kd_attention_decode_noalloc: batch %d x %d kv heads x %d splits needs %zu bytes of scratch, the built-in "
+                "buffer holds %zu; lower `splits` or use kd_attention_decode",
+                B, Hkv, splits, need, STATIC_SCRATCH_BYTES);
+  return attention_decode(q, k, v, out, scale, ctx_dev, ctx_host, nullptr, 0, splits, scratch_ptr[dev], STATIC_SCRATCH_BYTES);
+}
+
 }  // namespace kd

@@ -108,3 +108,18 @@ KD_API int kd_attention_decode_paged(const kd_tensor* q, const kd_tensor* k_pool
   KD_REQUIRE(block_table != nullptr, "kd_attention_decode_paged needs a block table");
   return decode_common(q, k_pool, v_pool, block_table, ctx_len, ctx_len_host, scale, splits, out);
 }
+
+KD_API int kd_attention_decode_noalloc(const kd_tensor* q, const kd_tensor* k_cache, const kd_tensor* v_cache,
+                                       const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
+                                       const kd_tensor* out) {
+  KD_TRY(require_init());
+  KD_REQUIRE(q && k_cache && v_cache && out, "null tensor");
+  const int* ctx_dev = nullptr;
+  if (ctx_len) {
+    KD_REQUIRE(ctx_len->dtype == KD_I32 && numel(ctx_len) == 1, "ctx_len must be a device int32 scalar");
+    void* pc = nullptr;
+    KD_TRY(tensor_ptr(ctx_len, &pc));
+    ctx_dev = static_cast<const int*>(pc);
+  }
+  return attention_decode_static(q, k_cache, v_cache, out, scale, ctx_dev, ctx_len_host, splits);
+}

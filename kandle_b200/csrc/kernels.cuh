@@ -38,4 +38,7 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
                      const int* ctx_dev, int ctx_host, const int* block_table, int max_pages, int splits,
                      void* scratch, size_t scratch_bytes);
 
+int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
+                            const int* ctx_dev, int ctx_host, int splits);
+
 }  // namespace kd

@@ -142,6 +142,7 @@ _SIGNATURES = {
     "kd_graph_launch": [_u64],
     "kd_graph_destroy": [_u64],
     "kd_attention_decode": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
+    "kd_attention_decode_noalloc": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_paged": [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
 }
 
