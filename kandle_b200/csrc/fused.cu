@@ -103,10 +103,12 @@ __global__ void qkv_norm_rope_kernel(const void* __restrict__ src, const void* _
   constexpr int V = D / 32;
   constexpr int HALF = D / 2;
   const int l16 = threadIdx.x & 15;
-  const int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  // grid: x = token, y = group of 16 heads; 16 lanes per (token, head)
   const int heads = p.Hq + 2 * p.Hkv;
-  const bool live = item < (int64_t)p.tokens * heads;
-  const int token = live ? (int)(item / heads) : 0, head = live ? (int)(item - (int64_t)token * heads) : 0;
+  const int token = blockIdx.x;
+  const int head_raw = blockIdx.y * 16 + (threadIdx.x >> 4);
+  const bool live = head_raw < heads;
+  const int head = live ? head_raw : 0;
   const int64_t ntot = (int64_t)heads * D;
   const int64_t row_off = (int64_t)token * ntot + (int64_t)head * D;
   const int64_t split_stride = (int64_t)p.tokens * ntot;
@@ -126,14 +128,17 @@ __global__ void qkv_norm_rope_kernel(const void* __restrict__ src, const void* _
     const float sc = 1.0f / sqrtf(ss / (float)D + p.eps);
     const void* w = is_q ? qw : kw;
     const int dtw = is_q ? dt_qw : dt_kw;
+    const VecF<V> w1 = load_src<V>(w, dtw == KD_BF16 ? 0 : 1, 0, 0, e0);
+    const VecF<V> w2 = load_src<V>(w, dtw == KD_BF16 ? 0 : 1, 0, 0, HALF + e0);
+    const VecF<V> c = load_src<V>(cos_t, 1, (int64_t)s_idx * HALF, 0, e0);
+    const VecF<V> sn = load_src<V>(sin_t, 1, (int64_t)s_idx * HALF, 0, e0);
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-      const float y1 = (x1.v[i] * sc) * load_float(w, dtw, e0 + i);
-      const float y2 = (x2.v[i] * sc) * load_float(w, dtw, HALF + e0 + i);
+      const float y1 = (x1.v[i] * sc) * w1.v[i];
+      const float y2 = (x2.v[i] * sc) * w2.v[i];
       // rotate: out[i] = y[i] cos - y[i+D/2] sin ; out[i+D/2] = y[i+D/2] cos + y[i] sin
-      const float c = cos_t[(int64_t)s_idx * HALF + e0 + i], sn = sin_t[(int64_t)s_idx * HALF + e0 + i];
-      x1.v[i] = y1 * c - y2 * sn;
-      x2.v[i] = y2 * c + y1 * sn;
+      x1.v[i] = y1 * c.v[i] - y2 * sn.v[i];
+      x2.v[i] = y2 * c.v[i] + y1 * sn.v[i];
     }
   }
   __nv_bfloat16* dst;
@@ -271,6 +276,7 @@ __global__ void __launch_bounds__(ARN_THREADS) add_rmsnorm_kernel(const void* __
 
 // Many-row variant (prefill): one warp per row, 8 rows per CTA, no shared memory.  Same arithmetic.
 constexpr int RWN_MAXV = 16;  // vectors of 8 per lane: rows up to 4096 wide
+template <int NV>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const void* __restrict__ src, int src_f32,
                                                             const void* __restrict__ resid, int resid_f32,
                                                             const void* __restrict__ w, int dt_w, float eps,
@@ -280,10 +286,10 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const void* __restric
   const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
   const int nvec = n / 8;
-  float v[RWN_MAXV][8];
+  float v[NV][8];
   float ss = 0.f;
 #pragma unroll
-  for (int t = 0; t < RWN_MAXV; ++t) {
+  for (int t = 0; t < NV; ++t) {
     const int vi = lane + t * 32;
     if (vi < nvec) {
       if (src_f32) {
@@ -329,13 +335,25 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const void* __restric
   ss = warp_sum(ss);
   const float sc = 1.0f / sqrtf(ss / (float)n + eps);
 #pragma unroll
-  for (int t = 0; t < RWN_MAXV; ++t) {
+  for (int t = 0; t < NV; ++t) {
     const int vi = lane + t * 32;
     if (vi < nvec) {
       uint4 o;
       __nv_bfloat16* ho = reinterpret_cast<__nv_bfloat16*>(&o);
+      float wv[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16_rn((v[t][e] * sc) * load_float(w, dt_w, vi * 8 + e));
+      for (int e = 0; e < 8; ++e) wv[e] = 1.f;
+      if (dt_w == KD_BF16) {
+        const uint4 u = reinterpret_cast<const uint4*>(w)[vi];
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wv[e] = __bfloat162float(h[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wv[e] = load_float(w, dt_w, vi * 8 + e);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16_rn((v[t][e] * sc) * wv[e]);
       reinterpret_cast<uint4*>(norm_out + row * n)[vi] = o;
     }
   }
@@ -432,21 +450,26 @@ KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_
   p.kc_b = k_cache->strides[0]; p.kc_h = k_cache->strides[1]; p.kc_s = k_cache->strides[2];
   p.max_s = (int)k_cache->shape[2];
   p.pos_host = start_pos;
-  const int64_t items = tokens * (Hq + 2 * Hkv);   // 16 lanes each
-  const int threads = 256;
-  const int64_t blocks = (items * 16 + threads - 1) / threads;
+  const int threads = 256;                          // 16 heads of one token per CTA
+  const dim3 blocks((unsigned)tokens, (unsigned)((Hq + 2 * Hkv + 15) / 16));
+  KD_REQUIRE((q_norm_weight->dtype == KD_BF16 || q_norm_weight->dtype == KD_F32) &&
+                 (k_norm_weight->dtype == KD_BF16 || k_norm_weight->dtype == KD_F32),
+             "q/k norm weights must be bf16 or fp32");
+  KD_REQUIRE((reinterpret_cast<uintptr_t>(pqw) & 15) == 0 && (reinterpret_cast<uintptr_t>(pkw) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(pcos) & 15) == 0 && (reinterpret_cast<uintptr_t>(psin) & 15) == 0,
+             "norm weights and cos/sin tables must be 16-byte aligned");
   KD_REQUIRE(k_cache->strides[0] % 4 == 0 && k_cache->strides[1] % 4 == 0 && k_cache->strides[2] % 4 == 0,
              "cache strides must be multiples of 4 elements");
   KD_REQUIRE((reinterpret_cast<uintptr_t>(psrc) & 15) == 0 && (reinterpret_cast<uintptr_t>(pkc) & 7) == 0 &&
                  (reinterpret_cast<uintptr_t>(pvc) & 7) == 0 && (reinterpret_cast<uintptr_t>(pqo) & 7) == 0,
              "qkv / cache / q_out must be 16- / 8-byte aligned");
-  KD_REQUIRE(blocks <= 0x7fffffff, "too many tokens for one launch");
+  KD_REQUIRE(tokens <= 0x7fffffff, "too many tokens for one launch");
   if (D == 128)
-    qkv_norm_rope_kernel<128><<<(unsigned)blocks, threads, 0, ctx().stream>>>(
+    qkv_norm_rope_kernel<128><<<blocks, threads, 0, ctx().stream>>>(
         psrc, pqw, q_norm_weight->dtype, pkw, k_norm_weight->dtype, (const float*)pcos, (const float*)psin, (__nv_bfloat16*)pqo,
         (__nv_bfloat16*)pkc, (__nv_bfloat16*)pvc, pos_dev, p, ctx().error_flag);
   else
-    qkv_norm_rope_kernel<64><<<(unsigned)blocks, threads, 0, ctx().stream>>>(
+    qkv_norm_rope_kernel<64><<<blocks, threads, 0, ctx().stream>>>(
         psrc, pqw, q_norm_weight->dtype, pkw, k_norm_weight->dtype, (const float*)pcos, (const float*)psin, (__nv_bfloat16*)pqo,
         (__nv_bfloat16*)pkc, (__nv_bfloat16*)pvc, pos_dev, p, ctx().error_flag);
   return after_launch("qkv_norm_rope_kernel");
@@ -509,9 +532,15 @@ KD_API int kd_add_rmsnorm(const kd_tensor* x, const kd_tensor* residual, const k
   KD_REQUIRE(aligned16(px) && aligned16(pn) && (!pr || aligned16(pr)) && (!ps || aligned16(ps)), "operands must be 16-byte aligned");
   if (rows >= 1024 && splits <= 1 && n <= 8 * 32 * RWN_MAXV) {
     const int round_sum = ((splits != 0 || residual) && !(sum_out == nullptr && sum_f32)) ? 1 : 0;
-    rmsnorm_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx().stream>>>(
-        px, splits == 1, pr, residual ? residual->dtype == KD_F32 : 0, pw, weight->dtype, eps, ps, sum_f32, round_sum,
-        (__nv_bfloat16*)pn, rows, (int)n);
+    KD_REQUIRE((reinterpret_cast<uintptr_t>(pw) & 15) == 0, "weight must be 16-byte aligned");
+    if (n <= 8 * 32 * 4)
+      rmsnorm_rows_kernel<4><<<(unsigned)((rows + 7) / 8), 256, 0, ctx().stream>>>(
+          px, splits == 1, pr, residual ? residual->dtype == KD_F32 : 0, pw, weight->dtype, eps, ps, sum_f32, round_sum,
+          (__nv_bfloat16*)pn, rows, (int)n);
+    else
+      rmsnorm_rows_kernel<RWN_MAXV><<<(unsigned)((rows + 7) / 8), 256, 0, ctx().stream>>>(
+          px, splits == 1, pr, residual ? residual->dtype == KD_F32 : 0, pw, weight->dtype, eps, ps, sum_f32, round_sum,
+          (__nv_bfloat16*)pn, rows, (int)n);
     return after_launch("rmsnorm_rows_kernel");
   }
   add_rmsnorm_kernel<<<(unsigned)rows, ARN_THREADS, 0, ctx().stream>>>(px, splits, pr, residual ? residual->dtype == KD_F32 : 0, pw,
