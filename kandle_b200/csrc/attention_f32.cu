@@ -17,12 +17,12 @@ namespace kd {
 constexpr int ATT_WARPS = 16;
 constexpr int ATT_TKV = 32;
 
-template <int DPL>  // head dims per lane: D = 32*DPL
+template <int DPL>  // head dims per lane: head_dim <= 32*DPL, padded with zeros
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_f32_kernel(const void* __restrict__ Q,
                                                                       const void* __restrict__ K,
                                                                       const void* __restrict__ V, void* __restrict__ O,
                                                                       AttnParams p) {
-  constexpr int D = 32 * DPL;
+  constexpr int D = 32 * DPL;   // padded head dim; p.D is the real one
   extern __shared__ float smem[];
   float* Ks = smem;                          // [TKV][D+1]
   float* Vs = Ks + ATT_TKV * (D + 1);        // [TKV][D]
@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_f32_kernel(const voi
   const float NEG = -1e20f;
 
   const int64_t q_off = (int64_t)b * p.sq[0] + (int64_t)h * p.sq[1] + (int64_t)row * p.sq[2];
-  for (int d = lane; d < D; d += 32) Qs[warp * D + d] = row_ok ? load_float(Q, p.dt_q, q_off + d * p.sq[3]) : 0.f;
+  for (int d = lane; d < D; d += 32) Qs[warp * D + d] = (row_ok && d < p.D) ? load_float(Q, p.dt_q, q_off + d * p.sq[3]) : 0.f;
 
   float acc[DPL];
 #pragma unroll
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_f32_kernel(const voi
       const int r = e / D, d = e - r * D;
       const int j = j0 + r;
       float kv = 0.f, vv = 0.f;
-      if (j < p.Skv) {
+      if (j < p.Skv && d < p.D) {
         kv = load_float(K, p.dt_k, k_base + (int64_t)j * p.sk[2] + d * p.sk[3]);
         vv = load_float(V, p.dt_v, v_base + (int64_t)j * p.sv[2] + d * p.sv[3]);
       }
@@ -94,7 +94,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_f32_kernel(const voi
   if (row_ok) {
     const int64_t o_off = (int64_t)b * p.so[0] + (int64_t)h * p.so[1] + (int64_t)row * p.so[2];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) store_float(O, p.dt_o, o_off + (int64_t)(lane + 32 * i) * p.so[3], acc[i] / l);
+    for (int i = 0; i < DPL; ++i)
+      if (lane + 32 * i < p.D) store_float(O, p.dt_o, o_off + (int64_t)(lane + 32 * i) * p.so[3], acc[i] / l);
   }
 }
 
@@ -148,13 +149,12 @@ int attention_f32_dispatch(const kd_tensor* q, const kd_tensor* k, const kd_tens
   if (p.B == 0 || p.Hq == 0 || p.Sq == 0) return KD_OK;
   KD_REQUIRE(p.Skv > 0, "flash_attention: empty key/value sequence");
   KD_REQUIRE(p.Hq <= 65535 && p.B <= 65535, "flash_attention: too many heads or batches for one launch");
-  switch (p.D) {
-    case 32: return launch_attention_f32<1>(pq, pk, pv, po, p);
-    case 64: return launch_attention_f32<2>(pq, pk, pv, po, p);
-    case 128: return launch_attention_f32<4>(pq, pk, pv, po, p);
-    case 256: return launch_attention_f32<8>(pq, pk, pv, po, p);
-    default: return fail(KD_ERR_UNSUPPORTED, "flash_attention: head_dim %d is not one of 32, 64, 128, 256", p.D);
-  }
+  KD_REQUIRE(p.D >= 1, "flash_attention: empty head dimension");
+  if (p.D <= 32) return launch_attention_f32<1>(pq, pk, pv, po, p);
+  if (p.D <= 64) return launch_attention_f32<2>(pq, pk, pv, po, p);
+  if (p.D <= 128) return launch_attention_f32<4>(pq, pk, pv, po, p);
+  if (p.D <= 256) return launch_attention_f32<8>(pq, pk, pv, po, p);
+  return fail(KD_ERR_UNSUPPORTED, "flash_attention: head_dim %d exceeds 256", p.D);
 }
 
 }  // namespace kd

@@ -32,7 +32,7 @@ def test_config1_sdpa_fp32_causal_gqa(backend, oracle):
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("b,hq,hkv,sq,skv,d", [
     (2, 4, 4, 33, 33, 64), (1, 8, 2, 1, 77, 128), (2, 2, 1, 17, 40, 32), (1, 4, 1, 127, 127, 128),
-    (1, 2, 2, 129, 129, 64), (1, 3, 3, 300, 300, 64), (1, 2, 1, 5, 260, 256)])
+    (1, 2, 2, 129, 129, 64), (1, 3, 3, 300, 300, 64), (1, 2, 1, 5, 260, 256), (2, 4, 2, 20, 20, 8), (1, 2, 2, 33, 40, 80)])
 def test_sdpa_shapes_and_tails(backend, oracle, causal, b, hq, hkv, sq, skv, d):
     q, k, v = synth.normal("q", (b, hq, sq, d)), synth.normal("k", (b, hkv, skv, d)), synth.normal("v", (b, hkv, skv, d))
     out = core.scaledDotProductAttention(Tensor(q), Tensor(k), Tensor(v), None, 0.0, causal)
