@@ -278,6 +278,21 @@ int kd_attention_decode_paged(const kd_tensor* q, const kd_tensor* k_pool, const
                               const kd_tensor* block_table, const kd_tensor* ctx_len, int ctx_len_host,
                               float scale, int splits, const kd_tensor* out);
 
+/* ---------------------------------------------------------------------------------------------
+ * Tensor-parallel collectives (no counterpart in the reference, which is single-device).  One
+ * process per GPU; NCCL is loaded at run time from `nccl_path` (NULL/"" = the system libnccl.so.2).
+ * Rank 0 creates the 128-byte id with kd_comm_unique_id, the host program distributes it, every
+ * rank calls kd_comm_init.  kd_allreduce_sum is enqueued on the library's stream (in place, bf16 or
+ * fp32) and is a no-op without a communicator.  kd_comm_check polls for asynchronous NCCL errors
+ * and aborts the communicator when one is found.
+ * ------------------------------------------------------------------------------------------- */
+int kd_comm_unique_id(const char* nccl_path, char* id_out, size_t id_bytes);
+int kd_comm_init(const char* nccl_path, int nranks, int rank, const char* id, size_t id_bytes);
+int kd_comm_info(int* nranks, int* rank);
+int kd_allreduce_sum(const kd_tensor* t);
+int kd_comm_check(void);
+int kd_comm_destroy(void);
+
 #ifdef __cplusplus
 }
 #endif

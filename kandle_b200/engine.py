@@ -46,13 +46,20 @@ def interleave_gate_up(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
 
 
 class Qwen3Engine:
-    def __init__(self, cfg: Qwen3Config, weights: dict, max_batch: int, max_seq_len: int):
-        """weights: HuggingFace-style names -> float32 arrays (rounded to bf16 on upload)."""
+    def __init__(self, cfg: Qwen3Config, weights: dict, max_batch: int, max_seq_len: int, tp_size: int = 1):
+        """weights: HuggingFace-style names -> float32 arrays (rounded to bf16 on upload).  With
+        tp_size > 1 `weights` is this rank's tensor-parallel slice (parallel.shard_qwen3_weights), cfg
+        describes the FULL model, and the library's communicator must have been initialised: the
+        partial outputs of o_proj and down_proj are all-reduced before the residual add."""
         self.cfg = cfg
+        self.tp = int(tp_size)
         self.B, self.max_seq_len = max_batch, max_seq_len
         c = cfg
-        self.H, self.D, self.Hq, self.Hkv, self.I, self.V, self.L = (c.hiddenSize, c.headDim, c.numAttentionHeads,
-                                                                     c.numKeyValueHeads, c.intermediateSize, c.vocabSize,
+        if c.numAttentionHeads % self.tp or c.numKeyValueHeads % self.tp or c.intermediateSize % self.tp:
+            raise ValueError(f"heads / intermediate size do not divide over {self.tp} ranks")
+        self.H, self.D, self.Hq, self.Hkv, self.I, self.V, self.L = (c.hiddenSize, c.headDim, c.numAttentionHeads // self.tp,
+                                                                     c.numKeyValueHeads // self.tp,
+                                                                     c.intermediateSize // self.tp, c.vocabSize,
                                                                      c.numHiddenLayers)
         if self.D not in (64, 128):
             raise ValueError("the fused engine supports head_dim 64 or 128")
@@ -92,6 +99,9 @@ class Qwen3Engine:
     def _norm(self, x, w, out, resid=None, sum_out=None):
         lib.call("kd_add_rmsnorm", _r(x), _r(resid), _r(w), ctypes.c_float(self.cfg.rmsNormEps), _r(sum_out), _r(out))
 
+    def _allreduce(self, t) -> None:
+        lib.call("kd_allreduce_sum", _r(t))
+
     def kv_bytes_per_token(self) -> int:
         return 2 * self.L * self.Hkv * self.D * 2
 
@@ -104,6 +114,7 @@ class Qwen3Engine:
             self._prefill_bufs = {key: {
                 "ids": core.empty((T,), "int32"), "emb": e(T, self.H), "h": core.empty((T, self.H), "float32"),
                 "h1": core.empty((T, self.H), "float32"), "x": e(T, self.H),
+                "part": e(T, self.H) if self.tp > 1 else None,
                 "qkv": e(T, self.nqkv), "q": e(B, S, self.Hq, self.D), "attn": e(B, S, self.Hq, self.D),
                 "act": e(T, self.I), "cos": core.empty((S, self.D // 2), "float32"),
                 "sin": core.empty((S, self.D // 2), "float32"), "last": core.empty((B, self.H), "float32"), "xl": e(B, self.H),
@@ -141,16 +152,29 @@ class Qwen3Engine:
         for li, lw in enumerate(self.layers):
             kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
             vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
-            self._norm(h, lw["in_norm"], w["x"])
+            if self.tp == 1 or li == 0:
+                self._norm(h, lw["in_norm"], w["x"])     # (tensor parallel: later layers get x from the fused add+norm)
             self._linear(w["x"], lw["wqkv"], w["qkv"])
             lib.call("kd_qkv_norm_rope_cachewrite", _r(w["qkv"]), _r(lw["q_norm"]), _r(lw["k_norm"]),
                      ctypes.c_float(c.rmsNormEps), _r(w["cos"]), _r(w["sin"]), _r(kc), _r(vc), None, 0, _r(w["q"]))
             kp, vp = kc.slice(f":, :, :{S}, :"), vc.slice(f":, :, :{S}, :")
             lib.call("kd_flash_attention", _r(q_bhsd), _r(kp), _r(vp), _r(o_bhsd), ctypes.c_float(self.scale), 1)
-            self._linear(attn2d, lw["wo"], h1, resid=h, epi=1)
-            self._norm(h1, lw["post_norm"], w["x"])
-            self._linear(w["x"], lw["wgu"], w["act"], epi=2)
-            self._linear(w["act"], lw["wdown"], h, resid=h1, epi=1)
+            if self.tp == 1:
+                self._linear(attn2d, lw["wo"], h1, resid=h, epi=1)
+                self._norm(h1, lw["post_norm"], w["x"])
+                self._linear(w["x"], lw["wgu"], w["act"], epi=2)
+                self._linear(w["act"], lw["wdown"], h, resid=h1, epi=1)
+            else:
+                # tensor parallel: each rank holds a partial sum of o_proj / down_proj (bf16), summed
+                # over ranks before the residual add (fused with the following RMSNorm)
+                self._linear(attn2d, lw["wo"], w["part"])
+                self._allreduce(w["part"])
+                self._norm(w["part"], lw["post_norm"], w["x"], resid=h, sum_out=h1)
+                self._linear(w["x"], lw["wgu"], w["act"], epi=2)
+                self._linear(w["act"], lw["wdown"], w["part"])
+                self._allreduce(w["part"])
+                nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
+                self._norm(w["part"], nxt, w["x"], resid=h1, sum_out=h)
             for t in (kc, vc, kp, vp):
                 t.dispose()
         # tied lm_head on the last position of every sequence (select commutes with the row-wise matmul)
@@ -220,10 +244,14 @@ class Qwen3Engine:
                      _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
             lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
             lib.call("kd_linear_bf16_skinny", _r(attn2d), _r(lw["wo"]), 0, _r(d["o_p"]))
+            if self.tp > 1:
+                self._allreduce(d["o_p"])
             self._norm(d["o_p"], lw["post_norm"], d["x"], resid=h, sum_out=h1)
             lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wgu"]), 0, _r(d["gu_p"]))
             lib.call("kd_swiglu", _r(d["gu_p"]), _r(d["act"]))
             lib.call("kd_linear_bf16_skinny", _r(d["act"]), _r(lw["wdown"]), 0, _r(d["down_p"]))
+            if self.tp > 1:
+                self._allreduce(d["down_p"])
             nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
             self._norm(d["down_p"], nxt, d["x"], resid=h1, sum_out=h)
             kc.dispose()

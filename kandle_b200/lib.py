@@ -141,6 +141,12 @@ _SIGNATURES = {
     "kd_graph_end": [ctypes.POINTER(_u64)],
     "kd_graph_launch": [_u64],
     "kd_graph_destroy": [_u64],
+    "kd_comm_unique_id": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t],
+    "kd_comm_init": [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t],
+    "kd_comm_info": [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+    "kd_allreduce_sum": [_T],
+    "kd_comm_check": [],
+    "kd_comm_destroy": [],
     "kd_attention_decode": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_noalloc": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_paged": [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
