@@ -41,7 +41,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 ARCH = dict(vocab=151936, hidden=1024, inter=3072, layers=28, heads=16, kv_heads=8, head_dim=128)
+ARCH_4B = dict(vocab=151936, hidden=2560, inter=9728, layers=36, heads=32, kv_heads=8, head_dim=128)
 METRIC = "qwen3_0.6b_bf16_prefill_decode_tokens_per_s"
+METRIC_4B = "qwen3_4b_bf16_tensor_parallel_prefill_decode_tokens_per_s"
 
 
 def parse_args():
@@ -50,18 +52,32 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=32)
-    ap.add_argument("--prompt", type=int, default=2048)
-    ap.add_argument("--decode", type=int, default=256)
-    ap.add_argument("--layers", type=int, default=ARCH["layers"])
+    ap.add_argument("--workload", default="qwen3-0.6b", choices=["qwen3-0.6b", "qwen3-4b-tp"],
+                    help="qwen3-0.6b: 32 sequences per GPU, replicated model (default, the headline); "
+                         "qwen3-4b-tp: 8 x 4096 + 128 steps, one model tensor-parallel over all ranks (strong scaling)")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--prompt", type=int, default=None)
+    ap.add_argument("--decode", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--vocab", type=int, default=ARCH["vocab"])
     ap.add_argument("--cpu-sample", default="1x256+8", help="cpu baseline sample: <seqs>x<prompt>+<decode steps>")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    return ap.parse_args()
+    a = ap.parse_args()
+    tp = a.workload == "qwen3-4b-tp"
+    a.arch = dict(ARCH_4B if tp else ARCH)
+    a.batch = a.batch or (8 if tp else 32)
+    a.prompt = a.prompt or (4096 if tp else 2048)
+    a.decode = a.decode or (128 if tp else 256)
+    a.layers = a.layers or a.arch["layers"]
+    a.metric = METRIC_4B if tp else METRIC
+    a.tp = tp
+    return a
 
 
 def workload_name(a) -> str:
-    return f"qwen3-0.6b-bf16-b{a.batch}-p{a.prompt}-d{a.decode}" + ("" if a.layers == 28 and a.vocab == 151936 else f"-L{a.layers}-V{a.vocab}")
+    base = "qwen3-4b-tp" if a.tp else "qwen3-0.6b"
+    full = a.layers == a.arch["layers"] and a.vocab == 151936
+    return f"{base}-bf16-b{a.batch}-p{a.prompt}-d{a.decode}" + ("" if full else f"-L{a.layers}-V{a.vocab}")
 
 
 # --------------------------------------------------------------------------- clocks sampler
@@ -111,7 +127,7 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm (oracle)
-def cpu_arm(sample: str, layers: int, vocab: int):
+def cpu_arm(sample: str, layers: int, vocab: int, arch: dict = ARCH):
     """Times the CPU oracle on `<seqs>x<prompt>+<steps>`: prefill + greedy decode with a KV cache,
     fp32, all host threads.  Returns (tokens/s, description, threads)."""
     from kandle_b200 import lib, synth
@@ -120,7 +136,7 @@ def cpu_arm(sample: str, layers: int, vocab: int):
     seqs, rest = sample.split("x")
     prompt, steps = rest.split("+")
     seqs, prompt, steps = int(seqs), int(prompt), int(steps)
-    dims = dict(ARCH, layers=layers, vocab=vocab)
+    dims = dict(arch, layers=layers, vocab=vocab)
     w = synth.qwen3_weights(**dims)
     w = {k: lib.round_to_bf16(v) for k, v in w.items()}
     cfg = orc.Qwen3Config(vocab_size=vocab, hidden_size=dims["hidden"], intermediate_size=dims["inter"],
@@ -143,7 +159,7 @@ def run_reference(a) -> None:
     vals = []
     desc, threads = "", 1
     for i in range(a.warmup + a.steps):
-        v, desc, threads, dt = cpu_arm(a.cpu_sample, a.layers, a.vocab)
+        v, desc, threads, dt = cpu_arm(a.cpu_sample, a.layers, a.vocab, a.arch)
         if i >= a.warmup:
             vals.append((v, dt))
         if i == 0 and dt > 60:     # keep the whole run within minutes
@@ -152,9 +168,9 @@ def run_reference(a) -> None:
     v = float(np.mean([x[0] for x in vals]))
     ms = float(np.mean([x[1] for x in vals])) * 1e3
     line = {
-        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": a.gpus, "steps": len(vals),
-        "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
+        "impl": "reference", "metric": a.metric, "value": v, "unit": "tokens/s", "n_gpus": a.gpus, "steps": len(vals),
+        "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if a.tp else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(a), "note": "CPU arm runs a bounded sample of the workload: " + desc},
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -185,15 +201,25 @@ def run_ours(a) -> None:
     from kandle_b200.model_utils import Qwen3Config
 
     be = kandle_b200.init(local_rank)
-    dims = dict(ARCH, layers=a.layers, vocab=a.vocab)
-    weights = synth.qwen3_weights(**dims)                     # identical on every rank (replicated model)
+    dims = dict(a.arch, layers=a.layers, vocab=a.vocab)
+    tp_size = world if a.tp else 1
+    if tp_size > 1:
+        from kandle_b200 import parallel
+        def bcast(obj):
+            box = [obj]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+        parallel.init_tensor_parallel(rank, world, bcast)
+    # one tensor at a time; replicated model (every rank identical) or this rank's tensor-parallel slice
+    weights = synth.LazyQwen3Weights(**dims, shard=(rank, world) if tp_size > 1 else None)
     cfg = Qwen3Config(vocabSize=a.vocab, hiddenSize=dims["hidden"], intermediateSize=dims["inter"], numHiddenLayers=a.layers,
                       numAttentionHeads=dims["heads"], numKeyValueHeads=dims["kv_heads"], headDim=dims["head_dim"], dtype="bfloat16")
     B, S, T = a.batch, a.prompt, a.decode
     max_s = S + T + 16
-    eng = Qwen3Engine(cfg, weights, B, max_s)
+    eng = Qwen3Engine(cfg, weights, B, max_s, tp_size=tp_size)
     del weights
-    ids_host = synth.token_ids(f"bench.ids.rank{rank}", (B, S), a.vocab)   # each rank: its own sequences
+    # data parallel: each rank its own sequences; tensor parallel: every rank the same batch
+    ids_host = synth.token_ids("bench.ids.tp" if a.tp else f"bench.ids.rank{rank}", (B, S), a.vocab)
     ids_dev = Tensor(ids_host)                                            # resident copy for `value`
     pinned = ctypes.c_void_p()
     lib.call("kd_host_alloc_pinned", ctypes.c_uint64(ids_host.nbytes), ctypes.byref(pinned))
@@ -305,7 +331,7 @@ def run_ours(a) -> None:
             attn_all_layers()
         k1.record()
         us = k0.elapsed_ms(k1) * 1e3 / (reps * n_l)
-        alg_bytes = 2.0 * B * dims["kv_heads"] * ctx_mean * dims["head_dim"] * 2
+        alg_bytes = 2.0 * B * (dims["kv_heads"] // tp_size) * ctx_mean * dims["head_dim"] * 2
         ach = alg_bytes / (us * 1e-6) / 1e9
         roofline = {"kernel": "flash_attention_tcgen05_kernel<decode> + decode_combine_kernel", "bound": "hbm", "achieved": ach,
                     "peak": hbm_peak, "peak_source": hbm_src, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
@@ -323,7 +349,7 @@ def run_ours(a) -> None:
         return a0.elapsed_ms(a1) / reps
     Tt = B * S
     ms = timed(lambda: eng._linear(w["x"], lw["wgu"], w["act"], epi=2))
-    fl = 2.0 * Tt * 2 * dims["inter"] * dims["hidden"]
+    fl = 2.0 * Tt * 2 * (dims["inter"] // tp_size) * dims["hidden"]
     other["gemm_gate_up_swiglu"] = {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": tc_peak, "peak_source": tc_src,
                                     "unit": "TFLOP/s", "frac": fl / ms / 1e9 / tc_peak, "us_per_launch": ms * 1e3}
     ms = timed(lambda: eng._linear(w["x"], lw["wqkv"], w["qkv"]))
@@ -334,7 +360,7 @@ def run_ours(a) -> None:
     kp, vp = eng.k_cache[0].slice(f":{B}, :, :{S}, :"), eng.v_cache[0].slice(f":{B}, :, :{S}, :")
     ms = timed(lambda: lib.call("kd_flash_attention", ctypes.byref(q_bhsd._handle.c()), ctypes.byref(kp._handle.c()),
                                 ctypes.byref(vp._handle.c()), ctypes.byref(o_bhsd._handle.c()), ctypes.c_float(eng.scale), 1))
-    fl = 4.0 * B * dims["heads"] * dims["head_dim"] * (S * (S + 1) / 2)
+    fl = 4.0 * B * (dims["heads"] // tp_size) * dims["head_dim"] * (S * (S + 1) / 2)
     other["flash_attention_prefill"] = {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": tc_peak, "peak_source": tc_src,
                                         "unit": "TFLOP/s", "frac": fl / ms / 1e9 / tc_peak, "us_per_launch": ms * 1e3}
     be.synchronize()
@@ -346,33 +372,39 @@ def run_ours(a) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e, ms_prefill, ms_decode = [float(x) for x in t.tolist()]
     tokens_rank = B * (S + T)
-    tokens_all = tokens_rank * world
+    tokens_all = tokens_rank * (1 if a.tp else world)     # tensor parallel: all ranks work on the same tokens
 
     cpu = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
-        v, desc, threads, _ = cpu_arm(a.cpu_sample, a.layers, a.vocab)
+        v, desc, threads, _ = cpu_arm(a.cpu_sample, a.layers, a.vocab, a.arch)
         cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc}
 
     if rank == 0:
-        flops_prefill = B * S * (2.0 * 15728640 * a.layers) + 4.0 * B * dims["heads"] * dims["head_dim"] * (S * (S + 1) / 2) * a.layers
+        per_layer_params = dims["hidden"] * ((dims["heads"] + 2 * dims["kv_heads"]) * dims["head_dim"]) + \
+            dims["hidden"] * dims["heads"] * dims["head_dim"] + 3 * dims["hidden"] * dims["inter"]
+        flops_prefill = B * S * (2.0 * per_layer_params * a.layers) + 4.0 * B * dims["heads"] * dims["head_dim"] * (S * (S + 1) / 2) * a.layers
         line = {
-            "metric": METRIC, "value": tokens_all / (ms_dev * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
-            "warmup": a.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": a.metric, "value": tokens_all / (ms_dev * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong" if a.tp else "weak",
+            "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(a), "sequences_per_gpu": B, "prompt_tokens": S, "decode_steps": T,
                        "tokens_per_step_per_gpu": tokens_rank, "logits": "last position only (select before the tied lm_head)",
-                       "l2": "inputs larger than L2 (weights 1.2 GB + KV cache 8.5 GB per pass)", "parallelism": f"dp{world}"},
+                       "l2": "inputs larger than L2 (bf16 weights and KV cache, GBs per pass)", "parallelism": f"tp{world}" if a.tp else f"dp{world}"},
             "e2e": {"value": tokens_all / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(ids_host.nbytes),
                     "d2h_bytes_per_step": int(B * 8 * T), "ms_per_step": ms_e2e},
             "gpu_launches": int(launches),
             "phases": {"prefill_ms": ms_prefill, "decode_ms": ms_decode,
-                       "prefill_tokens_per_s": B * S * world / (ms_prefill * 1e-3),
-                       "decode_tokens_per_s": B * max(T - 1, 1) * world / (max(ms_decode, 1e-9) * 1e-3),
-                       "prefill_tflops": flops_prefill / (ms_prefill * 1e-3) / 1e12,
-                       "prefill_frac_of_tensor_peak": flops_prefill / (ms_prefill * 1e-3) / 1e12 / tc_peak},
+                       "prefill_tokens_per_s": B * S * (tokens_all // tokens_rank) / (ms_prefill * 1e-3),
+                       "decode_tokens_per_s": B * max(T - 1, 1) * (tokens_all // tokens_rank) / (max(ms_decode, 1e-9) * 1e-3),
+                       "prefill_tflops_per_gpu": flops_prefill / (tp_size if a.tp else 1) / (ms_prefill * 1e-3) / 1e12,
+                       "prefill_frac_of_tensor_peak": flops_prefill / (tp_size if a.tp else 1) / (ms_prefill * 1e-3) / 1e12 / tc_peak},
             "roofline": roofline, "roofline_other": other, "cpu_baseline": cpu, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    eng.dispose()                 # graphs that captured NCCL work must go before the communicator
+    if tp_size > 1:
+        lib.call("kd_comm_destroy")
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

@@ -284,7 +284,8 @@ int kd_attention_decode_paged(const kd_tensor* q, const kd_tensor* k_pool, const
  * Rank 0 creates the 128-byte id with kd_comm_unique_id, the host program distributes it, every
  * rank calls kd_comm_init.  kd_allreduce_sum is enqueued on the library's stream (in place, bf16 or
  * fp32) and is a no-op without a communicator.  kd_comm_check polls for asynchronous NCCL errors
- * and aborts the communicator when one is found.
+ * and aborts the communicator when one is found.  Destroy every graph that captured an all-reduce
+ * (kd_graph_destroy) before kd_comm_destroy: NCCL waits for such references to go away.
  * ------------------------------------------------------------------------------------------- */
 int kd_comm_unique_id(const char* nccl_path, char* id_out, size_t id_bytes);
 int kd_comm_init(const char* nccl_path, int nranks, int rank, const char* id, size_t id_bytes);

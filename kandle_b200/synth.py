@@ -92,3 +92,41 @@ def synthetic_audio(name: str, n_samples: int = 480000, sr: int = 16000, base_se
         x += g.uniform(0.05, 0.3) * np.sin(2 * np.pi * g.uniform(80, 4000) * t + g.uniform(0, 2 * np.pi))
     x += g.standard_normal(n_samples) * 0.01
     return x.astype(np.float32)
+
+
+class LazyQwen3Weights:
+    """dict-like view of the synthetic Qwen3 weights that materialises one tensor at a time (a 4B
+    model would need 16 GB of host memory per rank otherwise).  Same values as qwen3_weights().
+    With `shard=(rank, world)` tensors come out as that rank's tensor-parallel slice; `transform`
+    (e.g. bf16 rounding) is applied to every tensor handed out."""
+
+    def __init__(self, *, vocab, hidden, inter, layers, heads, kv_heads, head_dim, std=0.02, norm_jitter=0.0,
+                 base_seed=BASE_SEED, shard=None, transform=None):
+        self.d = dict(vocab=vocab, hidden=hidden, inter=inter, layers=layers, heads=heads, kv_heads=kv_heads, head_dim=head_dim)
+        self.std, self.jitter, self.seed, self.shard, self.transform = std, norm_jitter, base_seed, shard, transform
+
+    def _shape(self, name):
+        d = self.d
+        if name == "model.embed_tokens.weight":
+            return (d["vocab"], d["hidden"])
+        if name.endswith("norm.weight"):
+            return (d["head_dim"],) if ("q_norm" in name or "k_norm" in name) else (d["hidden"],)
+        table = {"q_proj": (d["heads"] * d["head_dim"], d["hidden"]), "k_proj": (d["kv_heads"] * d["head_dim"], d["hidden"]),
+                 "v_proj": (d["kv_heads"] * d["head_dim"], d["hidden"]), "o_proj": (d["hidden"], d["heads"] * d["head_dim"]),
+                 "gate_proj": (d["inter"], d["hidden"]), "up_proj": (d["inter"], d["hidden"]), "down_proj": (d["hidden"], d["inter"])}
+        for k, shp in table.items():
+            if name.endswith(k + ".weight"):
+                return shp
+        raise KeyError(name)
+
+    def __getitem__(self, name):
+        shape = self._shape(name)
+        if name.endswith("norm.weight"):
+            w = normal(name, shape, self.jitter, 1.0, self.seed) if self.jitter else np.ones(shape, np.float32)
+        else:
+            w = normal(name, shape, self.std, base_seed=self.seed)
+        if self.shard is not None and self.shard[1] > 1:
+            from .parallel import shard_qwen3_weights
+            w = shard_qwen3_weights({name: w}, heads=self.d["heads"], kv_heads=self.d["kv_heads"], head_dim=self.d["head_dim"],
+                                    rank=self.shard[0], world=self.shard[1])[name]
+        return self.transform(w) if self.transform else w
