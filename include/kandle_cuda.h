@@ -203,11 +203,11 @@ int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_tensor*
                    const kd_tensor* out);
 
 /* `linear` for 1..128 activation rows (decode): weights are streamed once from HBM with the
- * operands swapped so that weight rows fill the MMA's M dimension.  out is either bf16 [rows,N]
- * or fp32 [splits,rows,N] split-K partial sums that the consumers below add up (splits is taken
- * from out's leading extent; the `splits` argument only matters for choosing that extent: 0 asks
- * the library, see kd_linear_bf16_skinny_splits). */
-int kd_linear_bf16_skinny(const kd_tensor* x, const kd_tensor* weight, int splits, const kd_tensor* out);
+ * operands swapped so that weight rows fill the MMA's M dimension.  The shape and dtype of `out`
+ * select the form: bf16 [rows,N] (no split-K); bf16 [rows,N/2] with epilogue = KD_EPI_SWIGLU; or fp32
+ * [splits,rows,N] split-K partial sums that the consumers below add up (kd_linear_bf16_skinny_splits
+ * suggests `splits` for a given weight shape). */
+int kd_linear_bf16_skinny(const kd_tensor* x, const kd_tensor* weight, int epilogue, const kd_tensor* out);
 int kd_linear_bf16_skinny_splits(int64_t N, int64_t K, int* splits_out);
 
 /* cos/sin tables [seq_len, D/2] fp32 for positions start..start+seq_len-1: arange -> mul(inv_freq)
@@ -237,6 +237,9 @@ int kd_increment_i32(const kd_tensor* scalar, int delta);
 
 /* CUDA-graph capture of everything enqueued between begin and end (no counterpart in the
  * reference, whose per-op host overhead is what this removes). */
+/* Enables programmatic dependent launch for the kernels of the decode step (they all begin with a
+ * grid-dependency wait), so that each kernel's launch latency overlaps its predecessor. */
+int kd_set_pdl(int enabled);
 int kd_graph_begin(void);
 int kd_graph_end(uint64_t* graph_out);
 int kd_graph_launch(uint64_t graph);

@@ -135,6 +135,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z;
   int h, hk, q0, kv_len, j_begin, j_end, kv_end;
+  if (DECODE) pdl_wait();   // the context length below is written by the previous step
   if (DECODE) {
     hk = blockIdx.y;
     h = hk;                     // Q tensor map is indexed by (row-in-group, kv head, batch)
@@ -189,6 +190,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (DECODE) pdl_trigger();   // after the TMEM allocation
 
   if (warp == 0) {
     if (lane == 0) {
@@ -428,7 +430,8 @@ static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured = true;
   }
-  flash_attention_tcgen05_kernel<D, DECODE><<<grid, FA_THREADS, SMEM, ctx().stream>>>(tq, tk, tv, p);
+  if (DECODE) KD_CUDA_CHECK(launch_ex(flash_attention_tcgen05_kernel<D, DECODE>, grid, dim3(FA_THREADS), (size_t)SMEM, tq, tk, tv, p));
+  else flash_attention_tcgen05_kernel<D, DECODE><<<grid, FA_THREADS, SMEM, ctx().stream>>>(tq, tk, tv, p);
   return after_launch(DECODE ? "flash_attention_tcgen05_kernel<decode>" : "flash_attention_tcgen05_kernel");
 }
 
@@ -479,6 +482,8 @@ int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       __nv_bfloat16* __restrict__ out, int64_t so_b, int64_t so_h, int B, int Hkv,
                                       int group, int splits, int D) {
+  pdl_wait();
+  pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int Hq = Hkv * group;
   if (warp >= B * Hq) return;
@@ -583,9 +588,9 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   if (D == 128) KD_TRY((launch_fa<128, true>(tq, tk, tv, p, grid)));
   else KD_TRY((launch_fa<64, true>(tq, tk, tv, p, grid)));
   const int warps = B * Hq;
-  decode_combine_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx().stream>>>(p.part_o, p.part_ml, static_cast<__nv_bfloat16*>(po),
-                                                                         out->strides[0], out->strides[1], B, Hkv, group,
-                                                                         splits, D);
+  KD_CUDA_CHECK(launch_ex(decode_combine_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, (const float*)p.part_o,
+                          (const float*)p.part_ml, static_cast<__nv_bfloat16*>(po), (int64_t)out->strides[0],
+                          (int64_t)out->strides[1], B, Hkv, group, splits, D));
   return after_launch("decode_combine_kernel");
 }
 
@@ -617,7 +622,7 @@ int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_ten
   const int max_blocks = (int)((k->shape[2] + FA_BKV - 1) / FA_BKV);
   if (splits <= 0) {
     const int pairs = B * Hkv > 0 ? B * Hkv : 1;
-    splits = (4 * ctx().sm_count + pairs - 1) / pairs;
+    splits = (2 * ctx().sm_count) / pairs;   // two CTAs fit per SM: stay within one wave
     if (splits > max_blocks) splits = max_blocks;
     if (splits < 1) splits = 1;
   }

@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <utility>
 
 #include "../../include/kandle_cuda.h"
 
@@ -53,6 +54,7 @@ struct Context {
   cudaStream_t stream = nullptr;
   uint64_t launches = 0;
   int* error_flag = nullptr;  // device int, set by kernels that detect a problem
+  bool pdl = false;           // launch kernels with programmatic dependent launch (kd_set_pdl)
   void* workspace = nullptr;  // library-owned scratch, grown on demand
   uint64_t workspace_bytes = 0;
 };
@@ -95,6 +97,32 @@ inline bool is_contiguous(const kd_tensor* t) {
 }
 
 inline bool is_float_dtype(int dt) { return dt == KD_F32 || dt == KD_F16 || dt == KD_BF16; }
+
+// ----------------------------------------------------------------------------- programmatic dependent launch
+// Every kernel of the decode step starts with pdl_wait() (all writes of the preceding kernels are
+// visible after it; without the launch attribute it is a no-op) and calls pdl_trigger() once its
+// CTAs hold their resources, so that the next kernel's launch latency and prologue overlap this
+// kernel's execution.  pdl_trigger() must come after any TMEM allocation: a dependent CTA that
+// grabbed tensor memory first would block this kernel's allocation while waiting for it to finish.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx().stream;
+  cudaLaunchAttribute attr[1];
+  if (ctx().pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // ----------------------------------------------------------------------------- device helpers
 __device__ __forceinline__ float load_float(const void* base, int dt, int64_t idx) {

@@ -418,3 +418,9 @@ KD_API int kd_event_destroy(uint64_t event) {
   KD_CUDA_CHECK(cudaEventDestroy(reinterpret_cast<cudaEvent_t>(event)));
   return KD_OK;
 }
+
+KD_API int kd_set_pdl(int enabled) {
+  KD_TRY(require_init());
+  ctx().pdl = enabled != 0;
+  return KD_OK;
+}

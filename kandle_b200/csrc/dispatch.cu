@@ -84,9 +84,9 @@ static int decode_common(const kd_tensor* q, const kd_tensor* k, const kd_tensor
   const int max_keys = table ? max_pages * 128 : (int)k->shape[2];
   const int max_blocks = (max_keys + 127) / 128;
   if (splits <= 0) {
-    // aim at ~4 CTAs per SM worth of work items, never more splits than key tiles
+    // one wave of CTAs (2 per SM), never more splits than key tiles
     const int pairs = B * Hkv > 0 ? B * Hkv : 1;
-    splits = (4 * ctx().sm_count + pairs - 1) / pairs;
+    splits = (2 * ctx().sm_count) / pairs;   // two CTAs fit per SM: stay within one wave
     if (splits > max_blocks) splits = max_blocks;
     if (splits < 1) splits = 1;
   }

@@ -17,6 +17,8 @@ namespace kd {
 // angles reach thousands of radians.
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int* __restrict__ pos_dev, int pos_host,
                                   int seq, int half, float* __restrict__ cos_out, float* __restrict__ sin_out) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= seq * half) return;
   const int s = i / half, e = i - s * half;
@@ -100,6 +102,8 @@ __global__ void qkv_norm_rope_kernel(const void* __restrict__ src, const void* _
                                      const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q_out,
                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                      const int* __restrict__ pos_dev, QkvRopeParams p, int* __restrict__ err) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int V = D / 32;
   constexpr int HALF = D / 2;
   const int l16 = threadIdx.x & 15;
@@ -199,6 +203,8 @@ __global__ void __launch_bounds__(ARN_THREADS) add_rmsnorm_kernel(const void* __
                                                                    void* __restrict__ sum_out, int sum_f32,
                                                                    __nv_bfloat16* __restrict__ norm_out, int rows, int n) {
   __shared__ float red[ARN_THREADS / 32];
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const int nvec = n / 8;
   float v[ARN_MAXV][8];
@@ -359,7 +365,11 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const void* __restric
   }
 }
 
-__global__ void increment_i32_kernel(int* p, int delta) { *p += delta; }
+__global__ void increment_i32_kernel(int* p, int delta) {
+  pdl_wait();
+  pdl_trigger();
+  *p += delta;
+}
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -390,8 +400,8 @@ KD_API int kd_rope_table(const kd_tensor* inv_freq, const kd_tensor* pos, int st
   KD_TRY(tensor_ptr(cos_out, &pc));
   KD_TRY(tensor_ptr(sin_out, &ps));
   const int total = seq_len * half;
-  rope_table_kernel<<<(total + 255) / 256, 256, 0, ctx().stream>>>((const float*)pi, pos_dev, start_pos, seq_len, half,
-                                                                 (float*)pc, (float*)ps);
+  KD_CUDA_CHECK(launch_ex(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, (const float*)pi, pos_dev, start_pos, seq_len,
+                          half, (float*)pc, (float*)ps));
   return after_launch("rope_table_kernel");
 }
 
@@ -464,14 +474,16 @@ KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_
                  (reinterpret_cast<uintptr_t>(pvc) & 7) == 0 && (reinterpret_cast<uintptr_t>(pqo) & 7) == 0,
              "qkv / cache / q_out must be 16- / 8-byte aligned");
   KD_REQUIRE(tokens <= 0x7fffffff, "too many tokens for one launch");
+  const void* csrc = psrc;
+  const void *cqw = pqw, *ckw = pkw;
   if (D == 128)
-    qkv_norm_rope_kernel<128><<<blocks, threads, 0, ctx().stream>>>(
-        psrc, pqw, q_norm_weight->dtype, pkw, k_norm_weight->dtype, (const float*)pcos, (const float*)psin, (__nv_bfloat16*)pqo,
-        (__nv_bfloat16*)pkc, (__nv_bfloat16*)pvc, pos_dev, p, ctx().error_flag);
+    KD_CUDA_CHECK(launch_ex(qkv_norm_rope_kernel<128>, blocks, dim3(threads), 0, csrc, cqw, (int)q_norm_weight->dtype, ckw,
+                            (int)k_norm_weight->dtype, (const float*)pcos, (const float*)psin, (__nv_bfloat16*)pqo,
+                            (__nv_bfloat16*)pkc, (__nv_bfloat16*)pvc, pos_dev, p, ctx().error_flag));
   else
-    qkv_norm_rope_kernel<64><<<blocks, threads, 0, ctx().stream>>>(
-        psrc, pqw, q_norm_weight->dtype, pkw, k_norm_weight->dtype, (const float*)pcos, (const float*)psin, (__nv_bfloat16*)pqo,
-        (__nv_bfloat16*)pkc, (__nv_bfloat16*)pvc, pos_dev, p, ctx().error_flag);
+    KD_CUDA_CHECK(launch_ex(qkv_norm_rope_kernel<64>, blocks, dim3(threads), 0, csrc, cqw, (int)q_norm_weight->dtype, ckw,
+                            (int)k_norm_weight->dtype, (const float*)pcos, (const float*)psin, (__nv_bfloat16*)pqo,
+                            (__nv_bfloat16*)pkc, (__nv_bfloat16*)pvc, pos_dev, p, ctx().error_flag));
   return after_launch("qkv_norm_rope_kernel");
 }
 
@@ -543,9 +555,9 @@ KD_API int kd_add_rmsnorm(const kd_tensor* x, const kd_tensor* residual, const k
           (__nv_bfloat16*)pn, rows, (int)n);
     return after_launch("rmsnorm_rows_kernel");
   }
-  add_rmsnorm_kernel<<<(unsigned)rows, ARN_THREADS, 0, ctx().stream>>>(px, splits, pr, residual ? residual->dtype == KD_F32 : 0, pw,
-                                                                     weight->dtype, eps, ps, sum_f32, (__nv_bfloat16*)pn,
-                                                                     (int)rows, (int)n);
+  KD_CUDA_CHECK(launch_ex(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(ARN_THREADS), 0, (const void*)px, splits, (const void*)pr,
+                          (int)(residual ? residual->dtype == KD_F32 : 0), (const void*)pw, (int)weight->dtype, eps, ps, sum_f32,
+                          (__nv_bfloat16*)pn, (int)rows, (int)n));
   return after_launch("add_rmsnorm_kernel");
 }
 
@@ -554,13 +566,14 @@ KD_API int kd_increment_i32(const kd_tensor* scalar, int delta) {
   KD_REQUIRE(scalar && scalar->dtype == KD_I32 && numel(scalar) == 1, "scalar must be a device int32 scalar");
   void* p = nullptr;
   KD_TRY(tensor_ptr(scalar, &p));
-  increment_i32_kernel<<<1, 1, 0, ctx().stream>>>((int*)p, delta);
+  KD_CUDA_CHECK(launch_ex(increment_i32_kernel, dim3(1), dim3(1), 0, (int*)p, delta));
   return after_launch("increment_i32_kernel");
 }
 
-KD_API int kd_linear_bf16_skinny(const kd_tensor* x, const kd_tensor* weight, int splits, const kd_tensor* out) {
+KD_API int kd_linear_bf16_skinny(const kd_tensor* x, const kd_tensor* weight, int epilogue, const kd_tensor* out) {
   KD_TRY(require_init());
   KD_REQUIRE(x && weight && out, "null tensor");
+  KD_REQUIRE(epilogue == KD_EPI_NONE || epilogue == KD_EPI_SWIGLU, "kd_linear_bf16_skinny supports KD_EPI_NONE and KD_EPI_SWIGLU");
   KD_REQUIRE(x->dtype == KD_BF16 && weight->dtype == KD_BF16, "kd_linear_bf16_skinny needs bf16 activations and weights");
   KD_REQUIRE(is_contiguous(x) && x->ndim >= 1 && weight->ndim == 2 && weight->strides[1] == 1 && is_contiguous(out),
              "activations / output must be contiguous, weight [N,K] with unit K stride");
@@ -568,21 +581,23 @@ KD_API int kd_linear_bf16_skinny(const kd_tensor* x, const kd_tensor* weight, in
   KD_REQUIRE(weight->shape[1] == K && K > 0, "weight has K=%lld, activations have K=%lld", (long long)weight->shape[1], (long long)K);
   const int64_t M = numel(x) / K;
   KD_REQUIRE(M >= 1 && M <= 128, "kd_linear_bf16_skinny handles 1..128 rows, got %lld", (long long)M);
-  if (splits <= 0) splits = gemm_skinny_auto_splits((int)N, (int)K);
   const int total_kb = (int)((K + 63) / 64);
-  if (splits > total_kb) splits = total_kb;
   void *px, *pw, *po;
   KD_TRY(tensor_ptr(x, &px));
   KD_TRY(tensor_ptr(weight, &pw));
   KD_TRY(tensor_ptr(out, &po));
+  if (epilogue == KD_EPI_SWIGLU) {
+    KD_REQUIRE(out->dtype == KD_BF16 && numel(out) == M * (N / 2), "SiLU*up output must be bf16 [rows, N/2]");
+    return gemm_bf16_skinny(px, K, pw, weight->strides[0], (int)M, (int)N, (int)K, 1, nullptr, po, 1);
+  }
   if (out->dtype == KD_BF16) {
     KD_REQUIRE(numel(out) == M * N, "bf16 output must be [rows, N]");
-    return gemm_bf16_skinny(px, K, pw, weight->strides[0], (int)M, (int)N, (int)K, 1, nullptr, po);
+    return gemm_bf16_skinny(px, K, pw, weight->strides[0], (int)M, (int)N, (int)K, 1, nullptr, po, 0);
   }
   KD_REQUIRE(out->dtype == KD_F32 && numel(out) % (M * N) == 0 && numel(out) > 0, "fp32 output must be [splits, rows, N]");
   const int out_splits = (int)(numel(out) / (M * N));
   KD_REQUIRE(out_splits <= total_kb, "output has %d split slices but K only has %d blocks of 64", out_splits, total_kb);
-  return gemm_bf16_skinny(px, K, pw, weight->strides[0], (int)M, (int)N, (int)K, out_splits, (float*)po, nullptr);
+  return gemm_bf16_skinny(px, K, pw, weight->strides[0], (int)M, (int)N, (int)K, out_splits, (float*)po, nullptr, 0);
 }
 
 KD_API int kd_linear_bf16_skinny_splits(int64_t N, int64_t K, int* splits_out) {

@@ -380,7 +380,8 @@ struct SkinnyParams {
   int splits, kblocks_per_split, stages;
   uint32_t tmem_cols;
   float* out_f32;         // [splits][Mb][N]
-  __nv_bfloat16* out_bf16;  // [Mb][N], only with splits == 1
+  __nv_bfloat16* out_bf16;  // [Mb][N] (or [Mb][N/2] with the SiLU*up epilogue), only with splits == 1
+  int swiglu;             // rows of W interleave 16 gate / 16 up rows: write silu(gate)*up
   int* err;
 };
 
@@ -421,6 +422,8 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();      // nothing above touches global memory
+  pdl_trigger();   // after the TMEM allocation (see common.cuh)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -476,7 +479,18 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 #pragma unroll
           for (int i = 0; i < 16; ++i) r[i] = 0u;
         }
-        if (n_ok) {
+        if (p.swiglu) {
+          // lanes 0-15 of a warp hold 16 gate rows, lanes 16-31 the matching up rows
+          const int j = (n_tile * 128 + q * 32) / 2 + (lane & 15);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float mine = __uint_as_float(r[i]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+            const int m = c0 + i;
+            if (lane < 16 && m < p.Mb && j < p.N / 2)
+              p.out_bf16[(int64_t)m * (p.N / 2) + j] = __float2bfloat16_rn(silu_f(mine) * other);
+          }
+        } else if (n_ok) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int m = c0 + i;
@@ -498,26 +512,27 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   }
 }
 
-// Picks the split-K factor for a skinny GEMM: enough CTAs to cover the SMs about twice, at least
-// two k-blocks per split.
+// Picks the split-K factor for a skinny GEMM.  One CTA streams its 128 weight rows at roughly
+// 100 GB/s, so about 40 CTAs already saturate HBM; beyond that more splits only add partial-sum
+// traffic.  Each split keeps at least 8 k-blocks (128 KB of weights).
 int gemm_skinny_auto_splits(int N, int K) {
   const int tiles = (N + 127) / 128;
   const int total_kb = (K + GEMM_BK - 1) / GEMM_BK;
-  int splits = (2 * ctx().sm_count + tiles - 1) / tiles;
-  if (splits > total_kb / 2) splits = total_kb / 2;
+  int splits = (40 + tiles - 1) / tiles;
+  if (splits > total_kb / 8) splits = total_kb / 8;
   if (splits < 1) splits = 1;
-  if (splits > 32) splits = 32;
   return splits;
 }
 
 // x [Mb<=128, K] bf16, W [N, K] bf16 -> fp32 partials [splits][Mb][N] (or bf16 [Mb][N] when
 // out_bf16 != NULL and splits == 1).
 int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int Mb, int N, int K, int splits,
-                     float* out_f32, void* out_bf16) {
+                     float* out_f32, void* out_bf16, int swiglu) {
   KD_REQUIRE(Mb >= 1 && Mb <= 128, "skinny gemm: %d rows; this path handles 1..128", Mb);
   KD_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "skinny gemm: K=%d must be a positive multiple of 8", K);
   KD_REQUIRE(splits >= 1, "skinny gemm: splits must be >= 1");
   KD_REQUIRE(out_bf16 == nullptr || splits == 1, "skinny gemm: bf16 output needs splits == 1");
+  KD_REQUIRE(!swiglu || (out_bf16 != nullptr && N % 32 == 0), "skinny gemm: the SiLU*up epilogue needs a bf16 output and N %% 32 == 0");
   SkinnyParams p{};
   p.Mb = Mb; p.N = N; p.K = K;
   p.mb_pad = (Mb + 15) / 16 * 16;
@@ -534,6 +549,7 @@ int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int
   p.tmem_cols = p.mb_pad <= 32 ? 32 : (p.mb_pad <= 64 ? 64 : 128);
   p.out_f32 = out_f32;
   p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16);
+  p.swiglu = swiglu;
   p.err = ctx().error_flag;
   CUtensorMap tw, tx;
   KD_TRY(make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, GEMM_BK));
@@ -545,7 +561,7 @@ int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int
     configured = 210 * 1024;
   }
   dim3 grid((N + 127) / 128, splits);
-  gemm_skinny_tcgen05_kernel<<<grid, GEMM_THREADS, smem, ctx().stream>>>(tw, tx, p);
+  KD_CUDA_CHECK(launch_ex(gemm_skinny_tcgen05_kernel, grid, dim3(GEMM_THREADS), (size_t)smem, tw, tx, p));
   return after_launch("gemm_skinny_tcgen05_kernel");
 }
 

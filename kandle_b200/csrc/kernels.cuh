@@ -32,7 +32,7 @@ int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
 int gemm_skinny_auto_splits(int N, int K);
 // x [Mb<=128,K] * W[N,K]^T -> fp32 partials [splits][Mb][N], or bf16 [Mb][N] when out_bf16 != NULL (splits == 1).
 int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int Mb, int N, int K, int splits,
-                     float* out_f32, void* out_bf16);
+                     float* out_f32, void* out_bf16, int swiglu);
 size_t attention_decode_scratch_bytes(int B, int Hkv, int group, int splits, int D);
 int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
                      const int* ctx_dev, int ctx_host, const int* block_table, int max_pages, int splits,

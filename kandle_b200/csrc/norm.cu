@@ -199,6 +199,8 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const void* __restrict_
                                                         int dt_o, RowIndex ridx, int64_t rows, int64_t n) {
   __shared__ float sv[THREADS / 32];
   __shared__ int64_t si[THREADS / 32];
+  pdl_wait();
+  pdl_trigger();
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const int64_t base = ridx.row_offset(row);
     float best = -3.402823466e38f;
@@ -273,6 +275,8 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const void* __restrict_
 __global__ void gather_rows_kernel(const char* __restrict__ table, const void* __restrict__ idx, int idx_dt,
                                    int64_t idx_stride, char* __restrict__ out, int64_t n_idx, int64_t table_rows,
                                    int64_t row_bytes, int64_t table_row_stride_bytes, int* __restrict__ err) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -326,7 +330,8 @@ KD_API int kd_argmax(const kd_tensor* x, const kd_tensor* out) {
   const RowIndex ridx = make_row_index(x);
   constexpr int T = 1024;
   const int64_t cap = (int64_t)ctx().sm_count * 2;
-  argmax_kernel<T><<<(int)(rows < cap ? rows : cap), T, 0, ctx().stream>>>(px, x->dtype, po, out->dtype, ridx, rows, n);
+  KD_CUDA_CHECK(launch_ex(argmax_kernel<T>, dim3((unsigned)(rows < cap ? rows : cap)), dim3(T), 0, (const void*)px, (int)x->dtype, po,
+                          (int)out->dtype, ridx, rows, n));
   return after_launch("argmax_kernel");
 }
 
@@ -349,8 +354,9 @@ KD_API int kd_index_select(const kd_tensor* self, const kd_tensor* index, int di
   int64_t blocks = (n_idx + 7) / 8;
   const int64_t cap = (int64_t)ctx().sm_count * 16;
   if (blocks > cap) blocks = cap;
-  gather_rows_kernel<<<(int)blocks, threads, 0, ctx().stream>>>(
-      (const char*)ps, pi, index->dtype, index->ndim == 1 ? index->strides[0] : 1, (char*)po, n_idx, self->shape[0],
-      self->shape[1] * esz, self->strides[0] * esz, ctx().error_flag);
+  KD_CUDA_CHECK(launch_ex(gather_rows_kernel, dim3((unsigned)blocks), dim3(threads), 0, (const char*)ps, (const void*)pi,
+                          (int)index->dtype, (int64_t)(index->ndim == 1 ? index->strides[0] : 1), (char*)po, n_idx,
+                          (int64_t)self->shape[0], (int64_t)(self->shape[1] * esz), (int64_t)(self->strides[0] * esz),
+                          ctx().error_flag));
   return after_launch("gather_rows_kernel");
 }

@@ -55,6 +55,8 @@ struct PwParams {
 
 __global__ void pointwise_strided_kernel(const void* __restrict__ a, const void* __restrict__ b, void* __restrict__ o,
                                          PwParams p) {
+  pdl_wait();
+  pdl_trigger();
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += stride) {
     int64_t lin = i, oa = 0, ob = 0, oo = 0;
@@ -93,6 +95,8 @@ template <typename T, int VEC>
 __global__ void pointwise_contig_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ o, int op,
                                         int has_b, float scalar, int64_t n_vec, int64_t n) {
   struct alignas(16) Pack { T v[VEC]; };
+  pdl_wait();
+  pdl_trigger();
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
     Pack pa = reinterpret_cast<const Pack*>(a)[i];
@@ -194,7 +198,7 @@ static int launch_pointwise(int op, const kd_tensor* a, const kd_tensor* b, floa
   KD_TRY(broadcast_strides(a, out, p.sa, "input a"));
   if (b) KD_TRY(broadcast_strides(b, out, p.sb, "input b"));
   const int threads = 256;
-  pointwise_strided_kernel<<<grid_for(n, threads), threads, 0, st>>>(pa, pb, po, p);
+  KD_CUDA_CHECK(launch_ex(pointwise_strided_kernel, dim3(grid_for(n, threads)), dim3(threads), 0, (const void*)pa, (const void*)pb, po, p));
   return after_launch("pointwise_strided_kernel");
 }
 

@@ -3,14 +3,14 @@ tcgen05 flash attention, split-KV decode attention and a CUDA-graph decode step.
 
 It computes what `Qwen3ForCausalLM.forwardWithKVCache` + greedy argmax compute on the eager path
 (packages/model-utils/src/qwen3/for_causal_lm.ts:170-194,475-508), with the ~41 backend calls per
-layer collapsed into 8 (prefill) / 10 (decode) kernels and no intermediate copies:
+layer collapsed into 8 (prefill) / 9 (decode) kernels and no intermediate copies:
 
   prefill, per layer     rms_norm -> QKV GEMM -> q/k-norm+RoPE+cache write -> flash attention ->
                          o_proj GEMM (+residual) -> rms_norm -> gate/up GEMM (SiLU*up epilogue) ->
                          down GEMM (+residual)
   decode step, per layer skinny QKV GEMM (split-K partials) -> norm+RoPE+cache write (sums the
                          partials) -> split-KV attention + combine -> skinny o_proj -> residual+rms_norm
-                         -> skinny gate/up -> SiLU*up -> skinny down -> residual+rms_norm
+                         -> skinny gate/up with SiLU*up epilogue -> skinny down -> residual+rms_norm
   The decode step reads the write position / context length from device memory, so one captured
   graph is replayed for every step.
 
@@ -91,6 +91,7 @@ class Qwen3Engine:
         self._prefill_bufs = {}
         self._decode = None
         self.pos = 0
+        self.use_pdl = True
 
     # ------------------------------------------------------------------ helpers
     def _linear(self, x, w, out, resid=None, epi=0):
@@ -182,7 +183,7 @@ class Qwen3Engine:
         last = h3.select(1, S - 1)
         core.copy_(w["last"], last)
         self._norm(w["last"], self.final_norm, w["xl"])
-        lib.call("kd_linear_bf16_skinny", _r(w["xl"]), _r(self.embed), 1, _r(w["logits"]))
+        lib.call("kd_linear_bf16_skinny", _r(w["xl"]), _r(self.embed), 0, _r(w["logits"]))
         lg = w["logits"].view(B, self.V)
         lib.call("kd_argmax", _r(lg), _r(w["tok"]))
         lg.dispose()
@@ -213,9 +214,11 @@ class Qwen3Engine:
             "B": B, "graph": None,
             "scalars": core.zeros((2,), "int32"),           # [write position, context length]
             "ids": core.zeros((B,), "int64"), "emb": e(B, self.H), "h": f(B, self.H), "h1": f(B, self.H), "x": e(B, self.H),
-            "qkv_p": f(splits(self.nqkv, self.H), B, self.nqkv), "q": e(B, 1, self.Hq, self.D),
+            # a projection whose suggested split factor is 1 writes bf16 directly, otherwise fp32 partials
+            "qkv_p": (e(B, self.nqkv) if splits(self.nqkv, self.H) == 1 else f(splits(self.nqkv, self.H), B, self.nqkv)),
+            "q": e(B, 1, self.Hq, self.D),
             "attn": e(B, 1, self.Hq, self.D), "o_p": f(splits(self.H, self.Hq * self.D), B, self.H),
-            "gu_p": f(splits(2 * self.I, self.H), B, 2 * self.I), "act": e(B, self.I),
+            "act": e(B, self.I),
             "down_p": f(splits(self.H, self.I), B, self.H), "logits": f(1, B, self.V),
             "cos": f(1, self.D // 2), "sin": f(1, self.D // 2),
         }
@@ -226,6 +229,13 @@ class Qwen3Engine:
 
     def _enqueue_decode_step(self, d: dict) -> None:
         """One decode step for d['ids'] at device position d['pos']; leaves the next ids in d['ids']."""
+        lib.call("kd_set_pdl", 1 if self.use_pdl else 0)   # every kernel below starts with a grid-dependency wait
+        try:
+            self._decode_step_kernels(d)
+        finally:
+            lib.call("kd_set_pdl", 0)
+
+    def _decode_step_kernels(self, d: dict) -> None:
         c, B = self.cfg, d["B"]
         eps = ctypes.c_float(c.rmsNormEps)
         core._kernel("index_select")(self.embed._handle, d["ids"]._handle, {"dim": 0}, d["emb"]._handle)
@@ -247,8 +257,7 @@ class Qwen3Engine:
             if self.tp > 1:
                 self._allreduce(d["o_p"])
             self._norm(d["o_p"], lw["post_norm"], d["x"], resid=h, sum_out=h1)
-            lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wgu"]), 0, _r(d["gu_p"]))
-            lib.call("kd_swiglu", _r(d["gu_p"]), _r(d["act"]))
+            lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wgu"]), 2, _r(d["act"]))   # SiLU*up in the epilogue
             lib.call("kd_linear_bf16_skinny", _r(d["act"]), _r(lw["wdown"]), 0, _r(d["down_p"]))
             if self.tp > 1:
                 self._allreduce(d["down_p"])
@@ -256,7 +265,7 @@ class Qwen3Engine:
             self._norm(d["down_p"], nxt, d["x"], resid=h1, sum_out=h)
             kc.dispose()
             vc.dispose()
-        lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(self.embed), 1, _r(d["logits"]))
+        lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(self.embed), 0, _r(d["logits"]))
         lg = d["logits"].view(B, self.V)
         lib.call("kd_argmax", _r(lg), _r(d["ids"]))
         lg.dispose()

@@ -137,6 +137,7 @@ _SIGNATURES = {
     "kd_swiglu": [_T, _T],
     "kd_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
     "kd_increment_i32": [_T, ctypes.c_int],
+    "kd_set_pdl": [ctypes.c_int],
     "kd_graph_begin": [],
     "kd_graph_end": [ctypes.POINTER(_u64)],
     "kd_graph_launch": [_u64],

@@ -51,15 +51,25 @@ def test_skinny_gemm_partials_sum_to_the_product(backend, oracle, m, n, k, split
         s = ctypes.c_int(0)
         lib.call("kd_linear_bf16_skinny_splits", ctypes.c_int64(n), ctypes.c_int64(k), ctypes.byref(s))
         splits = s.value
-        assert 1 <= splits <= k // 64
+        assert 1 <= splits <= max(1, k // 64)
     out = core.empty((splits, m, n), "float32")
     lib.call("kd_linear_bf16_skinny", _r(bf(x)), _r(bf(w)), 0, _r(out))
     got = out.dataAsync().sum(0)
     assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()
     if splits == 1:
         ob = core.empty((m, n), "bfloat16")
-        lib.call("kd_linear_bf16_skinny", _r(bf(x)), _r(bf(w)), 1, _r(ob))
+        lib.call("kd_linear_bf16_skinny", _r(bf(x)), _r(bf(w)), 0, _r(ob))
         close_bf16(ob.dataAsync(), ref)
+
+
+def test_skinny_gemm_swiglu_epilogue(backend, oracle):
+    m, K, I = 32, 1024, 3072
+    x = lib.round_to_bf16(synth.normal("x", (m, K)))
+    wg, wu = lib.round_to_bf16(synth.normal("wg", (I, K), 0.03)), lib.round_to_bf16(synth.normal("wu", (I, K), 0.03))
+    fused = np.stack([wg.reshape(I // 16, 16, K), wu.reshape(I // 16, 16, K)], 1).reshape(2 * I, K)
+    out = core.empty((m, I), "bfloat16")
+    lib.call("kd_linear_bf16_skinny", _r(bf(x)), _r(bf(fused)), 2, _r(out))
+    close_bf16(out.dataAsync(), oracle.mul(oracle.unary("silu", oracle.linear(x, wg)), oracle.linear(x, wu)))
 
 
 def test_rope_table_matches_oracle(backend, oracle):
