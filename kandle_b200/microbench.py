@@ -2,6 +2,8 @@
 
     python -m kandle_b200.microbench gemm  --m 65536 --n 4096 --k 1024 [--epilogue none|residual|swiglu]
     python -m kandle_b200.microbench attn  --b 4 --hq 16 --hkv 8 --s 2048 --d 128 [--no-causal]
+    python -m kandle_b200.microbench decode_attn --b 32 --hq 16 --hkv 8 --ctx 2176 --d 128
+    python -m kandle_b200.microbench skinny --m 32 --n 151936 --k 1024
 
 Each run prints one JSON line with the average launch time, the algorithmic work per launch and
 the achieved rate.  Inputs are seeded normal values (constant fills would flatter the power
@@ -70,6 +72,35 @@ def bench_attn(a) -> dict:
             "us": ms * 1e3, "flops": flops, "tflops": flops / ms / 1e9}
 
 
+def bench_decode_attn(a) -> dict:
+    max_s = (a.ctx + 127) // 128 * 128
+    q = _rand_bf16((a.b, a.hq, 1, a.d), 1)
+    # several cache slabs visited round-robin so that every launch streams from HBM, not from L2
+    slabs = [(_rand_bf16((a.b, a.hkv, max_s, a.d), 10 + i), _rand_bf16((a.b, a.hkv, max_s, a.d), 20 + i)) for i in range(a.slabs)]
+    out = core.empty((a.b, a.hq, 1, a.d), "bfloat16")
+    scale = ctypes.c_float(1.0 / float(np.sqrt(a.d)))
+    state = {"i": 0}
+
+    def run():
+        k, v = slabs[state["i"] % a.slabs]
+        state["i"] += 1
+        lib.call("kd_attention_decode", ctypes.byref(q._handle.c()), ctypes.byref(k._handle.c()), ctypes.byref(v._handle.c()), None,
+                 a.ctx, scale, a.splits, ctypes.byref(out._handle.c()))
+    ms = _time(run, a.iters, a.warmup)
+    nbytes = 2.0 * a.b * a.hkv * a.ctx * a.d * 2
+    return {"kernel": "flash_attention_tcgen05<decode>+combine", "b": a.b, "hq": a.hq, "hkv": a.hkv, "ctx": a.ctx, "d": a.d,
+            "splits": a.splits, "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+
+
+def bench_skinny(a) -> dict:
+    x, w = _rand_bf16((a.m, a.k), 1), _rand_bf16((a.n, a.k), 2, 0.02)
+    out = core.empty((a.m, a.n), "bfloat16")
+    args = (ctypes.byref(x._handle.c()), ctypes.byref(w._handle.c()), 0, ctypes.byref(out._handle.c()))
+    ms = _time(lambda: lib.call("kd_linear_bf16_skinny", *args), a.iters, a.warmup)
+    nbytes = 2.0 * a.n * a.k
+    return {"kernel": "gemm_skinny_tcgen05", "m": a.m, "n": a.n, "k": a.k, "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="which", required=True)
@@ -85,12 +116,24 @@ def main() -> None:
     t.add_argument("--s", type=int, default=2048)
     t.add_argument("--d", type=int, default=128)
     t.add_argument("--no-causal", action="store_true")
-    for p in (g, t):
+    dd = sub.add_parser("decode_attn")
+    dd.add_argument("--b", type=int, default=32)
+    dd.add_argument("--hq", type=int, default=16)
+    dd.add_argument("--hkv", type=int, default=8)
+    dd.add_argument("--ctx", type=int, default=2176)
+    dd.add_argument("--d", type=int, default=128)
+    dd.add_argument("--splits", type=int, default=0)
+    dd.add_argument("--slabs", type=int, default=3)
+    sk = sub.add_parser("skinny")
+    sk.add_argument("--m", type=int, default=32)
+    sk.add_argument("--n", type=int, default=151936)
+    sk.add_argument("--k", type=int, default=1024)
+    for p in (g, t, dd, sk):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     kandle_b200.init(0)
-    res = {"gemm": bench_gemm, "attn": bench_attn}[a.which](a)
+    res = {"gemm": bench_gemm, "attn": bench_attn, "decode_attn": bench_decode_attn, "skinny": bench_skinny}[a.which](a)
     print(json.dumps(res))
 
 
