@@ -103,13 +103,19 @@ __global__ void __launch_bounds__(FA_THREADS, DECODE ? 2 : 1)
 flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                const __grid_constant__ CUtensorMap tmap_v, FaParams p) {
   constexpr int SLABS = D / 64;                     // 64-wide head-dim slabs (one swizzle atom each)
-  constexpr int Q_BYTES = FA_BQ * D * 2;
+  // Decode: only the first Hq/Hkv (<= 16) rows of the query tile are real, so only 16 rows are
+  // staged; the MMA still reads 128 rows, the other 112 come from whatever follows in shared
+  // memory (the first K/V slot) and produce rows of S/O that are never looked at.
+  constexpr int QROWS = DECODE ? 16 : FA_BQ;
+  constexpr int Q_BYTES = QROWS * D * 2;
+  constexpr int Q_SLAB = QROWS * 128;
   constexpr int KV_BYTES = FA_BKV * D * 2;
   constexpr int SLAB_BYTES = FA_BKV * 128;          // 128 rows x 128 B
   // prefill: two S buffers (columns 0 and 128) + O at 256; decode: one S buffer + O at 128, one
   // smem stage per operand, so that two CTAs fit on an SM and overlap each other's latencies
   constexpr int NSBUF = DECODE ? 1 : 2;
-  constexpr int STAGES = DECODE ? 1 : FA_STAGES;
+  // K and V tiles travel through one ring in the order K0 V0 K1 V1 ...: tile t uses slot t % NSLOT
+  constexpr int NSLOT = DECODE ? 3 : 2 * FA_STAGES;
   constexpr uint32_t TMEM_COLS = DECODE ? 256 : 512;
   constexpr uint32_t S_COL0 = 0, O_COL0 = DECODE ? 128 : 256;
   constexpr uint32_t IDESC_QK = make_idesc_bf16(FA_BQ, FA_BKV, 0, 0);
@@ -118,14 +124,11 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;
-  uint8_t* k_smem = q_smem + Q_BYTES;                       // [STAGES][KV_BYTES]
-  uint8_t* v_smem = k_smem + STAGES * KV_BYTES;          // [STAGES][KV_BYTES]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + STAGES * KV_BYTES);
+  uint8_t* ring = q_smem + Q_BYTES;                         // [NSLOT][KV_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + NSLOT * KV_BYTES);
   uint64_t* q_full = bars;                 // 1
-  uint64_t* k_full = bars + 1;             // 2
-  uint64_t* k_empty = bars + 3;            // 2
-  uint64_t* v_full = bars + 5;             // 2
-  uint64_t* v_empty = bars + 7;            // 2
+  uint64_t* t_full = bars + 1;             // NSLOT (<= 4)
+  uint64_t* t_empty = bars + 5;            // NSLOT
   uint64_t* s_full = bars + 9;             // 2
   uint64_t* p_ready = bars + 11;           // 2
   uint64_t* o_done = bars + 13;            // 1
@@ -170,10 +173,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-    }
+    for (int s = 0; s < NSLOT; ++s) { mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], 1); }
     for (int s = 0; s < NSBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4); }
     mbar_init(o_done, 1);
     *abort_flag = 0;
@@ -196,9 +196,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-      for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * SLAB_BYTES, &tmap_q, q_full, s * 64, q0, h, b);
-      int stage = 0;
-      uint32_t phase = 0;
+      for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * Q_SLAB, &tmap_q, q_full, s * 64, q0, h, b);
       for (int jj = 0; jj < n_blocks; ++jj) {
         // key-tile coordinates: rows j*128.. of sequence b, or row 0 of the page the block table names
         int row = (j_begin + jj) * FA_BKV, outer = b;
@@ -206,17 +204,18 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
           outer = p.block_table[(int64_t)b * p.max_pages + (j_begin + jj)];
           row = 0;
         }
-        if (!mbar_wait(&k_empty[stage], phase ^ 1, abort_flag, p.err, 301)) break;
-        mbar_arrive_expect_tx(&k_full[stage], KV_BYTES);
+        const int tk = 2 * jj, tv = 2 * jj + 1;
+        const int sk = tk % NSLOT, sv = tv % NSLOT;
+        if (!mbar_wait(&t_empty[sk], (uint32_t)(((tk / NSLOT) & 1) ^ 1), abort_flag, p.err, 301)) break;
+        mbar_arrive_expect_tx(&t_full[sk], KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(k_smem + stage * KV_BYTES + s * SLAB_BYTES, &tmap_k, &k_full[stage], s * 64, row, hk, outer);
-        if (!mbar_wait(&v_empty[stage], phase ^ 1, abort_flag, p.err, 302)) break;
-        mbar_arrive_expect_tx(&v_full[stage], KV_BYTES);
+          tma_load_4d(ring + sk * KV_BYTES + s * SLAB_BYTES, &tmap_k, &t_full[sk], s * 64, row, hk, outer);
+        if (!mbar_wait(&t_empty[sv], (uint32_t)(((tv / NSLOT) & 1) ^ 1), abort_flag, p.err, 302)) break;
+        mbar_arrive_expect_tx(&t_full[sv], KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(v_smem + stage * KV_BYTES + s * SLAB_BYTES, &tmap_v, &v_full[stage], s * 64, row, hk, outer);
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          tma_load_4d(ring + sv * KV_BYTES + s * SLAB_BYTES, &tmap_v, &t_full[sv], s * 64, row, hk, outer);
       }
     }
   } else if (warp == 1) {
@@ -225,18 +224,19 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       const uint32_t q_addr = smem_u32(q_smem);
       // S(j) = Q K(j)^T into S buffer j % NSBUF   (j counts this CTA's key tiles from 0)
       auto issue_qk = [&](int j) -> bool {
-        const int stage = j % STAGES;
-        if (!mbar_wait(&k_full[stage], (uint32_t)((j / STAGES) & 1), abort_flag, p.err, 304)) return false;
+        const int t = 2 * j, stage = t % NSLOT;
+        if (!mbar_wait(&t_full[stage], (uint32_t)((t / NSLOT) & 1), abort_flag, p.err, 304)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(k_smem + stage * KV_BYTES);
+        const uint32_t k_addr = smem_u32(ring + stage * KV_BYTES);
         const uint32_t d_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (uint32_t)((k / 4) * SLAB_BYTES + (k % 4) * 32);
-          umma_ss(d_tmem, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
+          const uint32_t qoff = (uint32_t)((k / 4) * Q_SLAB + (k % 4) * 32);
+          const uint32_t koff = (uint32_t)((k / 4) * SLAB_BYTES + (k % 4) * 32);
+          umma_ss(d_tmem, make_smem_desc_sw128(q_addr + qoff, 16, 1024), make_smem_desc_sw128(k_addr + koff, 16, 1024),
                   IDESC_QK, k != 0 ? 1u : 0u);
         }
-        umma_commit(&k_empty[stage]);
+        umma_commit(&t_empty[stage]);
         umma_commit(&s_full[j % NSBUF]);
         return true;
       };
@@ -246,11 +246,11 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         if (NSBUF == 2 && j + 1 < n_blocks) {
           if (!issue_qk(j + 1)) break;
         }
-        const int stage = j % STAGES;
+        const int t = 2 * j + 1, stage = t % NSLOT;
         if (!mbar_wait(&p_ready[j % NSBUF], (uint32_t)((j / NSBUF) & 1), abort_flag, p.err, 305)) break;
-        if (!mbar_wait(&v_full[stage], (uint32_t)((j / STAGES) & 1), abort_flag, p.err, 306)) break;
+        if (!mbar_wait(&t_full[stage], (uint32_t)((t / NSLOT) & 1), abort_flag, p.err, 306)) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_smem + stage * KV_BYTES);
+        const uint32_t v_addr = smem_u32(ring + stage * KV_BYTES);
         const uint32_t p_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
         const uint32_t o_tmem = tmem_base + O_COL0;
 #pragma unroll
@@ -259,7 +259,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
           const uint64_t vdesc = make_smem_desc_sw128(v_addr + (uint32_t)(k * 2048), SLAB_BYTES, 1024);
           umma_ts(o_tmem, p_tmem + (uint32_t)(k * 8), vdesc, IDESC_PV, (j | k) != 0 ? 1u : 0u);
         }
-        umma_commit(&v_empty[stage]);
+        umma_commit(&t_empty[stage]);
         umma_commit(o_done);
         // one S buffer: the next QK^T overwrites P, so it is issued after PV (in-order pipe)
         if (NSBUF == 1 && j + 1 < n_blocks) {
@@ -309,8 +309,8 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       // Lazy rescale: keep the stale max unless it is more than 2^8 too small.
       float alpha = 1.f;
       bool rescale = false;
-      if (j == 0) {
-        m_used = m_blk;
+      if (j == 0 || (DECODE && row_in_tile >= p.group)) {
+        m_used = m_blk;   // first block; or a padding row of the decode tile, whose values nobody reads
       } else if (m_blk - m_used > 8.0f) {
         alpha = fast_exp2(m_used - m_blk);
         m_used = m_blk;
@@ -422,8 +422,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 
 template <int D, bool DECODE>
 static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid) {
-  constexpr int STAGES = DECODE ? 1 : FA_STAGES;
-  constexpr int SMEM = FA_BQ * D * 2 + 2 * STAGES * FA_BKV * D * 2 + 1024 + 256;
+  constexpr int SMEM = (DECODE ? 16 : FA_BQ) * D * 2 + (DECODE ? 3 : 2 * FA_STAGES) * FA_BKV * D * 2 + 1024 + 256;
   static bool configured = false;
   if (!configured) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(flash_attention_tcgen05_kernel<D, DECODE>,
@@ -535,7 +534,7 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   const int Hkv = (int)k->shape[1];
   KD_REQUIRE(q->shape[2] == 1 && out->shape[2] == 1, "attention_decode: exactly one query position per sequence");
   KD_REQUIRE(D == 64 || D == 128, "attention_decode: head_dim must be 64 or 128");
-  KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 128, "attention_decode: bad head counts %d / %d", Hq, Hkv);
+  KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 16, "attention_decode: %d query heads per KV head; this kernel stages at most 16", Hkv > 0 ? Hq / Hkv : 0);
   KD_REQUIRE(v->shape[1] == Hkv && v->shape[2] == k->shape[2] && v->shape[3] == D && k->shape[3] == D,
              "attention_decode: K and V cache shapes differ");
   KD_REQUIRE(scale > 0.f, "attention_decode: scale must be positive");
@@ -569,7 +568,7 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   const int64_t sq[3] = {q->strides[0], q->strides[1] * group, q->strides[1]};
   const int64_t ek[4] = {k->shape[0], Hkv, k->shape[2], D};
   CUtensorMap tq, tk, tv;
-  KD_TRY(make_tmap_bhsd(&tq, pq, eq, sq, FA_BQ));
+  KD_TRY(make_tmap_bhsd(&tq, pq, eq, sq, 16));
   KD_TRY(make_tmap_bhsd(&tk, pk, ek, k->strides, FA_BKV));
   KD_TRY(make_tmap_bhsd(&tv, pv, ek, v->strides, FA_BKV));
   FaParams p{};

@@ -545,6 +545,12 @@ int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int
   int stages = (200 * 1024) / stage_bytes;
   if (stages > 10) stages = 10;
   if (stages > p.kblocks_per_split) stages = p.kblocks_per_split < 2 ? 2 : p.kblocks_per_split;
+  // many tiles (lm_head): a shallower ring lets two CTAs share an SM, so that one CTA's prologue and
+  // epilogue overlap the other's streaming
+  if ((int64_t)((N + 127) / 128) * splits >= 2 * ctx().sm_count) {
+    const int two_per_sm = (108 * 1024) / stage_bytes;
+    if (stages > two_per_sm) stages = two_per_sm;
+  }
   p.stages = stages;
   p.tmem_cols = p.mb_pad <= 32 ? 32 : (p.mb_pad <= 64 ? 64 : 128);
   p.out_f32 = out_f32;
