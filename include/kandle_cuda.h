@@ -224,6 +224,13 @@ int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_norm_we
                                 const kd_tensor* k_norm_weight, float eps, const kd_tensor* cos,
                                 const kd_tensor* sin, const kd_tensor* k_cache, const kd_tensor* v_cache,
                                 const kd_tensor* pos, int start_pos, const kd_tensor* q_out);
+/* The QKV projection and kd_qkv_norm_rope_cachewrite in one tensor-core GEMM whose epilogue does the
+ * q/k-norm, RoPE and KV-cache write (head_dim 128, prefill): x bf16 [B*S,K], wqkv bf16 [(Hq+2Hkv)*128,K]
+ * (q rows, k rows, v rows). */
+int kd_qkv_linear_norm_rope_cachewrite(const kd_tensor* x, const kd_tensor* wqkv, const kd_tensor* q_norm_weight,
+                                       const kd_tensor* k_norm_weight, float eps, const kd_tensor* cos,
+                                       const kd_tensor* sin, const kd_tensor* k_cache, const kd_tensor* v_cache,
+                                       int start_pos, const kd_tensor* q_out);
 /* silu(gate) * up (packages/model-utils/src/mlp/swiglu.ts:121-131) from a bf16 [rows,2I] matrix or
  * fp32 partials [splits,rows,2I] whose columns interleave 16 gate / 16 up values. */
 int kd_swiglu(const kd_tensor* gate_up, const kd_tensor* out);

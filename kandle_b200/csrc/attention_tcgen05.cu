@@ -91,6 +91,7 @@ struct FaParams {
   int group;                   // query heads per KV head (valid rows of the tile)
   float* part_o;               // [B, Hkv, splits, group, D] un-normalised partial outputs
   float* part_ml;              // [B, Hkv, splits, group, 2] (running max in the log2 domain, sum)
+  int direct;                  // splits == 1: write O/l as bf16 straight to `o` (no combine kernel)
 };
 
 constexpr int FA_BQ = 128;
@@ -362,7 +363,32 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     }
     if (ok) {
       tc_fence_after();
-      if (DECODE) {
+      if (DECODE && p.direct) {
+        // a single split holds the whole key range: normalise and store the real rows directly
+        const bool valid = row_in_tile < p.group;
+        const float inv_l = 1.0f / l;
+        __nv_bfloat16* orow = p.o + (int64_t)b * p.so_b + (int64_t)(hk * p.group + row_in_tile) * p.so_h;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orr[32];
+          tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
+          tmem_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 v;
+              uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(orr[g * 8 + 2 * e]) * inv_l,
+                                                         __uint_as_float(orr[g * 8 + 2 * e + 1]) * inv_l);
+                vv[e] = *reinterpret_cast<uint32_t*>(&t);
+              }
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+            }
+          }
+        }
+      } else if (DECODE) {
         // un-normalised partial output + statistics; only the first `group` rows are real queries
         const int64_t slot = (((int64_t)b * p.Hkv + hk) * p.splits + blockIdx.x) * p.group + row_in_tile;
         const bool valid = row_in_tile < p.group;
@@ -583,9 +609,14 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   p.group = group;
   p.part_o = static_cast<float*>(scratch);
   p.part_ml = p.part_o + (size_t)B * Hkv * splits * group * D;
+  // one split and a 16-byte aligned output: the attention kernel writes the result itself
+  p.direct = (splits == 1 && (reinterpret_cast<uintptr_t>(po) & 15) == 0 && out->strides[0] % 8 == 0 && out->strides[1] % 8 == 0) ? 1 : 0;
+  p.o = static_cast<__nv_bfloat16*>(po);
+  p.so_b = out->strides[0]; p.so_h = out->strides[1]; p.so_s = out->strides[2];
   dim3 grid(splits, Hkv, B);
   if (D == 128) KD_TRY((launch_fa<128, true>(tq, tk, tv, p, grid)));
   else KD_TRY((launch_fa<64, true>(tq, tk, tv, p, grid)));
+  if (p.direct) return KD_OK;
   const int warps = B * Hq;
   KD_CUDA_CHECK(launch_ex(decode_combine_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, (const float*)p.part_o,
                           (const float*)p.part_ml, static_cast<__nv_bfloat16*>(po), (int64_t)out->strides[0],

@@ -123,3 +123,53 @@ KD_API int kd_attention_decode_noalloc(const kd_tensor* q, const kd_tensor* k_ca
   }
   return attention_decode_static(q, k_cache, v_cache, out, scale, ctx_dev, ctx_len_host, splits);
 }
+
+KD_API int kd_qkv_linear_norm_rope_cachewrite(const kd_tensor* x, const kd_tensor* wqkv, const kd_tensor* q_norm_weight,
+                                              const kd_tensor* k_norm_weight, float eps, const kd_tensor* cos,
+                                              const kd_tensor* sin, const kd_tensor* k_cache, const kd_tensor* v_cache,
+                                              int start_pos, const kd_tensor* q_out) {
+  KD_TRY(require_init());
+  KD_REQUIRE(x && wqkv && q_norm_weight && k_norm_weight && cos && sin && k_cache && v_cache && q_out, "null tensor");
+  KD_REQUIRE(q_out->ndim == 4 && q_out->dtype == KD_BF16 && is_contiguous(q_out), "q_out must be contiguous bf16 [B,S,Hq,D]");
+  const int B = (int)q_out->shape[0], S = (int)q_out->shape[1], Hq = (int)q_out->shape[2], D = (int)q_out->shape[3];
+  KD_REQUIRE(D == 128, "the fused QKV projection handles head_dim 128 (use kd_linear_bf16 + kd_qkv_norm_rope_cachewrite otherwise)");
+  KD_REQUIRE(k_cache->ndim == 4 && k_cache->dtype == KD_BF16 && v_cache->dtype == KD_BF16 && k_cache->shape[0] == B &&
+                 k_cache->shape[3] == D && k_cache->strides[3] == 1,
+             "caches must be bf16 [B,Hkv,maxS,128] with unit head_dim stride");
+  const int Hkv = (int)k_cache->shape[1];
+  for (int i = 0; i < 4; ++i)
+    KD_REQUIRE(v_cache->shape[i] == k_cache->shape[i] && v_cache->strides[i] == k_cache->strides[i],
+               "v_cache must have k_cache's shape and strides");
+  for (int i = 0; i < 3; ++i) KD_REQUIRE(k_cache->strides[i] % 8 == 0, "cache strides must be multiples of 8 elements");
+  KD_REQUIRE(start_pos >= 0 && start_pos + S <= k_cache->shape[2],
+             "Cache overflow: trying to write to position %d-%d, but maxSeqLen is %lld", start_pos, start_pos + S,
+             (long long)k_cache->shape[2]);
+  const int64_t tokens = (int64_t)B * S, N = (int64_t)(Hq + 2 * Hkv) * D;
+  KD_REQUIRE(x->dtype == KD_BF16 && is_contiguous(x) && x->ndim >= 1 && numel(x) % tokens == 0, "x must be contiguous bf16 [B*S, K]");
+  const int64_t K = numel(x) / tokens;
+  KD_REQUIRE(wqkv->dtype == KD_BF16 && wqkv->ndim == 2 && wqkv->shape[0] == N && wqkv->shape[1] == K && wqkv->strides[1] == 1,
+             "wqkv must be bf16 [(Hq+2Hkv)*128, K]");
+  KD_REQUIRE(q_norm_weight->dtype == KD_BF16 && k_norm_weight->dtype == KD_BF16 && numel(q_norm_weight) == D &&
+                 numel(k_norm_weight) == D && is_contiguous(q_norm_weight) && is_contiguous(k_norm_weight),
+             "q/k norm weights must be contiguous bf16 [128]");
+  KD_REQUIRE(cos->dtype == KD_F32 && sin->dtype == KD_F32 && is_contiguous(cos) && is_contiguous(sin) &&
+                 numel(cos) == (int64_t)S * 64 && numel(sin) == (int64_t)S * 64,
+             "cos/sin must be contiguous fp32 [S, 64]");
+  if (tokens == 0) return KD_OK;
+  void *px, *pw, *pqw, *pkw, *pc, *ps, *pkc, *pvc, *pq;
+  KD_TRY(tensor_ptr(x, &px));
+  KD_TRY(tensor_ptr(wqkv, &pw));
+  KD_TRY(tensor_ptr(q_norm_weight, &pqw));
+  KD_TRY(tensor_ptr(k_norm_weight, &pkw));
+  KD_TRY(tensor_ptr(cos, &pc));
+  KD_TRY(tensor_ptr(sin, &ps));
+  KD_TRY(tensor_ptr(k_cache, &pkc));
+  KD_TRY(tensor_ptr(v_cache, &pvc));
+  KD_TRY(tensor_ptr(q_out, &pq));
+  const uintptr_t all = reinterpret_cast<uintptr_t>(pqw) | reinterpret_cast<uintptr_t>(pkw) | reinterpret_cast<uintptr_t>(pc) |
+                        reinterpret_cast<uintptr_t>(ps) | reinterpret_cast<uintptr_t>(pkc) | reinterpret_cast<uintptr_t>(pvc) |
+                        reinterpret_cast<uintptr_t>(pq);
+  KD_REQUIRE((all & 15) == 0, "operands must be 16-byte aligned");
+  return gemm_bf16_qkv_rope(px, K, pw, wqkv->strides[0], (int)tokens, (int)K, S, Hq, Hkv, start_pos, eps, (const float*)pc,
+                            (const float*)ps, pqw, pkw, pq, pkc, pvc, k_cache->strides[0], k_cache->strides[1], k_cache->strides[2]);
+}

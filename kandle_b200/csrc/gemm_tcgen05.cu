@@ -90,6 +90,18 @@ struct GemmParams {
   int epi;
   int num_m_tiles, num_n_tiles;
   int* err;
+  // epi == 3: the columns are (Hq + 2 Hkv) heads of 128; q/k heads get RMSNorm over the head + RoPE,
+  // q goes to q_out [tokens, Hq, 128], k/v rows to the KV cache at position pos0 + (token % S)
+  int S, Hq, Hkv, pos0;
+  float eps;
+  const float* cos_t;
+  const float* sin_t;
+  const __nv_bfloat16* qw;
+  const __nv_bfloat16* kw;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  int64_t kc_b, kc_h, kc_s;
 };
 
 constexpr int GEMM_BM = 128;
@@ -207,7 +219,66 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int row = m_tile * GEMM_BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N);
-      if (p.epi == 2) {
+      if (BLOCK_N == 256 && p.epi == 3) {
+        // q/k-norm + RoPE + cache write (see fused.cu for the stand-alone kernel and the reference
+        // operators it replaces).  A thread owns one token row; a head is 128 consecutive columns,
+        // so the norm and both members of every rotation pair (i, i+64) are thread-local.
+        const int b_idx = row / p.S, s_idx = row - b_idx * p.S;
+#pragma unroll 1
+        for (int hd = 0; hd < BLOCK_N / 128; ++hd) {
+          uint32_t x[128];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_row + hd * 128 + c * 32, &x[c * 32]);
+          tmem_wait_ld();
+          const int head = n_tile * (BLOCK_N / 128) + hd;
+          if (!row_ok || head >= p.Hq + 2 * p.Hkv) continue;
+          const bool is_q = head < p.Hq, is_k = !is_q && head < p.Hq + p.Hkv;
+          if (is_q || is_k) {
+            float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 128; i += 2) {
+              ss0 = fmaf(__uint_as_float(x[i]), __uint_as_float(x[i]), ss0);
+              ss1 = fmaf(__uint_as_float(x[i + 1]), __uint_as_float(x[i + 1]), ss1);
+            }
+            const float sc = 1.0f / sqrtf((ss0 + ss1) * (1.0f / 128.0f) + p.eps);
+            const __nv_bfloat16* w = is_q ? p.qw : p.kw;
+            const float4* cr = reinterpret_cast<const float4*>(p.cos_t + (int64_t)s_idx * 64);
+            const float4* sr = reinterpret_cast<const float4*>(p.sin_t + (int64_t)s_idx * 64);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {   // 8 rotation pairs per step
+              const uint4 wa = reinterpret_cast<const uint4*>(w)[g], wb = reinterpret_cast<const uint4*>(w + 64)[g];
+              const uint32_t* wau = reinterpret_cast<const uint32_t*>(&wa);
+              const uint32_t* wbu = reinterpret_cast<const uint32_t*>(&wb);
+              const float4 c0 = cr[2 * g], c1 = cr[2 * g + 1], s0 = sr[2 * g], s1 = sr[2 * g + 1];
+              const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+              const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int i = g * 8 + e;
+                const float w1 = (e & 1) ? bf16_hi(wau[e >> 1]) : bf16_lo(wau[e >> 1]);
+                const float w2 = (e & 1) ? bf16_hi(wbu[e >> 1]) : bf16_lo(wbu[e >> 1]);
+                const float y1 = (__uint_as_float(x[i]) * sc) * w1;
+                const float y2 = (__uint_as_float(x[i + 64]) * sc) * w2;
+                x[i] = __float_as_uint(y1 * cc[e] - y2 * sn[e]);
+                x[i + 64] = __float_as_uint(y2 * cc[e] + y1 * sn[e]);
+              }
+            }
+          }
+          __nv_bfloat16* dst;
+          if (is_q) {
+            dst = p.q_out + ((int64_t)row * p.Hq + head) * 128;
+          } else {
+            const int hk = is_k ? head - p.Hq : head - p.Hq - p.Hkv;
+            dst = (is_k ? p.k_cache : p.v_cache) + (int64_t)b_idx * p.kc_b + (int64_t)hk * p.kc_h + (int64_t)(p.pos0 + s_idx) * p.kc_s;
+          }
+#pragma unroll
+          for (int g = 0; g < 16; ++g)
+            reinterpret_cast<uint4*>(dst)[g] = make_uint4(pack_bf16(__uint_as_float(x[g * 8 + 0]), __uint_as_float(x[g * 8 + 1])),
+                                                          pack_bf16(__uint_as_float(x[g * 8 + 2]), __uint_as_float(x[g * 8 + 3])),
+                                                          pack_bf16(__uint_as_float(x[g * 8 + 4]), __uint_as_float(x[g * 8 + 5])),
+                                                          pack_bf16(__uint_as_float(x[g * 8 + 6]), __uint_as_float(x[g * 8 + 7])));
+        }
+      } else if (p.epi == 2) {
         // SiLU(gate) * up.  Weight rows interleave 16 gate rows with the 16 matching up rows, so each
         // 32-column chunk of the accumulator holds 16 (gate, up) pairs and yields 16 outputs.
         __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + (int64_t)n_tile * (BLOCK_N / 2);
@@ -358,6 +429,28 @@ int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out,
   }
   KD_TRY(make_tmap_bf16_2d(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 64, GEMM_BK));
   return launch_gemm<64, 8>(ta, tb, p);
+}
+
+// QKV projection with the q/k-norm + RoPE + KV-cache write done in the epilogue (head_dim 128).
+int gemm_bf16_qkv_rope(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int K, int S, int Hq, int Hkv, int pos0,
+                       float eps, const float* cos_t, const float* sin_t, const void* qw, const void* kw, void* q_out,
+                       void* k_cache, void* v_cache, int64_t kc_b, int64_t kc_h, int64_t kc_s) {
+  KD_REQUIRE(M > 0 && K > 0 && K % 8 == 0, "qkv gemm: K=%d must be a positive multiple of 8", K);
+  const int N = (Hq + 2 * Hkv) * 128;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.epi = 3;
+  p.err = ctx().error_flag;
+  p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.pos0 = pos0; p.eps = eps;
+  p.cos_t = cos_t; p.sin_t = sin_t;
+  p.qw = static_cast<const __nv_bfloat16*>(qw); p.kw = static_cast<const __nv_bfloat16*>(kw);
+  p.q_out = static_cast<__nv_bfloat16*>(q_out);
+  p.k_cache = static_cast<__nv_bfloat16*>(k_cache); p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+  p.kc_b = kc_b; p.kc_h = kc_h; p.kc_s = kc_s;
+  CUtensorMap ta, tb;
+  KD_TRY(make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GEMM_BM, GEMM_BK));
+  KD_TRY(make_tmap_bf16_2d(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 256, GEMM_BK));
+  return launch_gemm<256, 4>(ta, tb, p);
 }
 
 // ----------------------------------------------------------------------------- skinny (decode) GEMM

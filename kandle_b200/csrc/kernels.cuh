@@ -29,6 +29,9 @@ int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out,
 int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out,
                      const AttnParams& p, int* handled);
 
+int gemm_bf16_qkv_rope(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int K, int S, int Hq, int Hkv, int pos0,
+                       float eps, const float* cos_t, const float* sin_t, const void* qw, const void* kw, void* q_out,
+                       void* k_cache, void* v_cache, int64_t kc_b, int64_t kc_h, int64_t kc_s);
 int gemm_skinny_auto_splits(int N, int K);
 // x [Mb<=128,K] * W[N,K]^T -> fp32 partials [splits][Mb][N], or bf16 [Mb][N] when out_bf16 != NULL (splits == 1).
 int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int Mb, int N, int K, int splits,

@@ -3,9 +3,9 @@ tcgen05 flash attention, split-KV decode attention and a CUDA-graph decode step.
 
 It computes what `Qwen3ForCausalLM.forwardWithKVCache` + greedy argmax compute on the eager path
 (packages/model-utils/src/qwen3/for_causal_lm.ts:170-194,475-508), with the ~41 backend calls per
-layer collapsed into 8 (prefill) / 9 (decode) kernels and no intermediate copies:
+layer collapsed into 7 (prefill) / 9 (decode) kernels and no intermediate copies:
 
-  prefill, per layer     rms_norm -> QKV GEMM -> q/k-norm+RoPE+cache write -> flash attention ->
+  prefill, per layer     rms_norm -> QKV GEMM (epilogue: q/k-norm+RoPE+cache write) -> flash attention ->
                          o_proj GEMM (+residual) -> rms_norm -> gate/up GEMM (SiLU*up epilogue) ->
                          down GEMM (+residual)
   decode step, per layer skinny QKV GEMM (split-K partials) -> norm+RoPE+cache write (sums the
@@ -155,9 +155,14 @@ class Qwen3Engine:
             vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
             if self.tp == 1 or li == 0:
                 self._norm(h, lw["in_norm"], w["x"])     # (tensor parallel: later layers get x from the fused add+norm)
-            self._linear(w["x"], lw["wqkv"], w["qkv"])
-            lib.call("kd_qkv_norm_rope_cachewrite", _r(w["qkv"]), _r(lw["q_norm"]), _r(lw["k_norm"]),
-                     ctypes.c_float(c.rmsNormEps), _r(w["cos"]), _r(w["sin"]), _r(kc), _r(vc), None, 0, _r(w["q"]))
+            if self.D == 128:
+                # QKV GEMM whose epilogue does q/k-norm + RoPE + the KV-cache write
+                lib.call("kd_qkv_linear_norm_rope_cachewrite", _r(w["x"]), _r(lw["wqkv"]), _r(lw["q_norm"]), _r(lw["k_norm"]),
+                         ctypes.c_float(c.rmsNormEps), _r(w["cos"]), _r(w["sin"]), _r(kc), _r(vc), 0, _r(w["q"]))
+            else:
+                self._linear(w["x"], lw["wqkv"], w["qkv"])
+                lib.call("kd_qkv_norm_rope_cachewrite", _r(w["qkv"]), _r(lw["q_norm"]), _r(lw["k_norm"]),
+                         ctypes.c_float(c.rmsNormEps), _r(w["cos"]), _r(w["sin"]), _r(kc), _r(vc), None, 0, _r(w["q"]))
             kp, vp = kc.slice(f":, :, :{S}, :"), vc.slice(f":, :, :{S}, :")
             lib.call("kd_flash_attention", _r(q_bhsd), _r(kp), _r(vp), _r(o_bhsd), ctypes.c_float(self.scale), 1)
             if self.tp == 1:

@@ -134,6 +134,7 @@ _SIGNATURES = {
     "kd_linear_bf16_skinny_splits": [ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)],
     "kd_rope_table": [_T, _T, ctypes.c_int, ctypes.c_int, _T, _T],
     "kd_qkv_norm_rope_cachewrite": [_T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, ctypes.c_int, _T],
+    "kd_qkv_linear_norm_rope_cachewrite": [_T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, ctypes.c_int, _T],
     "kd_swiglu": [_T, _T],
     "kd_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
     "kd_increment_i32": [_T, ctypes.c_int],

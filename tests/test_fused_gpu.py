@@ -200,3 +200,41 @@ def test_graph_capture_replays_with_device_side_state(backend):
         lib.call("kd_graph_launch", g)
     assert s.dataAsync()[0] == 6 + 3 * 5 and backend.launch_count() - n0 >= 6
     lib.call("kd_graph_destroy", g)
+
+
+def test_qkv_gemm_with_fused_norm_rope_cachewrite_matches_the_two_kernel_path(backend, oracle):
+    """kd_qkv_linear_norm_rope_cachewrite == kd_linear_bf16 followed by kd_qkv_norm_rope_cachewrite,
+    and both follow the oracle's unfused sequence."""
+    B, S, Hq, Hkv, K, max_s, pos0 = 2, 150, 4, 2, 256, 192, 7
+    d, n = 128, (4 + 2 * 2) * 128
+    x = lib.round_to_bf16(synth.normal("x", (B * S, K)))
+    w = lib.round_to_bf16(synth.normal("w", (n, K), 0.06))
+    qw, kw = lib.round_to_bf16(synth.normal("qw", (d,), 0.1, 1.0)), lib.round_to_bf16(synth.normal("kw", (d,), 0.1, 1.0))
+    cos_t, sin_t = core.empty((S, 64), "float32"), core.empty((S, 64), "float32")
+    lib.call("kd_rope_table", _r(f32(oracle.rope_inv_freq(d, 1e6))), None, pos0, S, _r(cos_t), _r(sin_t))
+    tx, tw, tqw, tkw = bf(x), bf(w), bf(qw), bf(kw)
+    outs = []
+    for fused in (True, False):
+        kc, vc = core.zeros((B, Hkv, max_s, d), "bfloat16"), core.zeros((B, Hkv, max_s, d), "bfloat16")
+        q_out = core.empty((B, S, Hq, d), "bfloat16")
+        if fused:
+            lib.call("kd_qkv_linear_norm_rope_cachewrite", _r(tx), _r(tw), _r(tqw), _r(tkw), ctypes.c_float(1e-6), _r(cos_t), _r(sin_t),
+                     _r(kc), _r(vc), pos0, _r(q_out))
+        else:
+            qkv = core.empty((B, S, n), "bfloat16")
+            lib.call("kd_linear_bf16", _r(tx), _r(tw), None, 0, _r(qkv))
+            lib.call("kd_qkv_norm_rope_cachewrite", _r(qkv), _r(tqw), _r(tkw), ctypes.c_float(1e-6), _r(cos_t), _r(sin_t), _r(kc), _r(vc),
+                     None, pos0, _r(q_out))
+        outs.append((q_out.dataAsync(), kc.dataAsync(), vc.dataAsync()))
+    qkv_ref = oracle.linear(x, w).reshape(B, S, n)
+    cos, sin = oracle.rope_tables(np.arange(pos0, pos0 + S, dtype=np.int32), d, 1e6)
+    q = oracle.apply_rope(oracle.rms_norm(qkv_ref[..., :Hq * d].reshape(B, S, Hq, d), qw, 1e-6).transpose(0, 2, 1, 3), cos, sin)
+    k = oracle.apply_rope(oracle.rms_norm(qkv_ref[..., Hq * d:(Hq + Hkv) * d].reshape(B, S, Hkv, d), kw, 1e-6).transpose(0, 2, 1, 3), cos, sin)
+    v = qkv_ref[..., (Hq + Hkv) * d:].reshape(B, S, Hkv, d).transpose(0, 2, 1, 3)
+    for q_got, k_got, v_got in outs:
+        close_bf16(q_got, q.transpose(0, 2, 1, 3), 6e-3)
+        close_bf16(k_got[:, :, pos0:pos0 + S], k, 6e-3)
+        close_bf16(v_got[:, :, pos0:pos0 + S], v, 6e-3)
+        assert not k_got[:, :, :pos0].any() and not k_got[:, :, pos0 + S:].any()      # nothing written outside [pos0, pos0+S)
+    # the fused epilogue skips one bf16 rounding (of the projection), so the two paths agree to bf16 precision
+    assert np.abs(outs[0][0] - outs[1][0]).max() <= 0.05 * np.abs(outs[1][0]).max()
