@@ -334,7 +334,10 @@ def run_ours(a) -> None:
         alg_bytes = 2.0 * B * (dims["kv_heads"] // tp_size) * ctx_mean * dims["head_dim"] * 2
         ach = alg_bytes / (us * 1e-6) / 1e9
         roofline = {"kernel": "flash_attention_tcgen05_kernel<decode> + decode_combine_kernel", "bound": "hbm", "achieved": ach,
-                    "peak": hbm_peak, "peak_source": hbm_src, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
+                    "peak": hbm_peak, "peak_source": hbm_src, "unit": "GB/s", "frac": ach / hbm_peak,
+                    # dram__bytes_read+write of one ncu capture at B=32, Hkv=8, ctx=2176 (290.1 MB for 285.2 MB
+                    # algorithmic); traffic is proportional to the keys read, so other shapes are scaled
+                    "traffic": alg_bytes * (290.1e6 / 285.212672e6),
                     "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": us, "context": ctx_mean}
     # prefill GEMM + attention, timed alone on the prefill buffers
     w = eng._bufs(B, S)
