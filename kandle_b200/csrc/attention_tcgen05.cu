@@ -4,13 +4,14 @@
 // (packages/backend-webgpu/src/kernels/attention/builder.ts:138-329: GQA head map, score =
 // dot*scale, causal mask top-left aligned, online softmax, O/l), re-tiled for sm_100a:
 //
-//   CTA = one 128-row query tile of one (batch, q-head); 192 threads.
+//   CTA = one 128-row query tile of one (batch, q-head); 320 threads (192 in decode mode).
 //   warp 0     TMA producer: Q tile once, then 128-row K and V tiles through a 2-stage ring
 //              (plain tiled loads with 128-byte swizzle, one 64-wide head-dim slab per load).
 //   warp 1     one elected thread issues tcgen05.mma:
 //                S = Q K^T   (A = Q in smem, K-major; B = K tile, K-major; fp32 S in TMEM, 2 buffers)
 //                O += P V    (A = P read from TMEM as packed bf16; B = V tile, MN-major)
-//   warps 2-5  softmax: each thread owns one query row; tcgen05.ld the S row, scale, mask,
+//   warps 2-9  softmax, two warpgroups that split the key columns of every row (decode: one
+//              warpgroup); each thread: tcgen05.ld its part of the S row, scale, mask,
 //              running max / sum in registers (exp2 with the scale folded in), write P back into
 //              the S buffer as packed bf16 (tcgen05.st), rescale O in TMEM only when the running
 //              max grew by more than 2^8 (the accumulated sum uses the same stale max, so the
@@ -96,11 +97,12 @@ struct FaParams {
 
 constexpr int FA_BQ = 128;
 constexpr int FA_BKV = 128;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 192;           // decode: TMA warp, MMA warp, one softmax warpgroup
+constexpr int FA_THREADS_PREFILL = 320;   // prefill: two softmax warpgroups
 constexpr int FA_STAGES = 2;
 
 template <int D, bool DECODE>
-__global__ void __launch_bounds__(FA_THREADS, DECODE ? 2 : 1)
+__global__ void __launch_bounds__(DECODE ? FA_THREADS : FA_THREADS_PREFILL, DECODE ? 2 : 1)
 flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                const __grid_constant__ CUtensorMap tmap_v, FaParams p) {
   constexpr int SLABS = D / 64;                     // 64-wide head-dim slabs (one swizzle atom each)
@@ -115,6 +117,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   // prefill: two S buffers (columns 0 and 128) + O at 256; decode: one S buffer + O at 128, one
   // smem stage per operand, so that two CTAs fit on an SM and overlap each other's latencies
   constexpr int NSBUF = DECODE ? 1 : 2;
+  constexpr int NWG = DECODE ? 1 : 2;   // softmax warpgroups
   // K and V tiles travel through one ring in the order K0 V0 K1 V1 ...: tile t uses slot t % NSLOT
   constexpr int NSLOT = DECODE ? 3 : 2 * FA_STAGES;
   constexpr uint32_t TMEM_COLS = DECODE ? 256 : 512;
@@ -133,8 +136,10 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   uint64_t* s_full = bars + 9;             // 2
   uint64_t* p_ready = bars + 11;           // 2
   uint64_t* o_done = bars + 13;            // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* x_bar = bars + 14;             // 2: row-maximum exchange between the softmax warpgroups
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xchg = reinterpret_cast<float*>(tmem_slot + 4);   // [2 buffers][2 warpgroups][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z;
@@ -175,7 +180,8 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < NSLOT; ++s) { mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], 1); }
-    for (int s = 0; s < NSBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4); }
+    for (int s = 0; s < NSBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4 * NWG); }
+    for (int s = 0; s < 2; ++s) mbar_init(&x_bar[s], 4 * NWG);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -269,6 +275,15 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       }
     }
   } else {
+    // Softmax.  Prefill runs two warpgroups on the same query tile: warps 2-5 own key columns 0-63
+    // of every row, warps 6-9 columns 64-127 (a warp may only touch the TMEM lanes of its own
+    // quarter, so the two threads that share a row sit in warps w and w+4).  They exchange the row
+    // maximum through shared memory every block and the row sum once at the end; everything else
+    // (P, the O rescale, the output store) is split by columns.  Decode runs one warpgroup.
+    constexpr int CW = FA_BKV / NWG;     // S columns per thread
+    constexpr int NCH = CW / 32;
+    constexpr int DW = D / NWG;          // O columns per thread
+    const int wg = (warp - 2) >> 2;
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     const int row = q0 + row_in_tile;
@@ -281,33 +296,46 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       if (!ok) break;
       tc_fence_after();
       const uint32_t s_addr = lane_addr + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
-      uint32_t sr[4][32];
+      uint32_t sr[NCH][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sr[c]);
+      for (int c = 0; c < NCH; ++c) tmem_ld_32x32(s_addr + wg * CW + c * 32, sr[c]);
       tmem_wait_ld();
       const int kv0 = (j_begin + j) * FA_BKV;
       // Only the diagonal block of a causal tile and the last (ragged) key block need masking;
       // the test is hoisted so that the common path carries no per-element predicates.
       if ((kv0 + FA_BKV > kv_end) || (p.causal && kv0 + FA_BKV - 1 > q0)) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < NCH; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int col = kv0 + c * 32 + i;
+            const int col = kv0 + wg * CW + c * 32 + i;
             if (col >= kv_len || (p.causal && col > row)) sr[c][i] = __float_as_uint(-1e30f);
           }
       }
       float mx0 = -1e30f, mx1 = -1e30f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < NCH; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])));
           mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])));
         }
+      float mloc = fmaxf(mx0, mx1);
+      if (NWG == 2) {
+        // exchange with the thread that owns the other half of this row (double-buffered by j&1)
+        float* slot = xchg + (j & 1) * 256;
+        slot[wg * 128 + row_in_tile] = mloc;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&x_bar[j & 1]);
+        ok = mbar_wait(&x_bar[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, p.err, 310);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        mloc = fmaxf(mloc, slot[(wg ^ 1) * 128 + row_in_tile]);
+      }
       // scores are scaled inside the exponential: exp2(s*c - m*c) with c = scale*log2(e) > 0
-      const float m_blk = fmaxf(mx0, mx1) * p.scale_log2;
-      // Lazy rescale: keep the stale max unless it is more than 2^8 too small.
+      const float m_blk = mloc * p.scale_log2;
+      // Lazy rescale: keep the stale max unless it is more than 2^8 too small.  Both owners of a row
+      // see the same m_blk and the same history, so they take the same decision.
       float alpha = 1.f;
       bool rescale = false;
       if (j == 0 || (DECODE && row_in_tile >= p.group)) {
@@ -324,20 +352,20 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < DW / 32; ++c) {
           uint32_t orr[32];
-          tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
+          tmem_ld_32x32(lane_addr + O_COL0 + wg * DW + c * 32, orr);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-          tmem_st_32x32(lane_addr + O_COL0 + c * 32, orr);
+          tmem_st_32x32(lane_addr + O_COL0 + wg * DW + c * 32, orr);
         }
         l *= alpha;
       }
       // P = exp2(s - m_used) as packed bf16 into the first 64 columns of this S buffer
       float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < CW / 64; ++c) {
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -349,7 +377,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
           __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
           pk[i] = *reinterpret_cast<uint32_t*>(&v);
         }
-        tmem_st_32x32(s_addr + c * 32, pk);
+        tmem_st_32x32(s_addr + wg * (CW / 2) + c * 32, pk);
       }
       l += sum0 + sum1;
       tmem_wait_st();
@@ -360,6 +388,17 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     if (ok) {
       ok = mbar_wait(o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, p.err, 309);
       ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && NWG == 2) {
+      // total row sum = the two column halves; use the exchange buffer the last block did not use
+      const int jb = n_blocks & 1;
+      float* slot = xchg + jb * 256;
+      slot[wg * 128 + row_in_tile] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_bar[jb]);
+      ok = mbar_wait(&x_bar[jb], (uint32_t)((n_blocks >> 1) & 1), abort_flag, p.err, 311);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) l += slot[(wg ^ 1) * 128 + row_in_tile];
     }
     if (ok) {
       tc_fence_after();
@@ -412,11 +451,11 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         }
       } else {
         const float inv_l = 1.0f / l;
-        __nv_bfloat16* orow = p.o + (int64_t)b * p.so_b + (int64_t)h * p.so_h + (int64_t)row * p.so_s;
+        __nv_bfloat16* orow = p.o + (int64_t)b * p.so_b + (int64_t)h * p.so_h + (int64_t)row * p.so_s + wg * DW;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < DW / 32; ++c) {
           uint32_t orr[32];
-          tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
+          tmem_ld_32x32(lane_addr + O_COL0 + wg * DW + c * 32, orr);
           tmem_wait_ld();
           if (row < p.Sq) {
 #pragma unroll
@@ -448,7 +487,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 
 template <int D, bool DECODE>
 static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid) {
-  constexpr int SMEM = (DECODE ? 16 : FA_BQ) * D * 2 + (DECODE ? 3 : 2 * FA_STAGES) * FA_BKV * D * 2 + 1024 + 256;
+  constexpr int SMEM = (DECODE ? 16 : FA_BQ) * D * 2 + (DECODE ? 3 : 2 * FA_STAGES) * FA_BKV * D * 2 + 1024 + 256 + 2048;
   static bool configured = false;
   if (!configured) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(flash_attention_tcgen05_kernel<D, DECODE>,
@@ -456,7 +495,7 @@ static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
     configured = true;
   }
   if (DECODE) KD_CUDA_CHECK(launch_ex(flash_attention_tcgen05_kernel<D, DECODE>, grid, dim3(FA_THREADS), (size_t)SMEM, tq, tk, tv, p));
-  else flash_attention_tcgen05_kernel<D, DECODE><<<grid, FA_THREADS, SMEM, ctx().stream>>>(tq, tk, tv, p);
+  else flash_attention_tcgen05_kernel<D, DECODE><<<grid, FA_THREADS_PREFILL, SMEM, ctx().stream>>>(tq, tk, tv, p);
   return after_launch(DECODE ? "flash_attention_tcgen05_kernel<decode>" : "flash_attention_tcgen05_kernel");
 }
 
