@@ -499,6 +499,9 @@ static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
   return after_launch(DECODE ? "flash_attention_tcgen05_kernel<decode>" : "flash_attention_tcgen05_kernel");
 }
 
+// attention_prefill2.cu: two query sub-tiles per CTA share each K/V tile.
+int attention_prefill2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& a, void* out);
+
 int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out,
                      const AttnParams& a, int* handled) {
   *handled = 0;
@@ -525,6 +528,14 @@ int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   KD_TRY(make_tmap_bhsd(&tq, pq, eq, a.sq, FA_BQ));
   KD_TRY(make_tmap_bhsd(&tk, pk, ek, a.sk, FA_BKV));
   KD_TRY(make_tmap_bhsd(&tv, pv, ek, a.sv, FA_BKV));
+  // More than one query tile per KV head: the kernel that shares K/V tiles between two sub-tiles.
+  // KD_ATTENTION_ONE_TILE=1 in the environment keeps the one-tile kernel (for comparisons).
+  static const bool one_tile = [] { const char* e = getenv("KD_ATTENTION_ONE_TILE"); return e && e[0] == '1'; }();
+  if (!one_tile && ((a.Hq / a.Hkv) % 2 == 0 || a.Sq > FA_BQ)) {
+    KD_TRY(attention_prefill2(tq, tk, tv, a, po));
+    *handled = 1;
+    return KD_OK;
+  }
   FaParams p{};
   p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Sq = a.Sq; p.Skv = a.Skv;
   p.causal = a.causal;
