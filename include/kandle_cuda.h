@@ -288,6 +288,30 @@ int kd_attention_decode_paged(const kd_tensor* q, const kd_tensor* k_pool, const
                               const kd_tensor* block_table, const kd_tensor* ctx_len, int ctx_len_host,
                               float scale, int splits, const kd_tensor* out);
 
+/* Everything a decoder layer does between two attention calls of a decode step, as ONE
+ * persistent cooperative kernel (one CTA per SM; phases separated by grid-wide counters instead of
+ * kernel boundaries, weight tiles of the next phase prefetched while the current one finishes):
+ *   h1 = resid_in + attn W_o^T                      o_proj + residual add   (decoder_layer.ts:218-224)
+ *   x  = rmsnorm(h1) * post_norm_w                  post_attention_layernorm (decoder_layer.ts:226)
+ *   act = silu(x Wg^T) * (x Wu^T)                   mlp/swiglu.ts:119-134 (w_gate_up rows interleaved 16/16)
+ *   resid_out = h1 + act W_down^T                   down_proj + residual add (decoder_layer.ts:232-238)
+ *   x_out = rmsnorm(resid_out) * next_norm_w        the next layer's input_layernorm, or the final norm
+ *   qkv_partials[s] = x_out W_qkv_next^T (split s)  the next layer's q/k/v projections (gqa.ts:246-290),
+ *                                                   consumed by kd_qkv_norm_rope_cachewrite
+ * (paths under packages/model-utils/src/qwen3/ and .../attention/).  attn [Mb,Hq*D] bf16 (row
+ * stride a multiple of 8), resid_* fp32 [Mb,H] (resid_out may be resid_in; resid_mid is scratch that
+ * receives h1), x_out [Mb,H] and act [Mb,I] bf16, qkv_partials fp32 [splits,Mb,Nqkv] with `splits`
+ * as kd_decode_layer_chain_splits suggests (any value whose K split leaves no slice empty works).
+ * w_qkv_next and qkv_partials are NULL after the last layer.  1 <= Mb <= 128, H <= 4096.  The
+ * launch fails (no hang) if the device cannot hold one CTA per SM at once.  A wait that runs out
+ * (about one second) reports KD_ERR_DEVICE at the next synchronisation, codes 501-507. */
+int kd_decode_layer_chain(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
+                          const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
+                          const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
+                          const kd_tensor* resid_mid, const kd_tensor* resid_out, const kd_tensor* x_out,
+                          const kd_tensor* act, const kd_tensor* qkv_partials);
+int kd_decode_layer_chain_splits(int64_t N, int64_t K, int* splits_out);
+
 /* ---------------------------------------------------------------------------------------------
  * Tensor-parallel collectives (no counterpart in the reference, which is single-device).  One
  * process per GPU; NCCL is loaded at run time from `nccl_path` (NULL/"" = the system libnccl.so.2).

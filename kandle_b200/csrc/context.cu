@@ -164,6 +164,8 @@ int get_workspace(uint64_t bytes, void** out) {
 
 }  // namespace kd
 
+namespace kd { int decode_chain_reset_counters(); }
+
 using namespace kd;
 
 KD_API int kd_device_count(int* count) {
@@ -239,6 +241,7 @@ static int check_device_flag() {
   KD_CUDA_CHECK(cudaStreamSynchronize(c.stream));
   if (h[0] != 0) {
     cudaMemsetAsync(c.error_flag, 0, sizeof(h), c.stream);
+    decode_chain_reset_counters();
     return fail(KD_ERR_DEVICE, "a kernel reported error code %d (detail %d, %d, %d)", h[0], h[1], h[2], h[3]);
   }
   return KD_OK;

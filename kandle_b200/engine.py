@@ -92,6 +92,9 @@ class Qwen3Engine:
         self._decode = None
         self.pos = 0
         self.use_pdl = True
+        # decode: run o_proj .. next layer's QKV as one persistent kernel per layer (kd_decode_layer_chain);
+        # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
+        self.use_chain = self.tp == 1 and self.H <= 4096
 
     # ------------------------------------------------------------------ helpers
     def _linear(self, x, w, out, resid=None, epi=0):
@@ -215,8 +218,12 @@ class Qwen3Engine:
             return s.value
         e = lambda *shape: core.empty(shape, "bfloat16")  # noqa: E731
         f = lambda *shape: core.empty(shape, "float32")  # noqa: E731
+        def chain_splits(n, k):
+            s = ctypes.c_int(0)
+            lib.call("kd_decode_layer_chain_splits", ctypes.c_int64(n), ctypes.c_int64(k), ctypes.byref(s))
+            return s.value
         d = {
-            "B": B, "graph": None,
+            "B": B, "graph": None, "chain": self.use_chain,
             "scalars": core.zeros((2,), "int32"),           # [write position, context length]
             "ids": core.zeros((B,), "int64"), "emb": e(B, self.H), "h": f(B, self.H), "h1": f(B, self.H), "x": e(B, self.H),
             # a projection whose suggested split factor is 1 writes bf16 directly, otherwise fp32 partials
@@ -227,6 +234,9 @@ class Qwen3Engine:
             "down_p": f(splits(self.H, self.I), B, self.H), "logits": f(1, B, self.V),
             "cos": f(1, self.D // 2), "sin": f(1, self.D // 2),
         }
+        if self.use_chain:
+            d["qkv_p"].dispose()
+            d["qkv_p"] = f(chain_splits(self.nqkv, self.H), B, self.nqkv)
         d["pos"] = d["scalars"].slice([slice(0, 1)])
         d["ctx"] = d["scalars"].slice([slice(1, 2)])
         self._decode = d
@@ -254,10 +264,20 @@ class Qwen3Engine:
         for li, lw in enumerate(self.layers):
             kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
             vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
-            lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wqkv"]), 0, _r(d["qkv_p"]))
+            if li == 0 or not d["chain"]:
+                lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wqkv"]), 0, _r(d["qkv_p"]))
             lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
                      _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
             lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
+            nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
+            if d["chain"]:
+                last = li + 1 == self.L
+                lib.call("kd_decode_layer_chain", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
+                         _r(lw["wdown"]), _r(nxt), eps, None if last else _r(self.layers[li + 1]["wqkv"]), _r(h1), _r(h),
+                         _r(d["x"]), _r(d["act"]), None if last else _r(d["qkv_p"]))
+                kc.dispose()
+                vc.dispose()
+                continue
             lib.call("kd_linear_bf16_skinny", _r(attn2d), _r(lw["wo"]), 0, _r(d["o_p"]))
             if self.tp > 1:
                 self._allreduce(d["o_p"])
@@ -266,7 +286,6 @@ class Qwen3Engine:
             lib.call("kd_linear_bf16_skinny", _r(d["act"]), _r(lw["wdown"]), 0, _r(d["down_p"]))
             if self.tp > 1:
                 self._allreduce(d["down_p"])
-            nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
             self._norm(d["down_p"], nxt, d["x"], resid=h1, sum_out=h)
             kc.dispose()
             vc.dispose()
