@@ -4,6 +4,7 @@
     python -m kandle_b200.microbench attn  --b 4 --hq 16 --hkv 8 --s 2048 --d 128 [--no-causal]
     python -m kandle_b200.microbench decode_attn --b 32 --hq 16 --hkv 8 --ctx 2176 --d 128
     python -m kandle_b200.microbench skinny --m 32 --n 151936 --k 1024
+    python -m kandle_b200.microbench chain --m 32 --hidden 1024 --attn 2048 --inter 3072 --qkv 4096
 
 Each run prints one JSON line with the average launch time, the algorithmic work per launch and
 the achieved rate.  Inputs are seeded normal values (constant fills would flatter the power
@@ -101,6 +102,36 @@ def bench_skinny(a) -> dict:
     return {"kernel": "gemm_skinny_tcgen05", "m": a.m, "n": a.n, "k": a.k, "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
 
 
+def bench_chain(a) -> dict:
+    """kd_decode_layer_chain over several weight sets visited round-robin, so that every launch
+    streams its weights from HBM as a decode step does (one layer's weights are ~30 MB, L2 is 126 MB)."""
+    m, H, Ko, I, Nq = a.m, a.hidden, a.attn, a.inter, a.qkv
+    sets = []
+    for i in range(a.sets):
+        sets.append({"wo": _rand_bf16((H, Ko), 10 + i, 0.03), "wgu": _rand_bf16((2 * I, H), 20 + i, 0.03),
+                     "wd": _rand_bf16((H, I), 30 + i, 0.03), "wq": _rand_bf16((Nq, H), 40 + i, 0.03)})
+    attn = _rand_bf16((m, Ko), 1)
+    post, nxt = _rand_bf16((H,), 2), _rand_bf16((H,), 3)
+    h = Tensor(np.zeros((m, H), np.float32))
+    h1, h2 = core.empty((m, H), "float32"), core.empty((m, H), "float32")
+    x, act = core.empty((m, H), "bfloat16"), core.empty((m, I), "bfloat16")
+    sp = ctypes.c_int(0)
+    lib.call("kd_decode_layer_chain_splits", ctypes.c_int64(Nq), ctypes.c_int64(H), ctypes.byref(sp))
+    qp = core.empty((sp.value, m, Nq), "float32")
+    r = lambda t: ctypes.byref(t._handle.c())  # noqa: E731
+    state = {"i": 0}
+
+    def run():
+        w = sets[state["i"] % a.sets]
+        state["i"] += 1
+        lib.call("kd_decode_layer_chain", r(attn), r(w["wo"]), r(h), r(post), r(w["wgu"]), r(w["wd"]), r(nxt),
+                 ctypes.c_float(1e-6), r(w["wq"]), r(h1), r(h2), r(x), r(act), r(qp))
+    ms = _time(run, a.iters, a.warmup)
+    nbytes = 2.0 * (H * Ko + 2 * I * H + H * I + Nq * H)
+    return {"kernel": "decode_chain_kernel", "m": m, "hidden": H, "attn": Ko, "inter": I, "qkv": Nq, "weight_sets": a.sets,
+            "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="which", required=True)
@@ -128,12 +159,20 @@ def main() -> None:
     sk.add_argument("--m", type=int, default=32)
     sk.add_argument("--n", type=int, default=151936)
     sk.add_argument("--k", type=int, default=1024)
-    for p in (g, t, dd, sk):
+    ch = sub.add_parser("chain")
+    ch.add_argument("--m", type=int, default=32)
+    ch.add_argument("--hidden", type=int, default=1024)
+    ch.add_argument("--attn", type=int, default=2048)
+    ch.add_argument("--inter", type=int, default=3072)
+    ch.add_argument("--qkv", type=int, default=4096)
+    ch.add_argument("--sets", type=int, default=8)
+    for p in (g, t, dd, sk, ch):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     kandle_b200.init(0)
-    res = {"gemm": bench_gemm, "attn": bench_attn, "decode_attn": bench_decode_attn, "skinny": bench_skinny}[a.which](a)
+    res = {"gemm": bench_gemm, "attn": bench_attn, "decode_attn": bench_decode_attn, "skinny": bench_skinny,
+           "chain": bench_chain}[a.which](a)
     print(json.dumps(res))
 
 
