@@ -74,6 +74,12 @@ int kd_device_count(int* count);
 int kd_last_error(char* buf, size_t buf_len);
 /* Native stream handle (cudaStream_t) the library enqueues on, for event timing by the host. */
 int kd_stream(void** stream_out);
+/* Self-test of the bounded waits: runs a one-CTA kernel whose mbarrier wait can never be satisfied,
+ * with a limit of `limit_us` microseconds (1..100000) instead of the ~1 s the real kernels use.
+ * The kernel gives up, records error code 901, raises its abort flag and returns; the call
+ * returns KD_OK and the NEXT kd_synchronize / kd_download reports KD_ERR_DEVICE, after which the
+ * context works normally.  No reference counterpart (WebGPU has no device-side waits). */
+int kd_selftest_wait_timeout(uint32_t limit_us);
 /* Number of kernel launches the library has issued since kd_init (or the last reset). */
 int kd_launch_count(uint64_t* count, int reset);
 

@@ -45,14 +45,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` is a shared-memory int that any role sets when it gives up; every
 // waiter polls it so that the whole CTA drains instead of deadlocking on a dead partner.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                                long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (((++spins) & 63) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_CYCLE_LIMIT) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         if (atomicCAS(err, 0, code) == 0) { err[1] = (int)blockIdx.x; err[2] = (int)threadIdx.x; err[3] = (int)parity; }
         return false;
@@ -60,6 +61,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, err, code, WAIT_CYCLE_LIMIT);
 }
 
 // ----------------------------------------------------------------------------- TMA (tiled, non-multicast)

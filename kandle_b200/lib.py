@@ -99,6 +99,7 @@ _SIGNATURES = {
     "kd_device_count": [ctypes.POINTER(ctypes.c_int)],
     "kd_last_error": [ctypes.c_char_p, ctypes.c_size_t],
     "kd_stream": [ctypes.POINTER(ctypes.c_void_p)],
+    "kd_selftest_wait_timeout": [ctypes.c_uint32],
     "kd_launch_count": [ctypes.POINTER(_u64), ctypes.c_int],
     "kd_storage_alloc": [_u64, ctypes.c_int, ctypes.POINTER(_u64)],
     "kd_storage_retain": [_u64],
