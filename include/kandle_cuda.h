@@ -182,6 +182,20 @@ int kd_conv1d(const kd_tensor* input, const kd_tensor* weight, const kd_tensor* 
               int padding, const kd_tensor* out);
 
 /* ---------------------------------------------------------------------------------------------
+ * Next-token sampling on the device.  Replaces `sample` / `sampleGreedy`
+ * (packages/model-utils/src/sampling/index.ts:103-238): temperature, top-k, top-p, renormalise,
+ * draw by running sum in index order; do_sample == 0 is the greedy branch (argmax, lowest index on
+ * ties).  logits fp32 [V] or [B,V]; uniforms fp32 [B] in [0,1) stand in for Math.random() (one per
+ * sequence; ignored when greedy); out_ids int64 [B]; out_logprob fp32 [B] or NULL receives
+ * log(p_token + 1e-10) of the filtered, renormalised distribution, as SampleResult.logProb.  The
+ * reference's host path (download, stable sort of V indices, Float32Array storage with double
+ * arithmetic) is reproduced without a sort: radix selection on a monotone key with the sort's tie
+ * rule, probability mass in exact fixed point.  Its display list (top-10 ids/probs) is not produced.
+ * ------------------------------------------------------------------------------------------- */
+int kd_sample(const kd_tensor* logits, double temperature, int top_k, double top_p, int do_sample,
+              const kd_tensor* uniforms, const kd_tensor* out_ids, const kd_tensor* out_logprob);
+
+/* ---------------------------------------------------------------------------------------------
  * Timing.  CUDA events recorded on the library's stream (the reference only has host-side
  * performance.now() around dataAsync(), playground-node/src/qwen3/index.ts:161,253).
  * ------------------------------------------------------------------------------------------- */

@@ -96,6 +96,7 @@ class Qwen3Engine:
         # decode: run o_proj .. next layer's QKV as one persistent kernel per layer (kd_decode_layer_chain);
         # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
         self.use_chain = self.tp == 1 and self.H <= 4096
+        self.sampler = None   # None: greedy argmax; else dict(temperature, top_k, top_p, rng), see set_sampler
 
     # ------------------------------------------------------------------ helpers
     def _linear(self, x, w, out, resid=None, epi=0):
@@ -103,6 +104,30 @@ class Qwen3Engine:
 
     def _norm(self, x, w, out, resid=None, sum_out=None):
         lib.call("kd_add_rmsnorm", _r(x), _r(resid), _r(w), ctypes.c_float(self.cfg.rmsNormEps), _r(sum_out), _r(out))
+
+    def set_sampler(self, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
+        """Next tokens are drawn on the device (kd_sample: temperature, top-k, top-p, multinomial, the
+        reference's `sample` of packages/model-utils/src/sampling/index.ts:103-238) instead of the
+        greedy argmax.  The uniform numbers come from a seeded host generator, one per sequence and
+        step (128 bytes uploaded per step).  set_sampler(None) restores greedy decoding."""
+        self.dispose()       # a captured decode graph holds the old choice
+        if temperature is None:
+            self.sampler = None
+            return
+        self.sampler = {"temperature": float(temperature), "top_k": int(top_k), "top_p": float(top_p),
+                        "rng": np.random.Generator(np.random.PCG64(seed))}
+
+    def _next_tokens(self, logits2d: Tensor, uniforms, out_ids: Tensor) -> None:
+        if self.sampler is None:
+            lib.call("kd_argmax", _r(logits2d), _r(out_ids))
+        else:
+            sp = self.sampler
+            lib.call("kd_sample", _r(logits2d), ctypes.c_double(sp["temperature"]), sp["top_k"], ctypes.c_double(sp["top_p"]), 1,
+                     _r(uniforms), _r(out_ids), None)
+
+    def _fresh_uniforms(self, t: Tensor) -> None:
+        u = self.sampler["rng"].random(t.shape[0], dtype=np.float32)
+        core._backend().upload(t._handle, u)
 
     def _allreduce(self, t) -> None:
         lib.call("kd_allreduce_sum", _r(t))
@@ -124,6 +149,7 @@ class Qwen3Engine:
                 "act": e(T, self.I), "cos": core.empty((S, self.D // 2), "float32"),
                 "sin": core.empty((S, self.D // 2), "float32"), "last": core.empty((B, self.H), "float32"), "xl": e(B, self.H),
                 "logits": core.empty((1, B, self.V), "float32"), "tok": core.empty((B,), "int64"),
+                "uniforms": core.zeros((B,), "float32"),
             }}
         return self._prefill_bufs[key]
 
@@ -194,7 +220,9 @@ class Qwen3Engine:
         self._norm(w["last"], self.final_norm, w["xl"])
         lib.call("kd_linear_bf16_skinny", _r(w["xl"]), _r(self.embed), 0, _r(w["logits"]))
         lg = w["logits"].view(B, self.V)
-        lib.call("kd_argmax", _r(lg), _r(w["tok"]))
+        if self.sampler is not None:
+            self._fresh_uniforms(w["uniforms"])
+        self._next_tokens(lg, w["uniforms"], w["tok"])
         lg.dispose()
         full = None
         if all_logits:
@@ -233,7 +261,7 @@ class Qwen3Engine:
             "attn": e(B, 1, self.Hq, self.D), "o_p": f(splits(self.H, self.Hq * self.D), B, self.H),
             "act": e(B, self.I),
             "down_p": f(splits(self.H, self.I), B, self.H), "logits": f(1, B, self.V),
-            "cos": f(1, self.D // 2), "sin": f(1, self.D // 2),
+            "cos": f(1, self.D // 2), "sin": f(1, self.D // 2), "uniforms": core.zeros((B,), "float32"),
         }
         if self.use_chain:
             d["qkv_p"].dispose()
@@ -292,7 +320,7 @@ class Qwen3Engine:
             vc.dispose()
         lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(self.embed), 0, _r(d["logits"]))
         lg = d["logits"].view(B, self.V)
-        lib.call("kd_argmax", _r(lg), _r(d["ids"]))
+        self._next_tokens(lg, d["uniforms"], d["ids"])
         lg.dispose()
         lib.call("kd_increment_i32", _r(d["pos"]), 1)
         lib.call("kd_increment_i32", _r(d["ctx"]), 1)
@@ -332,6 +360,8 @@ class Qwen3Engine:
         d = self._decode
         if self.pos + 1 > self.max_seq_len:
             raise ValueError(f"Cache overflow: position {self.pos} but maxSeqLen is {self.max_seq_len}")
+        if self.sampler is not None:
+            self._fresh_uniforms(d["uniforms"])     # read by the (replayed) sampling kernel of this step
         if d["use_graph"]:
             lib.call("kd_graph_launch", ctypes.c_uint64(d["graph"]))
         else:
@@ -340,7 +370,7 @@ class Qwen3Engine:
         return d["ids"]
 
     def generate(self, ids, steps: int, use_graph: bool = True) -> np.ndarray:
-        """Greedy generation: prefill + `steps` tokens (the first comes from the prefill).  Returns
+        """Generation (greedy, or sampled after set_sampler): prefill + `steps` tokens (the first comes from the prefill).  Returns
         int64 [B, steps] on the host; every step's ids are read back, as the reference does."""
         tok = self.prefill(ids)
         B = tok.shape[0]

@@ -2,3 +2,4 @@
 from .qwen3 import (GroupedQueryAttention, Qwen3Config, Qwen3DecoderLayer, Qwen3ForCausalLM, Qwen3Model,  # noqa: F401
                     RotaryEmbedding, StaticKVCache, SwiGLUMLP, applyRotaryPosEmbDirect)
 from .whisper import ResidualAttentionBlock, WhisperAudioEncoder, WhisperConfig  # noqa: F401
+from .sampling import SampleResult, SamplerConfig, sample, sampleGreedy  # noqa: F401

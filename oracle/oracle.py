@@ -230,6 +230,56 @@ def argmax_rows(x: np.ndarray) -> np.ndarray:
     return out
 
 
+def _softmax_cpu(logits: np.ndarray, temperature: float) -> np.ndarray:
+    """softmaxCPU of packages/model-utils/src/sampling/index.ts:260-283: Float32Array storage,
+    double arithmetic, sequential double sum of the stored floats."""
+    x = np.asarray(logits, dtype=np.float32).astype(np.float64)
+    mx = x.max()
+    e = np.exp((x - mx) * (1.0 / temperature)).astype(np.float32)
+    total = np.cumsum(e.astype(np.float64))[-1]          # cumsum adds left to right, as the JS loop does
+    return (e.astype(np.float64) / total).astype(np.float32)
+
+
+def sample(logits: np.ndarray, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, do_sample: bool = True,
+           r: float = 0.5) -> dict:
+    """`sample` of packages/model-utils/src/sampling/index.ts:103-238 for one row of logits, with the
+    uniform number `r` in place of Math.random() (:291).  Returns token id, logProb and the final
+    probability vector."""
+    lg = np.asarray(logits, dtype=np.float32).reshape(-1)
+    V = lg.size
+    order = np.argsort(-lg.astype(np.float64), kind="stable")       # :133, a stable sort: ties keep index order
+    if not do_sample:                                                # :138-160
+        probs = _softmax_cpu(lg, temperature)
+        tok = int(order[0])
+        return {"token": tok, "logprob": float(np.log(np.float64(probs[tok]) + 1e-10)), "probs": probs}
+    scaled = lg
+    if temperature != 1.0:                                           # :167-175
+        scaled = (lg.astype(np.float64) * (1.0 / temperature)).astype(np.float32)
+    probs = _softmax_cpu(scaled, 1.0)                                # :178
+    k_eff = V
+    if 0 < top_k < V:                                                # :181-193
+        k_eff = top_k
+        mask = np.zeros(V, dtype=np.float32)
+        mask[order[:top_k]] = 1.0
+        probs = (probs * mask).astype(np.float32)
+    if top_p < 1.0:                                                  # :196-214
+        cum = np.cumsum(probs[order[:k_eff]].astype(np.float64))
+        hit = np.nonzero(cum >= top_p)[0]
+        cutoff = int(hit[0]) + 1 if hit.size else k_eff
+        probs[order[cutoff:]] = 0.0
+    total = np.cumsum(probs.astype(np.float64))[-1]                  # :217-222
+    if total > 0:
+        probs = (probs.astype(np.float64) / total).astype(np.float32)
+    cum = np.cumsum(probs.astype(np.float64))                        # :291-306
+    hit = np.nonzero(r < cum)[0]
+    if hit.size:
+        tok = int(hit[0])
+    else:
+        nz = np.nonzero(probs > 0)[0]
+        tok = int(nz[-1]) if nz.size else 0
+    return {"token": tok, "logprob": float(np.log(np.float64(probs[tok]) + 1e-10)), "probs": probs}
+
+
 def conv1d(x: np.ndarray, w: np.ndarray, bias: np.ndarray | None, stride: int = 1, padding: int = 0) -> np.ndarray:
     x, w = _f32(x), _f32(w)
     B, Cin, L = x.shape

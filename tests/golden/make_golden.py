@@ -33,6 +33,20 @@ def tiny_qwen3():
     return w, orc.Qwen3Oracle(cfg, w), synth.token_ids("golden.ids", (2, 11), 97)
 
 
+SAMPLER_CASES = [(1.0, 0, 1.0), (0.7, 50, 1.0), (1.0, 0, 0.9), (0.8, 40, 0.95), (1.3, 5, 0.5)]
+
+
+def sampler_inputs():
+    row = synth.normal("golden.sample", (4099,), 2.5)
+    us = ((np.arange(16) + 0.5) / 16).astype(np.float32)
+    return row, us
+
+
+def sampler_tokens():
+    row, us = sampler_inputs()
+    return np.array([[orc.sample(row, t, k, p, True, float(u))["token"] for u in us] for t, k, p in SAMPLER_CASES], dtype=np.int64)
+
+
 def main():
     orc.build()
     q, k, v = config1_inputs()
@@ -52,6 +66,7 @@ def main():
         softmax=orc.softmax(x),
         silu=orc.unary("silu", x), gelu=orc.unary("gelu", x),
         rope_cos=cos, rope_sin=sin,
+        sampler_tokens=sampler_tokens(),
     )
     print("wrote", os.path.join(HERE, "oracle_golden.npz"))
 

@@ -116,3 +116,24 @@ def test_engine_reports_cache_overflow(backend, oracle):
     with pytest.raises(ValueError):
         eng.prefill(synth.token_ids("ids", (1, 17), 216))
     eng.dispose()
+
+
+def test_sampled_generation_replays_and_degenerates_to_greedy(backend, oracle):
+    """Device-side sampling inside the decode graph: the replayed graph reads each step's fresh
+    uniform numbers (graph and eager runs with the same seed give the same tokens), top_k = 1 is
+    greedy decoding, and a wide sampler actually leaves the greedy path."""
+    eng, _ = _setup(oracle, vocab=216, hidden=128, inter=192, layers=2, heads=4, kv_heads=2, head_dim=64, batch=4,
+                    max_s=64, std=0.08, jitter=0.05)
+    ids = synth.token_ids("ids-sampled", (4, 17), 216)
+    greedy = eng.generate(ids, 10)
+    eng.set_sampler(temperature=0.9, top_k=1, top_p=1.0, seed=3)
+    assert np.array_equal(eng.generate(ids, 10), greedy)
+    eng.set_sampler(temperature=1.5, top_k=50, top_p=0.95, seed=7)
+    a = eng.generate(ids, 10, use_graph=True)
+    eng.set_sampler(temperature=1.5, top_k=50, top_p=0.95, seed=7)
+    b = eng.generate(ids, 10, use_graph=False)
+    assert np.array_equal(a, b)
+    assert (a != greedy).any()
+    assert a.min() >= 0 and a.max() < 216
+    eng.set_sampler(None)
+    assert np.array_equal(eng.generate(ids, 10), greedy)

@@ -33,6 +33,7 @@ def test_oracle_reproduces_golden(oracle):
     assert np.abs(oracle.unary("gelu", x) - G["gelu"]).max() <= 1e-6
     cos, sin = oracle.rope_tables(np.arange(2040, 2048, dtype=np.int32), 128, 1e6)
     assert np.abs(cos - G["rope_cos"]).max() <= 1e-6 and np.abs(sin - G["rope_sin"]).max() <= 1e-6
+    assert np.array_equal(make_golden.sampler_tokens(), G["sampler_tokens"])
 
 
 @pytest.mark.gpu
@@ -62,3 +63,9 @@ def test_cuda_kernels_reproduce_golden(backend):
     close(core.softmax(Tensor(x)).dataAsync(), G["softmax"])
     close(core.silu(Tensor(x)).dataAsync(), G["silu"], 1e-5)
     close(core.gelu(Tensor(x)).dataAsync(), G["gelu"], 1e-5)
+    from kandle_b200.model_utils import SamplerConfig, sample
+    row, us = make_golden.sampler_inputs()
+    rt = Tensor(row)
+    for ci, (t_, k_, p_) in enumerate(make_golden.SAMPLER_CASES):
+        got = [sample(rt, SamplerConfig(temperature=t_, topK=k_, topP=p_), uniform=float(u)).tokenId for u in us]
+        assert got == list(G["sampler_tokens"][ci])

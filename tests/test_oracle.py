@@ -245,3 +245,35 @@ def test_whisper_encoder_oracle_shapes_and_torch_block(oracle):
     x = x + F.gelu(yl @ W[p + "fc1.weight"].T + W[p + "fc1.bias"], approximate="tanh") @ W[p + "fc2.weight"].T + W[p + "fc2.bias"]
     ref = F.layer_norm(x, (32,), W["layer_norm.weight"], W["layer_norm.bias"]).detach().numpy()
     assert np.abs(y - ref).max() < 1e-4
+
+
+def test_sampler_restatement_against_a_sorted_float64_formulation(oracle):
+    """oracle.sample restates the reference's host sampler; here the same selection is written the
+    textbook way (sort, cumulative sums in float64) and the kept sets / draws must agree."""
+    rng = np.random.default_rng(5)
+    lg = (rng.standard_normal(3000) * 2.5).astype(np.float32)
+    for temperature, top_k, top_p in [(1.0, 0, 1.0), (0.7, 50, 1.0), (1.0, 0, 0.9), (0.8, 40, 0.95), (1.3, 5, 0.5)]:
+        x = lg.astype(np.float64) / temperature
+        p = np.exp(x - x.max())
+        p /= p.sum()
+        order = np.argsort(-lg.astype(np.float64), kind="stable")
+        keep = len(lg)
+        if 0 < top_k < len(lg):
+            keep = top_k
+        if top_p < 1.0:
+            cum = np.cumsum(p[order[:keep]])
+            keep = min(keep, int(np.searchsorted(cum, top_p, side="left")) + 1)
+        kept = np.zeros(len(lg), bool)
+        kept[order[:keep]] = True
+        q = np.where(kept, p, 0.0)
+        q /= q.sum()
+        for r in (0.01, 0.25, 0.5, 0.75, 0.99):
+            got = oracle.sample(lg, temperature, top_k, top_p, True, r)
+            assert np.array_equal(got["probs"] > 0, kept)
+            assert np.abs(got["probs"] - q).max() <= 1e-6
+            assert got["token"] == int(np.searchsorted(np.cumsum(q), r, side="right"))
+    g = oracle.sample(lg, 0.7, 0, 1.0, False)
+    assert g["token"] == int(lg.argmax())
+    tied = np.array([1.0, 3.0, 3.0, -1.0, 3.0], np.float32)
+    assert oracle.sample(tied, 1.0, 2, 1.0, True, 0.99)["token"] == 2        # stable sort keeps indices 1 and 2
+    assert oracle.sample(tied, 1.0, 0, 1.0, False)["token"] == 1
