@@ -182,6 +182,25 @@ int kd_conv1d(const kd_tensor* input, const kd_tensor* weight, const kd_tensor* 
               int padding, const kd_tensor* out);
 
 /* ---------------------------------------------------------------------------------------------
+ * Whisper log-mel front end (fp32), the step before the audio encoder.  Replaces the chain
+ * stft -> abs -> square -> MelScale of packages/core/src/dispatch/handlers/composite.ts:527-681,
+ * audio/functional/spectrogram.ts:28-76, audio/transforms/MelScale.ts:95-108, and the host loop of
+ * playground-node/src/whisper/audio.ts:379-405.
+ *   kd_stft_frames: frames_out[b,t,n] = waveform[b, t*hop + n - (center ? n_fft/2 : 0)] * window[n],
+ *     zero outside the signal (the reference pads in constant mode whatever pad_mode says);
+ *     frames_out is [B, 1 + (L + 2 pad - n_fft) / hop, n_fft].  The DFT itself is a kd_matmul of the
+ *     frames with a [n_fft, 2F] basis (cosines, then minus sines), F = n_fft/2 + 1.
+ *   kd_power_spectrum: spec [..., 2F] (real parts then imaginary parts) -> |X|^2 [..., F], computed
+ *     as the reference does: the magnitude rounded to fp32, then squared.
+ *   kd_whisper_log_mel_norm: mel [B, T, M] -> out [B, M, T'] (T' <= T: the reference drops the last
+ *     frame), out = (max(log10(max(mel, 1e-10)), item_max - 8) + 4) / 4.
+ * ------------------------------------------------------------------------------------------- */
+int kd_stft_frames(const kd_tensor* waveform, const kd_tensor* window, int n_fft, int hop_length, int center,
+                   const kd_tensor* frames_out);
+int kd_power_spectrum(const kd_tensor* spec_re_im, const kd_tensor* power_out);
+int kd_whisper_log_mel_norm(const kd_tensor* mel, const kd_tensor* out);
+
+/* ---------------------------------------------------------------------------------------------
  * Next-token sampling on the device.  Replaces `sample` / `sampleGreedy`
  * (packages/model-utils/src/sampling/index.ts:103-238): temperature, top-k, top-p, renormalise,
  * draw by running sum in index order; do_sample == 0 is the greedy branch (argmax, lowest index on

@@ -139,6 +139,9 @@ _SIGNATURES = {
     "kd_swiglu": [_T, _T],
     "kd_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
     "kd_increment_i32": [_T, ctypes.c_int],
+    "kd_stft_frames": [_T, _T, ctypes.c_int, ctypes.c_int, ctypes.c_int, _T],
+    "kd_power_spectrum": [_T, _T],
+    "kd_whisper_log_mel_norm": [_T, _T],
     "kd_sample": [_T, ctypes.c_double, ctypes.c_int, ctypes.c_double, ctypes.c_int, _T, _T, _T],
     "kd_decode_layer_chain": [_T, _T, _T, _T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T],
     "kd_decode_layer_chain_splits": [ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)],

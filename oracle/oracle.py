@@ -280,6 +280,42 @@ def sample(logits: np.ndarray, temperature: float = 1.0, top_k: int = 0, top_p: 
     return {"token": tok, "logprob": float(np.log(np.float64(probs[tok]) + 1e-10)), "probs": probs}
 
 
+def stft_power(x: np.ndarray, window: np.ndarray, n_fft: int, hop: int, center: bool = True) -> np.ndarray:
+    """|STFT|^2 of a [L] signal -> [T, n_fft/2+1], following the reference's `stft` composite
+    (packages/core/src/dispatch/handlers/composite.ts:527-681: constant-mode centre padding, framing,
+    window multiply in f32, one-sided transform) and `spectrogram` with power 2
+    (audio/functional/spectrogram.ts:63-68: abs, then abs*abs).  The transform itself is evaluated in
+    float64 and rounded to f32, i.e. an exactly rounded version of the reference's f32 Bluestein."""
+    x = np.asarray(x, dtype=np.float32).reshape(-1)
+    w = np.asarray(window, dtype=np.float32)
+    pad = n_fft // 2 if center else 0
+    xp = np.concatenate([np.zeros(pad, np.float32), x, np.zeros(pad, np.float32)])
+    T = 1 + (xp.size - n_fft) // hop
+    idx = np.arange(T)[:, None] * hop + np.arange(n_fft)[None, :]
+    frames = (xp[idx] * w[None, :]).astype(np.float32)
+    spec = np.fft.rfft(frames.astype(np.float64), axis=-1)
+    re, im = spec.real.astype(np.float32), spec.imag.astype(np.float32)
+    mag = np.sqrt(re * re + im * im, dtype=np.float32)
+    return (mag * mag).astype(np.float32)
+
+
+def whisper_log_mel(samples: np.ndarray, window: np.ndarray, fbanks: np.ndarray, n_fft: int = 400, hop: int = 160,
+                    n_samples: int = 480000) -> np.ndarray:
+    """WhisperFeatureExtractor.extract (playground-node/src/whisper/audio.ts:322-414) for 16 kHz input:
+    pad/cut to 30 s, mel power [M, T], drop the last frame, log10(max(x,1e-10)), clamp to max-8,
+    (x+4)/4, with the Float32Array storage of the host loop.  Returns [1, M, 3000]."""
+    x = np.zeros(n_samples, dtype=np.float32)
+    s = np.asarray(samples, dtype=np.float32).reshape(-1)[:n_samples]
+    x[: s.size] = s
+    power = stft_power(x, window, n_fft, hop)                                  # [T, F]
+    mel = linear(power, np.ascontiguousarray(np.asarray(fbanks, np.float32).T))  # [T, M], f32 accumulation as the GEMM shader
+    mel = mel.T[:, : n_samples // hop]                                          # [M, 3000]
+    log_spec = np.log10(np.maximum(mel.astype(np.float64), np.float64(np.float32(1e-10)))).astype(np.float32)
+    mx = log_spec.max()
+    log_spec = np.maximum(log_spec.astype(np.float64), np.float64(mx) - 8.0).astype(np.float32)
+    return ((log_spec.astype(np.float64) + 4.0) / 4.0).astype(np.float32)[None]
+
+
 def conv1d(x: np.ndarray, w: np.ndarray, bias: np.ndarray | None, stride: int = 1, padding: int = 0) -> np.ndarray:
     x, w = _f32(x), _f32(w)
     B, Cin, L = x.shape

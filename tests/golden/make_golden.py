@@ -47,6 +47,13 @@ def sampler_tokens():
     return np.array([[orc.sample(row, t, k, p, True, float(u))["token"] for u in us] for t, k, p in SAMPLER_CASES], dtype=np.int64)
 
 
+def log_mel_golden():
+    from kandle_b200 import audio
+    x = synth.synthetic_audio("golden.audio", 16000 * 4)
+    full = orc.whisper_log_mel(x, audio.hann_window_host(400), audio.melscale_fbanks_host(201, 0, 8000, 80, 16000, "slaney", "slaney"))
+    return x, full
+
+
 def main():
     orc.build()
     q, k, v = config1_inputs()
@@ -67,6 +74,7 @@ def main():
         silu=orc.unary("silu", x), gelu=orc.unary("gelu", x),
         rope_cos=cos, rope_sin=sin,
         sampler_tokens=sampler_tokens(),
+        log_mel=log_mel_golden()[1][0, ::4, ::25],          # every 4th mel band, every 25th frame of a 4 s clip
     )
     print("wrote", os.path.join(HERE, "oracle_golden.npz"))
 

@@ -34,6 +34,7 @@ def test_oracle_reproduces_golden(oracle):
     cos, sin = oracle.rope_tables(np.arange(2040, 2048, dtype=np.int32), 128, 1e6)
     assert np.abs(cos - G["rope_cos"]).max() <= 1e-6 and np.abs(sin - G["rope_sin"]).max() <= 1e-6
     assert np.array_equal(make_golden.sampler_tokens(), G["sampler_tokens"])
+    assert np.abs(make_golden.log_mel_golden()[1][0, ::4, ::25] - G["log_mel"]).max() <= 1e-6
 
 
 @pytest.mark.gpu
@@ -63,6 +64,9 @@ def test_cuda_kernels_reproduce_golden(backend):
     close(core.softmax(Tensor(x)).dataAsync(), G["softmax"])
     close(core.silu(Tensor(x)).dataAsync(), G["silu"], 1e-5)
     close(core.gelu(Tensor(x)).dataAsync(), G["gelu"], 1e-5)
+    from kandle_b200 import audio
+    feats = audio.WhisperFeatureExtractor(80).extract(make_golden.log_mel_golden()[0], 16000).dataAsync()
+    assert np.abs(feats[0, ::4, ::25] - G["log_mel"]).max() <= 1e-3
     from kandle_b200.model_utils import SamplerConfig, sample
     row, us = make_golden.sampler_inputs()
     rt = Tensor(row)

@@ -277,3 +277,24 @@ def test_sampler_restatement_against_a_sorted_float64_formulation(oracle):
     tied = np.array([1.0, 3.0, 3.0, -1.0, 3.0], np.float32)
     assert oracle.sample(tied, 1.0, 2, 1.0, True, 0.99)["token"] == 2        # stable sort keeps indices 1 and 2
     assert oracle.sample(tied, 1.0, 0, 1.0, False)["token"] == 1
+
+
+def test_log_mel_restatement_against_torch_stft(oracle):
+    """oracle.whisper_log_mel against the same pipeline written with torch.stft (constant-mode centre
+    padding, the symmetric Hann window and the slaney filterbank the reference builds)."""
+    from kandle_b200 import audio
+    w = audio.hann_window_host(400)
+    fb = audio.melscale_fbanks_host(201, 0, 8000, 80, 16000, "slaney", "slaney")
+    assert abs(w[0]) == 0.0 and abs(w[399]) < 1e-7 and abs(w[200] - w[199]) < 1e-6      # symmetric: M = N - 1
+    assert fb.shape == (201, 80) and (fb >= 0).all() and ((fb > 0).sum(0) >= 1).all()
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal(16000 * 3) * 0.1).astype(np.float32)
+    got = oracle.whisper_log_mel(x, w, fb)
+    xt = torch.zeros(480000)
+    xt[: x.size] = torch.from_numpy(x)
+    st = torch.stft(xt, 400, 160, window=torch.from_numpy(w), center=True, pad_mode="constant", return_complex=True)
+    mel = (torch.from_numpy(fb).T @ (st.abs() ** 2))[:, :3000]
+    ls = torch.clamp(mel, min=1e-10).log10()
+    ls = (torch.maximum(ls, ls.max() - 8.0) + 4.0) / 4.0
+    assert got.shape == (1, 80, 3000)
+    assert np.abs(ls.numpy() - got[0]).max() <= 5e-6
