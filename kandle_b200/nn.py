@@ -29,6 +29,13 @@ class Module:
     def registerParameter(self, name: str, t: Tensor | None) -> None:
         setattr(self, name, t)
 
+    def registerBuffer(self, name: str, t: Tensor, persistent: bool = True) -> None:
+        """nn/module.ts registerBuffer: a non-persistent buffer is an attribute that stays out of the state dict."""
+        if persistent:
+            setattr(self, name, t)
+        else:
+            object.__setattr__(self, name, t)
+
     def namedParameters(self, prefix: str = ""):
         for n, p in self._parameters.items():
             yield prefix + n, p
@@ -150,8 +157,8 @@ class Conv1d(Module):
 
 
 class MultiheadAttention(Module):
-    """Self-attention form of packages/core/src/nn/modules/attention/MultiheadAttention.ts:280-437
-    (batchFirst=true): inputs are transposed to (L,N,E) views, q/k/v projections use row slices of
+    """packages/core/src/nn/modules/attention/MultiheadAttention.ts:280-437 (batchFirst=true), self- and
+    cross-attention: inputs are transposed to (L,N,E) views, q/k/v projections use row slices of
     `in_proj_weight` / `in_proj_bias` (views with non-zero offsets), heads become (N*H, L, E/H) and
     attention runs through scaledDotProductAttention on 3-D tensors."""
 
@@ -162,25 +169,31 @@ class MultiheadAttention(Module):
         self.in_proj_bias = core.zeros((3 * embedDim,), dtype)
         self.out_proj = Linear(embedDim, embedDim, True, dtype)
 
-    def forward(self, query: Tensor) -> Tensor:
+    def forward(self, query: Tensor, key: Tensor | None = None, value: Tensor | None = None,
+                attnMask: Tensor | None = None) -> Tensor:
+        """query (N,L,E); key/value (N,S,E), default: the query (self-attention).  attnMask is an
+        additive float mask broadcastable to (N*H, L, S); with a mask scaledDotProductAttention takes
+        the naive matmul -> add -> softmax -> matmul path, as the reference does."""
         E, H, D = self.embedDim, self.numHeads, self.headDim
-        x = query.transpose(0, 1)                      # (L, N, E) view
-        L, N = x.shape[0], x.shape[1]
+        srcs = [query, query if key is None else key, query if value is None else value]
+        N = query.shape[0]
         outs = []
         for j in range(3):
+            x = srcs[j].transpose(0, 1)                # (L or S, N, E) view
+            Lj = x.shape[0]
             w = self.in_proj_weight.slice([slice(j * E, (j + 1) * E), slice(None)])
             b = self.in_proj_bias.slice([slice(j * E, (j + 1) * E)])
-            p = core.linear(x, w, b)                   # (L, N, E)
+            p = core.linear(x, w, b)                   # (Lj, N, E)
             w.dispose()
             b.dispose()
-            v1 = p.view(L, N * H, D)
-            v2 = v1.permute([1, 0, 2])                 # (N*H, L, D)
+            v1 = p.view(Lj, N * H, D)
+            v2 = v1.permute([1, 0, 2])                 # (N*H, Lj, D)
             outs.append(core.contiguous(v2))
-            for t in (v2, v1, p):
+            for t in (v2, v1, p, x):
                 t.dispose()
-        x.dispose()
+        L = query.shape[1]
         q, k, v = outs
-        o = core.scaledDotProductAttention(q, k, v, None, 0.0, False)
+        o = core.scaledDotProductAttention(q, k, v, attnMask, 0.0, False)
         for t in outs:
             t.dispose()
         o1 = o.permute([1, 0, 2])                      # (L, N*H, D)

@@ -82,6 +82,27 @@ def whisper_encoder_weights(*, n_mels: int, state: int, layers: int, n_ctx: int,
     return w
 
 
+def whisper_decoder_weights(*, vocab: int, state: int, layers: int, n_ctx: int, std: float = 0.02,
+                            base_seed: int = BASE_SEED) -> dict:
+    w = {}
+
+    def t(name, shape, s=std, mean=0.0):
+        w[name] = normal("dec." + name, shape, s, mean, base_seed)
+
+    t("embed_tokens.weight", (vocab, state)); t("embed_positions.weight", (n_ctx, state))
+    for i in range(layers):
+        p = f"layers.{i}."
+        for a in ("self_attn", "encoder_attn"):
+            t(p + a + "_layer_norm.weight", (state,), std, 1.0); t(p + a + "_layer_norm.bias", (state,))
+            t(p + a + ".in_proj_weight", (3 * state, state)); t(p + a + ".in_proj_bias", (3 * state,))
+            t(p + a + ".out_proj.weight", (state, state)); t(p + a + ".out_proj.bias", (state,))
+        t(p + "final_layer_norm.weight", (state,), std, 1.0); t(p + "final_layer_norm.bias", (state,))
+        t(p + "fc1.weight", (4 * state, state)); t(p + "fc1.bias", (4 * state,))
+        t(p + "fc2.weight", (state, 4 * state)); t(p + "fc2.bias", (state,))
+    t("layer_norm.weight", (state,), std, 1.0); t("layer_norm.bias", (state,))
+    return w
+
+
 def synthetic_audio(name: str, n_samples: int = 480000, sr: int = 16000, base_seed: int = BASE_SEED) -> np.ndarray:
     """Sum of 3..8 sines (80..4000 Hz, amplitude 0.05..0.3, random phase) plus N(0, 0.01) noise."""
     g = _rng(name, base_seed)

@@ -534,5 +534,74 @@ class WhisperEncoderOracle:
         return layer_norm(x, w["layer_norm.weight"], w["layer_norm.bias"], c.ln_eps)
 
 
+# ----------------------------------------------------------------------------- Whisper text decoder
+@dataclass
+class WhisperDecoderConfig:
+    """packages/model-utils/src/whisper/config.ts (decoder fields)."""
+    n_vocab: int = 51865
+    n_text_ctx: int = 448
+    n_text_state: int = 768
+    n_text_head: int = 12
+    n_text_layer: int = 12
+    ln_eps: float = 1e-5
+
+
+class WhisperDecoderOracle:
+    """WhisperTextDecoder.forward (packages/model-utils/src/whisper/decoder.ts:203-261) with the
+    cross-attention ResidualAttentionBlock (whisper/block.ts:150-200).  Self-attention carries the
+    additive -inf mask, which sends scaled_dot_product_attention down the naive path
+    matmul(alpha=scale) -> add(mask) -> softmax -> matmul
+    (packages/core/src/dispatch/handlers/composite.ts:262-347); cross-attention has no mask and uses
+    the fused attention kernel.
+
+    weights: embed_tokens.weight, embed_positions.weight, layer_norm.{weight,bias}, and per layer
+      layers.{i}.{self_attn,encoder_attn}.{in_proj_weight,in_proj_bias,out_proj.weight,out_proj.bias},
+      layers.{i}.{self_attn_layer_norm,encoder_attn_layer_norm,final_layer_norm}.{weight,bias},
+      layers.{i}.fc1.{weight,bias}, layers.{i}.fc2.{weight,bias}
+    """
+
+    def __init__(self, cfg: WhisperDecoderConfig, weights: dict):
+        self.cfg, self.w = cfg, weights
+
+    def _mha(self, prefix: str, xq: np.ndarray, xkv: np.ndarray, mask: np.ndarray | None) -> np.ndarray:
+        c, w = self.cfg, self.w
+        B, L, E = xq.shape
+        S, H = xkv.shape[1], c.n_text_head
+        D = E // H
+        W_in, b_in = w[prefix + "in_proj_weight"], w[prefix + "in_proj_bias"]
+        q = linear(xq, W_in[0:E], b_in[0:E])
+        k = linear(xkv, W_in[E:2 * E], b_in[E:2 * E])
+        v = linear(xkv, W_in[2 * E:], b_in[2 * E:])
+        def heads(t, n):
+            return np.ascontiguousarray(t.reshape(B, n, H, D).transpose(0, 2, 1, 3)).reshape(1, B * H, n, D)
+        qh, kh, vh = heads(q, L), heads(k, S), heads(v, S)
+        if mask is None:
+            o = sdpa(qh[0], kh[0], vh[0], is_causal=False)[None]
+        else:
+            scores = matmul4d(qh, kh, trans_b=True, alpha=1.0 / math.sqrt(D))
+            scores = add(scores, mask[None, None])
+            o = matmul4d(softmax(scores), vh)
+        o = np.ascontiguousarray(o.reshape(B, H, L, D).transpose(0, 2, 1, 3)).reshape(B, L, E)
+        return linear(o, w[prefix + "out_proj.weight"], w[prefix + "out_proj.bias"])
+
+    def forward(self, tokens: np.ndarray, xa: np.ndarray, offset: int = 0, num_layers: int | None = None) -> np.ndarray:
+        c, w = self.cfg, self.w
+        S = tokens.shape[1]
+        x = add(embedding(w["embed_tokens.weight"], tokens), w["embed_positions.weight"][offset:offset + S][None])
+        mask = np.where(np.arange(S)[None, :] > np.arange(S)[:, None], -np.inf, 0.0).astype(np.float32)
+        L = c.n_text_layer if num_layers is None else num_layers
+        for li in range(L):
+            p = f"layers.{li}."
+            y = layer_norm(x, w[p + "self_attn_layer_norm.weight"], w[p + "self_attn_layer_norm.bias"], c.ln_eps)
+            x = add(x, self._mha(p + "self_attn.", y, y, mask))
+            y = layer_norm(x, w[p + "encoder_attn_layer_norm.weight"], w[p + "encoder_attn_layer_norm.bias"], c.ln_eps)
+            x = add(x, self._mha(p + "encoder_attn.", y, xa, None))
+            y = layer_norm(x, w[p + "final_layer_norm.weight"], w[p + "final_layer_norm.bias"], c.ln_eps)
+            y = unary("gelu", linear(y, w[p + "fc1.weight"], w[p + "fc1.bias"]))
+            x = add(x, linear(y, w[p + "fc2.weight"], w[p + "fc2.bias"]))
+        x = layer_norm(x, w["layer_norm.weight"], w["layer_norm.bias"], c.ln_eps)
+        return linear(x, w["embed_tokens.weight"])
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))

@@ -298,3 +298,45 @@ def test_log_mel_restatement_against_torch_stft(oracle):
     ls = (torch.maximum(ls, ls.max() - 8.0) + 4.0) / 4.0
     assert got.shape == (1, 80, 3000)
     assert np.abs(ls.numpy() - got[0]).max() <= 5e-6
+
+
+def test_whisper_decoder_restatement_against_float64(oracle):
+    """WhisperDecoderOracle against a direct float64 evaluation of the same block structure."""
+    from kandle_b200 import synth as sy
+    V, E, H, L, C = 61, 32, 4, 2, 16
+    w = sy.whisper_decoder_weights(vocab=V, state=E, layers=L, n_ctx=C, std=0.1)
+    cfg = oracle.WhisperDecoderConfig(n_vocab=V, n_text_ctx=C, n_text_state=E, n_text_head=H, n_text_layer=L)
+    tokens = sy.token_ids("dec-cpu", (2, 7), V)
+    xa = sy.normal("dec-cpu-xa", (2, 11, E), 0.5)
+    got = oracle.WhisperDecoderOracle(cfg, w).forward(tokens, xa, offset=3)
+    W = {k: v.astype(np.float64) for k, v in w.items()}
+
+    def ln(x, p):
+        m = x.mean(-1, keepdims=True)
+        v = ((x - m) ** 2).mean(-1, keepdims=True)
+        return (x - m) / np.sqrt(v + 1e-5) * W[p + ".weight"] + W[p + ".bias"]
+
+    def mha(p, xq, xkv, causal):
+        Wi, bi = W[p + ".in_proj_weight"], W[p + ".in_proj_bias"]
+        q, k, v = xq @ Wi[:E].T + bi[:E], xkv @ Wi[E:2 * E].T + bi[E:2 * E], xkv @ Wi[2 * E:].T + bi[2 * E:]
+        B, Lq, S, D = xq.shape[0], xq.shape[1], xkv.shape[1], E // H
+        q, k, v = (t.reshape(B, -1, H, D).transpose(0, 2, 1, 3) for t in (q, k, v))
+        s = q @ k.transpose(0, 1, 3, 2) / math.sqrt(D)
+        if causal:
+            s = s + np.where(np.arange(S)[None, :] > np.arange(Lq)[:, None], -np.inf, 0.0)
+        s = np.exp(s - s.max(-1, keepdims=True))
+        o = (s / s.sum(-1, keepdims=True)) @ v
+        return o.transpose(0, 2, 1, 3).reshape(B, Lq, E) @ W[p + ".out_proj.weight"].T + W[p + ".out_proj.bias"]
+
+    def gelu(x):   # tanh form with the reference's clamp
+        return 0.5 * x * (1.0 + np.tanh(np.clip(0.7978845608028654 * (x + 0.044715 * x ** 3), -20, 20)))
+
+    x = W["embed_tokens.weight"][tokens] + W["embed_positions.weight"][3:10][None]
+    for i in range(L):
+        p = f"layers.{i}."
+        x = x + mha(p + "self_attn", ln(x, p + "self_attn_layer_norm"), ln(x, p + "self_attn_layer_norm"), True)
+        x = x + mha(p + "encoder_attn", ln(x, p + "encoder_attn_layer_norm"), xa.astype(np.float64), False)
+        y = gelu(ln(x, p + "final_layer_norm") @ W[p + "fc1.weight"].T + W[p + "fc1.bias"])
+        x = x + y @ W[p + "fc2.weight"].T + W[p + "fc2.bias"]
+    ref = ln(x, "layer_norm") @ W["embed_tokens.weight"].T
+    assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()

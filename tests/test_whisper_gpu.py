@@ -56,3 +56,48 @@ def test_whisper_small_shapes_bf16_two_layers(backend, oracle):
     ref = orc.forward(mel)
     err = np.abs(got - ref)
     assert np.quantile(err, 0.999) <= 3e-2 * np.abs(ref).max() and err.max() <= 6e-2 * np.abs(ref).max(), (err.max(), np.abs(ref).max())
+
+
+def _build_decoder(oracle, *, vocab, state, heads, layers, n_ctx, std=0.08):
+    from kandle_b200.model_utils import WhisperTextDecoder
+    w = synth.whisper_decoder_weights(vocab=vocab, state=state, layers=layers, n_ctx=n_ctx, std=std)
+    cfg = WhisperConfig(nVocab=vocab, nTextCtx=n_ctx, nTextState=state, nTextHead=heads, nTextLayer=layers)
+    dec = WhisperTextDecoder(cfg)
+    dec.loadStateDict(w)
+    ocfg = oracle.WhisperDecoderConfig(n_vocab=vocab, n_text_ctx=n_ctx, n_text_state=state, n_text_head=heads, n_text_layer=layers)
+    return dec, oracle.WhisperDecoderOracle(ocfg, w)
+
+
+def test_text_decoder_fp32_masked_self_attention_and_cross_attention(backend, oracle):
+    """WhisperTextDecoder on the eager path: learned positions at an offset, causal self-attention
+    through the additive -inf mask (the naive matmul/add/softmax/matmul path), cross-attention over
+    an encoder output of a different length, logits through the transposed token embedding."""
+    dec, orc = _build_decoder(oracle, vocab=203, state=64, heads=4, layers=2, n_ctx=32)
+    names = set(dec.stateDict())
+    assert "layers.1.encoder_attn.in_proj_weight" in names and "layers.0.encoder_attn_layer_norm.bias" in names
+    tokens = synth.token_ids("dec-tokens", (2, 9), 203)
+    xa = synth.normal("dec-xa", (2, 20, 64), 0.5)
+    for offset in (0, 5):
+        got = dec.forward(Tensor(tokens), Tensor(xa), offset).dataAsync()
+        ref = orc.forward(tokens, xa, offset)
+        assert got.shape == ref.shape == (2, 9, 203)
+        assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()
+    # causality: logits of the first 4 positions do not depend on later tokens
+    t2 = tokens.copy()
+    t2[:, 4:] = (t2[:, 4:] + 7) % 203
+    a = dec.forward(Tensor(tokens), Tensor(xa), 0).dataAsync()
+    b = dec.forward(Tensor(t2), Tensor(xa), 0).dataAsync()
+    assert np.array_equal(a[:, :4], b[:, :4]) and not np.array_equal(a[:, 4:], b[:, 4:])
+    with pytest.raises(ValueError):
+        dec.forward(Tensor(tokens), Tensor(xa), 30)
+
+
+def test_text_decoder_whisper_small_widths_one_layer(backend, oracle):
+    """Whisper-small decoder widths (768 state, 12 heads of 64, vocabulary 51865) against 1500 encoder positions."""
+    dec, orc = _build_decoder(oracle, vocab=51865, state=768, heads=12, layers=1, n_ctx=448, std=0.02)
+    tokens = synth.token_ids("dec-tokens-small", (1, 12), 51865)
+    xa = synth.normal("dec-xa-small", (1, 1500, 768), 0.3)
+    got = dec.forward(Tensor(tokens), Tensor(xa)).dataAsync()
+    ref = orc.forward(tokens, xa)
+    assert got.shape == (1, 12, 51865)
+    assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()
