@@ -333,12 +333,34 @@ def run_ours(a) -> None:
         us = k0.elapsed_ms(k1) * 1e3 / (reps * n_l)
         alg_bytes = 2.0 * B * (dims["kv_heads"] // tp_size) * ctx_mean * dims["head_dim"] * 2
         ach = alg_bytes / (us * 1e-6) / 1e9
-        roofline = {"kernel": "flash_attention_tcgen05_kernel<decode> + decode_combine_kernel", "bound": "hbm", "achieved": ach,
+        roofline = {"kernel": "flash_attention_tcgen05_kernel<decode> (+ decode_combine_kernel when the keys are split)", "bound": "hbm", "achieved": ach,
                     "peak": hbm_peak, "peak_source": hbm_src, "unit": "GB/s", "frac": ach / hbm_peak,
                     # dram__bytes_read+write of one ncu capture at B=32, Hkv=8, ctx=2176 (290.1 MB for 285.2 MB
                     # algorithmic); traffic is proportional to the keys read, so other shapes are scaled
                     "traffic": alg_bytes * (290.1e6 / 285.212672e6),
                     "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": us, "context": ctx_mean}
+        if d.get("chain") and n_l > 1:
+            # the per-layer chain kernel (o_proj .. next QKV), one launch per layer so that weights stream from HBM
+            attn2d = d["attn"].view(B, eng.Hq * eng.D)
+            eps = ctypes.c_float(eng.cfg.rmsNormEps)
+            r_ = lambda t: ctypes.byref(t._handle.c())  # noqa: E731
+            def chain_all_layers():
+                for li in range(n_l - 1):
+                    lw_ = eng.layers[li]
+                    lib.call("kd_decode_layer_chain", r_(attn2d), r_(lw_["wo"]), r_(d["h"]), r_(lw_["post_norm"]), r_(lw_["wgu"]),
+                             r_(lw_["wdown"]), r_(eng.layers[li + 1]["in_norm"]), eps, r_(eng.layers[li + 1]["wqkv"]), r_(d["h1"]),
+                             r_(d["h"]), r_(d["x"]), r_(d["act"]), r_(d["qkv_p"]))
+            chain_all_layers()
+            c0, c1 = CudaEvent(), CudaEvent()
+            c0.record()
+            for _ in range(reps):
+                chain_all_layers()
+            c1.record()
+            us_c = c0.elapsed_ms(c1) * 1e3 / (reps * (n_l - 1))
+            wbytes = 2.0 * (eng.H * eng.Hq * eng.D + 3 * eng.I * eng.H + eng.nqkv * eng.H)
+            other["decode_chain"] = {"bound": "hbm", "achieved": wbytes / (us_c * 1e-6) / 1e9, "peak": hbm_peak, "peak_source": hbm_src,
+                                     "unit": "GB/s", "frac": wbytes / (us_c * 1e-6) / 1e9 / hbm_peak, "us_per_launch": us_c,
+                                     "note": "latency-bound: six dependent phases per launch; eager launches, gaps included"}
     # prefill GEMM + attention, timed alone on the prefill buffers
     w = eng._bufs(B, S)
     lw = eng.layers[0]

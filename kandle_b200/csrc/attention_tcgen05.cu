@@ -93,6 +93,17 @@ struct FaParams {
   float* part_o;               // [B, Hkv, splits, group, D] un-normalised partial outputs
   float* part_ml;              // [B, Hkv, splits, group, 2] (running max in the log2 domain, sum)
   int direct;                  // splits == 1: write O/l as bf16 straight to `o` (no combine kernel)
+  // Fused decode prologue (qkv_part != NULL): Q and the new token's K/V cache row are produced here
+  // from the split-K partial sums of the QKV projection: q/k RMSNorm over head_dim, RoPE, bf16.
+  const float* qkv_part;       // [qkv_splits][B][n_qkv] fp32, columns: q heads, k heads, v heads
+  int qkv_splits, n_qkv;
+  const __nv_bfloat16 *qw, *kw;   // q_norm / k_norm weights [D]
+  float eps;
+  const float *cos_t, *sin_t;  // [D/2] for the new token's position
+  const int* pos_ptr;          // device scalar: position of the new token; the context length is pos + 1
+  __nv_bfloat16 *k_cache, *v_cache;
+  int64_t kc_b, kc_h, kc_s;
+  int max_s;
 };
 
 constexpr int FA_BQ = 128;
@@ -101,10 +112,115 @@ constexpr int FA_THREADS = 192;           // decode: TMA warp, MMA warp, one sof
 constexpr int FA_THREADS_PREFILL = 320;   // prefill: two softmax warpgroups
 constexpr int FA_STAGES = 2;
 
+// Fused decode prologue, run by the four softmax warps (128 threads, `q` = warp & 3): the Q tile and
+// the new K/V cache row from the QKV partial sums.  Half a warp per head row, lane l holds 4 (2 for
+// head_dim 64) elements of the first half of the head and the elements D/2 further on (both members
+// of each rotation pair); arithmetic and its order are those of qkv_norm_rope_kernel.  Kept out of
+// line so that its registers do not weigh on the attention loop.
+template <int D>
+__device__ __noinline__ void decode_qkv_prologue(const FaParams& p, uint8_t* q_smem, int Q_SLAB, int QROWS, int b, int hk,
+                                                 int kv_len, int j_begin, int j_end, int q, int lane, uint64_t* q_full,
+                                                 uint64_t* kv_ready) {
+      // Q tile and the new K/V cache row from the QKV partial sums.  Half a warp per head row, lane l
+      // holds 4 elements of the first half of the head and the 4 elements D/2 further on (both members
+      // of each rotation pair), the arithmetic and its order being those of qkv_norm_rope_kernel.
+      constexpr int HALF = D / 2, VE = D / 32;
+      const int new_tile = (kv_len - 1) / FA_BKV;
+      const bool writer = new_tile >= j_begin && new_tile < j_end;
+      const int n_rows = p.group + (writer ? 2 : 0);        // the group's query heads, then k, then v
+      const int l16 = lane & 15;
+      const int e0 = VE * l16;
+      const int pos = kv_len - 1;
+      for (int r0 = q * 2; r0 < n_rows; r0 += 8) {
+        const int r = r0 + (lane >> 4);
+        const bool live = r < n_rows;
+        const int rr = live ? r : 0;
+        const bool is_q = rr < p.group, is_k = rr == p.group;
+        const int col = (is_q ? hk * p.group + rr : (is_k ? p.Hq + hk : p.Hq + p.Hkv + hk)) * D;
+        float x1[VE], x2[VE];
+#pragma unroll
+        for (int i = 0; i < VE; ++i) { x1[i] = 0.f; x2[i] = 0.f; }
+        for (int sp = 0; sp < p.qkv_splits; ++sp) {
+          const float* src = p.qkv_part + ((int64_t)sp * p.B + b) * p.n_qkv + col;
+          if constexpr (VE == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(src + e0);
+            const float4 c = *reinterpret_cast<const float4*>(src + HALF + e0);
+            x1[0] += a.x; x1[1] += a.y; x1[2] += a.z; x1[3] += a.w;
+            x2[0] += c.x; x2[1] += c.y; x2[2] += c.z; x2[3] += c.w;
+          } else {
+            const float2 a = *reinterpret_cast<const float2*>(src + e0);
+            const float2 c = *reinterpret_cast<const float2*>(src + HALF + e0);
+            x1[0] += a.x; x1[1] += a.y;
+            x2[0] += c.x; x2[1] += c.y;
+          }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VE; ++i) ss += x1[i] * x1[i] + x2[i] * x2[i];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // stays inside the 16-lane half
+        if (!live) continue;
+        if (is_q || is_k) {
+          const float sc = 1.0f / sqrtf(ss / (float)D + p.eps);
+          const __nv_bfloat16* w = is_q ? p.qw : p.kw;
+#pragma unroll
+          for (int i = 0; i < VE; ++i) {
+            const float y1 = (x1[i] * sc) * __bfloat162float(w[e0 + i]);
+            const float y2 = (x2[i] * sc) * __bfloat162float(w[HALF + e0 + i]);
+            const float cs = p.cos_t[e0 + i], sn = p.sin_t[e0 + i];
+            x1[i] = y1 * cs - y2 * sn;
+            x2[i] = y2 * cs + y1 * sn;
+          }
+        }
+        uint32_t o1[VE / 2], o2[VE / 2];
+#pragma unroll
+        for (int i = 0; i < VE; i += 2) {
+          __nv_bfloat162 t1 = __floats2bfloat162_rn(x1[i], x1[i + 1]), t2 = __floats2bfloat162_rn(x2[i], x2[i + 1]);
+          o1[i / 2] = *reinterpret_cast<uint32_t*>(&t1);
+          o2[i / 2] = *reinterpret_cast<uint32_t*>(&t2);
+        }
+        if (is_q) {
+          // row rr of the Q tile, 128-byte swizzle: 16-byte chunk c of a row sits at chunk (c ^ (row & 7))
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int d = half * HALF + e0;                       // first element this lane writes in this half
+            const int slab = d / 64, chunk = (d % 64) / 8, within = (d % 8) * 2;
+            uint8_t* dst = q_smem + slab * Q_SLAB + rr * 128 + ((chunk ^ (rr & 7)) * 16) + within;
+            const uint32_t* ov = half ? o2 : o1;
+#pragma unroll
+            for (int i = 0; i < VE / 2; ++i) reinterpret_cast<uint32_t*>(dst)[i] = ov[i];
+          }
+        } else if (pos >= 0 && pos < p.max_s) {
+          __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) + (int64_t)b * p.kc_b + (int64_t)hk * p.kc_h + (int64_t)pos * p.kc_s;
+#pragma unroll
+          for (int i = 0; i < VE / 2; ++i) {
+            reinterpret_cast<uint32_t*>(dst + e0)[i] = o1[i];
+            reinterpret_cast<uint32_t*>(dst + HALF + e0)[i] = o2[i];
+          }
+        } else if (l16 == 0 && atomicCAS(p.err, 0, 102) == 0) {   // never write outside the cache; report instead
+          p.err[1] = pos; p.err[2] = p.max_s;
+        }
+      }
+      // rows of the 16-row tile beyond the group are padding: zero them (TMA would have)
+      for (int i = threadIdx.x - 64; i < (QROWS - p.group) * (D * 2 / 16); i += 128) {
+        const int rrow = p.group + i / (D * 2 / 16), ch = i % (D * 2 / 16);
+        const int slab = ch / 8, chunk = ch % 8;
+        *reinterpret_cast<uint4*>(q_smem + slab * Q_SLAB + rrow * 128 + ((chunk ^ (rrow & 7)) * 16)) = make_uint4(0, 0, 0, 0);
+      }
+      fence_async_proxy();                                  // Q tile: generic writes -> tcgen05.mma reads
+      if (writer) asm volatile("fence.proxy.async;" ::: "memory");   // cache row: generic writes -> TMA reads
+      __threadfence_block();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(q_full);
+        if (writer) mbar_arrive(kv_ready);
+      }
+}
+
 template <int D, bool DECODE>
 __global__ void __launch_bounds__(DECODE ? FA_THREADS : FA_THREADS_PREFILL, DECODE ? 2 : 1)
 flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                               const __grid_constant__ CUtensorMap tmap_v, FaParams p) {
+                               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FaParams p) {
   constexpr int SLABS = D / 64;                     // 64-wide head-dim slabs (one swizzle atom each)
   // Decode: only the first Hq/Hkv (<= 16) rows of the query tile are real, so only 16 rows are
   // staged; the MMA still reads 128 rows, the other 112 come from whatever follows in shared
@@ -149,7 +265,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     hk = blockIdx.y;
     h = hk;                     // Q tensor map is indexed by (row-in-group, kv head, batch)
     q0 = 0;
-    kv_len = p.ctx_ptr ? *p.ctx_ptr : p.Skv;
+    kv_len = p.qkv_part ? *p.pos_ptr + 1 : (p.ctx_ptr ? *p.ctx_ptr : p.Skv);
     kv_len = max(0, min(kv_len, p.Skv));
     kv_end = kv_len;
     const int n_total = (kv_len + FA_BKV - 1) / FA_BKV;
@@ -178,7 +294,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   const int n_blocks = j_end - j_begin;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(q_full, (DECODE && p.qkv_part) ? 4 : 1);   // fused prologue: the four softmax warps fill the Q tile
     for (int s = 0; s < NSLOT; ++s) { mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], 1); }
     for (int s = 0; s < NSBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4 * NWG); }
     for (int s = 0; s < 2; ++s) mbar_init(&x_bar[s], 4 * NWG);
@@ -201,10 +317,19 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, Q_BYTES);
+      const bool fused = DECODE && p.qkv_part != nullptr;
+      if (!fused) {
+        mbar_arrive_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-      for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * Q_SLAB, &tmap_q, q_full, s * 64, q0, h, b);
+        for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * Q_SLAB, &tmap_q, q_full, s * 64, q0, h, b);
+      }
+      const int new_tile = fused ? (kv_len - 1) / FA_BKV : -1;   // the tile that receives the new token's K/V row
       for (int jj = 0; jj < n_blocks; ++jj) {
+        if (fused && j_begin + jj == new_tile) {
+          // the softmax warps of this CTA write that row (generic proxy) before TMA may read the tile
+          if (!mbar_wait(&x_bar[0], 0, abort_flag, p.err, 312)) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         // key-tile coordinates: rows j*128.. of sequence b, or row 0 of the page the block table names
         int row = (j_begin + jj) * FA_BKV, outer = b;
         if (DECODE && p.block_table) {
@@ -288,6 +413,8 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     const int row_in_tile = q * 32 + lane;
     const int row = q0 + row_in_tile;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    if (DECODE && p.qkv_part)
+      decode_qkv_prologue<D>(p, q_smem, Q_SLAB, QROWS, b, hk, kv_len, j_begin, j_end, q, lane, q_full, &x_bar[0]);
     float m_used = -1e30f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
@@ -602,10 +729,13 @@ size_t attention_decode_scratch_bytes(int B, int Hkv, int group, int splits, int
 // with block_table [B,max_pages]; out [B,Hq,1,D].  `scratch` holds the split partials.
 int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
                      const int* ctx_dev, int ctx_host, const int* block_table, int max_pages, int splits,
-                     void* scratch, size_t scratch_bytes) {
+                     void* scratch, size_t scratch_bytes, const DecodeQkvSource* qkv) {
+  // with a QKV source there is no Q tensor: `out` [B,Hq,1,D] stands in for its shape
+  if (qkv) q = out;
   KD_REQUIRE(q->ndim == 4 && k->ndim == 4 && v->ndim == 4 && out->ndim == 4, "attention_decode: operands must be 4-D");
   KD_REQUIRE(q->dtype == KD_BF16 && k->dtype == KD_BF16 && v->dtype == KD_BF16 && out->dtype == KD_BF16,
              "attention_decode: bf16 tensors required");
+  KD_REQUIRE(!qkv || (!block_table && ctx_dev == nullptr), "attention_decode: the fused QKV source needs the contiguous cache and takes the context from the position");
   const int B = (int)q->shape[0], Hq = (int)q->shape[1], D = (int)q->shape[3];
   const int Hkv = (int)k->shape[1];
   KD_REQUIRE(q->shape[2] == 1 && out->shape[2] == 1, "attention_decode: exactly one query position per sequence");
@@ -624,7 +754,7 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
     KD_REQUIRE(k->shape[0] == B, "attention_decode: cache batch differs from the query batch");
     Skv = (int)k->shape[2];
   }
-  if (!ctx_dev) KD_REQUIRE(ctx_host >= 1 && ctx_host <= Skv, "attention_decode: context length %d outside [1,%d]", ctx_host, Skv);
+  if (!ctx_dev && !qkv) KD_REQUIRE(ctx_host >= 1 && ctx_host <= Skv, "attention_decode: context length %d outside [1,%d]", ctx_host, Skv);
   KD_REQUIRE(q->strides[3] == 1 && k->strides[3] == 1 && v->strides[3] == 1 && out->strides[3] == 1,
              "attention_decode: unit stride along head_dim required");
   for (int i = 0; i < 3; ++i)
@@ -644,11 +774,25 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   const int64_t sq[3] = {q->strides[0], q->strides[1] * group, q->strides[1]};
   const int64_t ek[4] = {k->shape[0], Hkv, k->shape[2], D};
   CUtensorMap tq, tk, tv;
-  KD_TRY(make_tmap_bhsd(&tq, pq, eq, sq, 16));
   KD_TRY(make_tmap_bhsd(&tk, pk, ek, k->strides, FA_BKV));
+  if (qkv) tq = tk;   // unused by the kernel in this mode
+  else KD_TRY(make_tmap_bhsd(&tq, pq, eq, sq, 16));
   KD_TRY(make_tmap_bhsd(&tv, pv, ek, v->strides, FA_BKV));
   FaParams p{};
-  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = group; p.Skv = ctx_dev ? Skv : ctx_host;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = group; p.Skv = (ctx_dev || qkv) ? Skv : ctx_host;
+  if (qkv) {
+    KD_REQUIRE(qkv->splits >= 1 && qkv->n_qkv == (Hq + 2 * Hkv) * D, "attention_decode: QKV partials must have (Hq + 2 Hkv) * D columns");
+    KD_REQUIRE((reinterpret_cast<uintptr_t>(qkv->partials) & 15) == 0 && k->strides[2] % 2 == 0 && v->strides[2] % 2 == 0,
+               "attention_decode: QKV partials / cache rows must be 16- / 4-byte aligned");
+    KD_REQUIRE(v->strides[0] == k->strides[0] && v->strides[1] == k->strides[1] && v->strides[2] == k->strides[2],
+               "attention_decode: K and V caches must share their strides");
+    p.qkv_part = qkv->partials; p.qkv_splits = qkv->splits; p.n_qkv = qkv->n_qkv;
+    p.qw = static_cast<const __nv_bfloat16*>(qkv->q_norm_w); p.kw = static_cast<const __nv_bfloat16*>(qkv->k_norm_w);
+    p.eps = qkv->eps; p.cos_t = qkv->cos_t; p.sin_t = qkv->sin_t; p.pos_ptr = qkv->pos_dev;
+    p.k_cache = static_cast<__nv_bfloat16*>(pk); p.v_cache = static_cast<__nv_bfloat16*>(pv);
+    p.kc_b = k->strides[0]; p.kc_h = k->strides[1]; p.kc_s = k->strides[2];
+    p.max_s = Skv;
+  }
   p.causal = 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = ctx().error_flag;

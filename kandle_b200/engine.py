@@ -96,6 +96,7 @@ class Qwen3Engine:
         # decode: run o_proj .. next layer's QKV as one persistent kernel per layer (kd_decode_layer_chain);
         # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
         self.use_chain = self.tp == 1 and self.H <= 4096
+        self.fuse_rope_into_attention = False   # verified on the GPU before it becomes the default
         self.sampler = None   # None: greedy argmax; else dict(temperature, top_k, top_p, rng), see set_sampler
 
     # ------------------------------------------------------------------ helpers
@@ -295,9 +296,14 @@ class Qwen3Engine:
             vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
             if li == 0 or not d["chain"]:
                 lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wqkv"]), 0, _r(d["qkv_p"]))
-            lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
-                     _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
-            lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
+            if d["chain"] and self.fuse_rope_into_attention:
+                # q/k-norm + RoPE + cache write happen inside the attention kernel, under its first key tiles
+                lib.call("kd_attention_decode_qkv", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
+                         _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), ctypes.c_float(self.scale), 0, _r(o_bh1d))
+            else:
+                lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
+                         _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
+                lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
             nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
             if d["chain"]:
                 last = li + 1 == self.L
