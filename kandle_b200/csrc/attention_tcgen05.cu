@@ -140,18 +140,31 @@ __device__ __noinline__ void decode_qkv_prologue(const FaParams& p, uint8_t* q_s
         float x1[VE], x2[VE];
 #pragma unroll
         for (int i = 0; i < VE; ++i) { x1[i] = 0.f; x2[i] = 0.f; }
-        for (int sp = 0; sp < p.qkv_splits; ++sp) {
-          const float* src = p.qkv_part + ((int64_t)sp * p.B + b) * p.n_qkv + col;
-          if constexpr (VE == 4) {
-            const float4 a = *reinterpret_cast<const float4*>(src + e0);
-            const float4 c = *reinterpret_cast<const float4*>(src + HALF + e0);
-            x1[0] += a.x; x1[1] += a.y; x1[2] += a.z; x1[3] += a.w;
-            x2[0] += c.x; x2[1] += c.y; x2[2] += c.z; x2[3] += c.w;
-          } else {
-            const float2 a = *reinterpret_cast<const float2*>(src + e0);
-            const float2 c = *reinterpret_cast<const float2*>(src + HALF + e0);
-            x1[0] += a.x; x1[1] += a.y;
-            x2[0] += c.x; x2[1] += c.y;
+        // four splits per round: all their loads are in flight together (the sums keep split order)
+        for (int sp0 = 0; sp0 < p.qkv_splits; sp0 += 4) {
+          float a1[4][VE], a2[4][VE];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int sp = min(sp0 + u, p.qkv_splits - 1);
+            const float* src = p.qkv_part + ((int64_t)sp * p.B + b) * p.n_qkv + col;
+            if constexpr (VE == 4) {
+              const float4 a = *reinterpret_cast<const float4*>(src + e0);
+              const float4 c = *reinterpret_cast<const float4*>(src + HALF + e0);
+              a1[u][0] = a.x; a1[u][1] = a.y; a1[u][2] = a.z; a1[u][3] = a.w;
+              a2[u][0] = c.x; a2[u][1] = c.y; a2[u][2] = c.z; a2[u][3] = c.w;
+            } else {
+              const float2 a = *reinterpret_cast<const float2*>(src + e0);
+              const float2 c = *reinterpret_cast<const float2*>(src + HALF + e0);
+              a1[u][0] = a.x; a1[u][1] = a.y;
+              a2[u][0] = c.x; a2[u][1] = c.y;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (sp0 + u < p.qkv_splits) {
+#pragma unroll
+              for (int i = 0; i < VE; ++i) { x1[i] += a1[u][i]; x2[i] += a2[u][i]; }
+            }
           }
         }
         float ss = 0.f;
@@ -208,7 +221,12 @@ __device__ __noinline__ void decode_qkv_prologue(const FaParams& p, uint8_t* q_s
         *reinterpret_cast<uint4*>(q_smem + slab * Q_SLAB + rrow * 128 + ((chunk ^ (rrow & 7)) * 16)) = make_uint4(0, 0, 0, 0);
       }
       fence_async_proxy();                                  // Q tile: generic writes -> tcgen05.mma reads
-      if (writer) asm volatile("fence.proxy.async;" ::: "memory");   // cache row: generic writes -> TMA reads
+      if (writer) {
+        // cache row: generic-proxy stores that a TMA load (async proxy, served from L2) of this CTA reads
+        // next: make them visible device-wide first, then order the two proxies
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       __threadfence_block();
       __syncwarp();
       if (lane == 0) {

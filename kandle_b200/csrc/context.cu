@@ -140,26 +140,34 @@ int tensor_ptr(const kd_tensor* t, void** out) {
   return KD_OK;
 }
 
+// Scratch buffers that were outgrown.  They are kept until kd_shutdown instead of being freed at
+// once: a captured CUDA graph may still hold their address (decode attention
+// partial sums, chain partial sums, sampling probabilities), and kernels already enqueued may
+// still use them.  Sizes grow by 1.5x, so the retired buffers sum to less than three times the last.
+static std::vector<void*> g_retired_workspaces;
+
 int get_workspace(uint64_t bytes, void** out) {
   Context& c = ctx();
   if (bytes > c.workspace_bytes) {
-    // Growing frees the old buffer; earlier kernels on the stream may still use it, so drain.
-    if (c.workspace) {
-      KD_CUDA_CHECK(cudaStreamSynchronize(c.stream));
-      KD_CUDA_CHECK(cudaFree(c.workspace));
-      c.workspace = nullptr;
-      c.workspace_bytes = 0;
-    }
     const uint64_t want = Allocator::round_size(bytes + bytes / 2);
-    cudaError_t e = cudaMalloc(&c.workspace, want);
+    void* fresh = nullptr;
+    cudaError_t e = cudaMalloc(&fresh, want);
     if (e != cudaSuccess) {
       cudaGetLastError();
       return fail(KD_ERR_OOM, "workspace allocation of %llu bytes failed", (unsigned long long)want);
     }
+    if (c.workspace) g_retired_workspaces.push_back(c.workspace);
+    c.workspace = fresh;
     c.workspace_bytes = want;
   }
   *out = c.workspace;
   return KD_OK;
+}
+
+// Frees the outgrown scratch buffers (shutdown only: no graph built before can run afterwards).
+static void release_retired_workspaces() {
+  for (void* p : g_retired_workspaces) cudaFree(p);
+  g_retired_workspaces.clear();
 }
 
 }  // namespace kd
@@ -227,6 +235,7 @@ KD_API int kd_shutdown(void) {
   if (c.workspace) cudaFree(c.workspace);
   c.workspace = nullptr;
   c.workspace_bytes = 0;
+  release_retired_workspaces();
   cudaFree(c.error_flag);
   cudaStreamDestroy(c.stream);
   c = Context();

@@ -96,7 +96,7 @@ class Qwen3Engine:
         # decode: run o_proj .. next layer's QKV as one persistent kernel per layer (kd_decode_layer_chain);
         # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
         self.use_chain = self.tp == 1 and self.H <= 4096
-        self.fuse_rope_into_attention = False   # verified on the GPU before it becomes the default
+        self.fuse_rope_into_attention = True
         self.sampler = None   # None: greedy argmax; else dict(temperature, top_k, top_p, rng), see set_sampler
 
     # ------------------------------------------------------------------ helpers

@@ -99,7 +99,9 @@ def test_decode_attention_rejects_bad_arguments(backend):
 ])
 def test_decode_attention_with_fused_qkv_prologue(backend, b, hq, hkv, max_s, pos, d, splits, qkv_splits):
     """kd_attention_decode_qkv = kd_qkv_norm_rope_cachewrite + kd_attention_decode: the cache rows it
-    writes and its output must equal the two-kernel sequence bit for bit (same arithmetic, same order)."""
+    writes must equal the two-kernel sequence bit for bit, its output up to the compiler's choice of
+    fused multiply-adds in the two copies of the q-norm/RoPE arithmetic (a last-bit difference in one
+    head's scale can flip the bf16 rounding of a query element: measured, one output row in 512)."""
     n_qkv = (hq + 2 * hkv) * d
     part = synth.normal("fq-part", (qkv_splits, b, n_qkv), 0.7)
     qw = lib.round_to_bf16(1.0 + synth.normal("fq-qw", (d,), 0.1))
@@ -129,7 +131,9 @@ def test_decode_attention_with_fused_qkv_prologue(backend, b, hq, hkv, max_s, po
     backend.synchronize()
     assert np.array_equal(k2.dataAsync(), k1.dataAsync()) and np.array_equal(v2.dataAsync(), v1.dataAsync())
     assert not np.array_equal(k2.dataAsync()[:, :, pos], kc0[:, :, pos])        # the row was really written
-    assert np.array_equal(o2.dataAsync(), o1.dataAsync())
+    a, c = o2.dataAsync(), o1.dataAsync()
+    rows_differ = (np.abs(a - c).max(-1) > 0).mean()
+    assert np.abs(a - c).max() <= 2.0 ** -7 * np.abs(c).max() and rows_differ <= 0.01
 
 
 def test_fused_qkv_prologue_reports_a_position_outside_the_cache(backend):

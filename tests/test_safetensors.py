@@ -101,7 +101,7 @@ def test_sharded_index(tmp_path):
 def test_native_bf16_upload_and_module_loading(backend, oracle, tmp_path):
     from kandle_b200.model_utils import Qwen3Config, Qwen3ForCausalLM
     from kandle_b200.core import Tensor
-    dims = dict(vocab=97, hidden=64, inter=96, layers=2, heads=4, kv_heads=2, head_dim=32)
+    dims = dict(vocab=96, hidden=64, inter=96, layers=2, heads=2, kv_heads=1, head_dim=64)
     w = synth.qwen3_weights(std=0.1, norm_jitter=0.05, **dims)
     bits = {k: (lib.f32_to_bf16_bits(v), "BF16") for k, v in w.items()}
     p = str(tmp_path / "qwen.safetensors")
@@ -109,19 +109,19 @@ def test_native_bf16_upload_and_module_loading(backend, oracle, tmp_path):
     g = kio.loadSafetensor(p)
     lay = g.getLayer("model.embed_tokens.weight")
     t = kio.tensorFromSafetensorLayer(lay)                      # stays bf16 on the device
-    assert t.dtype == "bfloat16" and t.shape == (97, 64)
+    assert t.dtype == "bfloat16" and t.shape == (96, 64)
     assert np.array_equal(t.dataAsync(), lay.to_float32())
     t32 = kio.tensorFromSafetensorLayer(lay, "float32")         # the reference's behaviour on request
     assert t32.dtype == "float32" and np.array_equal(t32.dataAsync(), lay.to_float32())
-    cfg = Qwen3Config(vocabSize=97, hiddenSize=64, intermediateSize=96, numHiddenLayers=2, numAttentionHeads=4,
-                      numKeyValueHeads=2, headDim=32)
+    cfg = Qwen3Config(vocabSize=96, hiddenSize=64, intermediateSize=96, numHiddenLayers=2, numAttentionHeads=2,
+                      numKeyValueHeads=1, headDim=64)
     model = Qwen3ForCausalLM(cfg)
     res = kio.loadModuleFromSafetensor(model, g, keyMapper=lambda k: None if k == "lm_head.weight" else k, strict=False)
     assert set(res["missingKeys"]) <= {"lm_head.weight"} and not res["unexpectedKeys"]
-    ids = synth.token_ids("st.ids", (2, 9), 97)
+    ids = synth.token_ids("st.ids", (2, 9), 96)
     wr = {k: lib.round_to_bf16(v) for k, v in w.items()}
-    ocfg = oracle.Qwen3Config(vocab_size=97, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
-                              num_key_value_heads=2, head_dim=32)
+    ocfg = oracle.Qwen3Config(vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=2,
+                              num_key_value_heads=1, head_dim=64)
     ref = oracle.Qwen3Oracle(ocfg, wr).logits(ids)
     got = model.forward(Tensor(ids)).dataAsync()
     assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()
@@ -129,8 +129,8 @@ def test_native_bf16_upload_and_module_loading(backend, oracle, tmp_path):
         kio.loadModuleFromSafetensor(model, g, keyMapper=lambda k: k + ".nope")
     # the fused engine straight from the checkpoint
     from kandle_b200.engine import Qwen3Engine
-    ecfg = Qwen3Config(vocabSize=97, hiddenSize=64, intermediateSize=96, numHiddenLayers=2, numAttentionHeads=4,
-                       numKeyValueHeads=2, headDim=32, dtype="bfloat16")
+    ecfg = Qwen3Config(vocabSize=96, hiddenSize=64, intermediateSize=96, numHiddenLayers=2, numAttentionHeads=2,
+                       numKeyValueHeads=1, headDim=64, dtype="bfloat16")
     eng = Qwen3Engine(ecfg, kio.SafetensorStateDict(g), 2, 32)
     _, logits = eng.prefill(ids, all_logits=True)
     assert np.abs(logits.dataAsync() - ref).max() <= 3e-2 * max(1.0, np.abs(ref).max())
