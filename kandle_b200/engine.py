@@ -3,13 +3,13 @@ tcgen05 flash attention, split-KV decode attention and a CUDA-graph decode step.
 
 It computes what `Qwen3ForCausalLM.forwardWithKVCache` + greedy argmax compute on the eager path
 (packages/model-utils/src/qwen3/for_causal_lm.ts:170-194,475-508), with the ~41 backend calls per
-layer collapsed into 7 (prefill) / 3 (decode) kernels and no intermediate copies:
+layer collapsed into 7 (prefill) / 2 (decode) kernels and no intermediate copies:
 
   prefill, per layer     rms_norm -> QKV GEMM (epilogue: q/k-norm+RoPE+cache write) -> flash attention ->
                          o_proj GEMM (+residual) -> rms_norm -> gate/up GEMM (SiLU*up epilogue) ->
                          down GEMM (+residual)
-  decode step, per layer norm+RoPE+cache write (sums the QKV split-K partials) -> split-KV attention ->
-                         one persistent kernel: o_proj -> residual+rms_norm -> gate/up with SiLU*up
+  decode step, per layer split-KV attention whose prologue sums the QKV split-K partials and does q/k-norm,
+                         RoPE and the cache write -> one persistent kernel: o_proj -> residual+rms_norm -> gate/up with SiLU*up
                          -> down -> residual+rms_norm -> the NEXT layer's QKV partials
                          (tensor parallel: the same steps as separate kernels, with all-reduces)
   The decode step reads the write position / context length from device memory, so one captured
