@@ -93,6 +93,7 @@ struct FaParams {
   float* part_o;               // [B, Hkv, splits, group, D] un-normalised partial outputs
   float* part_ml;              // [B, Hkv, splits, group, 2] (running max in the log2 domain, sum)
   int direct;                  // splits == 1: write O/l as bf16 straight to `o` (no combine kernel)
+  int colsplit;                // decode, group <= 8: each softmax warp handles a quarter of the key columns (see kernel)
   // Fused decode prologue (qkv_part != NULL): Q and the new token's K/V cache row are produced here
   // from the split-K partial sums of the QKV projection: q/k RMSNorm over head_dim, RoPE, bf16.
   const float* qkv_part;       // [qkv_splits][B][n_qkv] fp32, columns: q heads, k heads, v heads
@@ -383,8 +384,10 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t qoff = (uint32_t)((k / 4) * Q_SLAB + (k % 4) * 32);
           const uint32_t koff = (uint32_t)((k / 4) * SLAB_BYTES + (k % 4) * 32);
-          umma_ss(d_tmem, make_smem_desc_sw128(q_addr + qoff, 16, 1024), make_smem_desc_sw128(k_addr + koff, 16, 1024),
-                  IDESC_QK, k != 0 ? 1u : 0u);
+          // colsplit: a stride of 0 between the 8-row groups of the A tile makes every group read rows
+          // 0-7 of the Q tile, i.e. query r appears in S rows r, 8 + r, ..., 120 + r
+          umma_ss(d_tmem, make_smem_desc_sw128(q_addr + qoff, 16, (DECODE && p.colsplit) ? 0u : 1024u),
+                  make_smem_desc_sw128(k_addr + koff, 16, 1024), IDESC_QK, k != 0 ? 1u : 0u);
         }
         umma_commit(&t_empty[stage]);
         umma_commit(&s_full[j % NSBUF]);
@@ -433,6 +436,162 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     if (DECODE && p.qkv_part)
       decode_qkv_prologue<D>(p, q_smem, Q_SLAB, QROWS, b, hk, kv_len, j_begin, j_end, q, lane, q_full, &x_bar[0]);
+    bool colsplit_done = false;
+    if constexpr (DECODE) {
+      if (p.colsplit) {
+        // Decode with at most 8 query heads per KV head.  One thread per S row would leave 120 of the
+        // 128 softmax threads on padding rows and the valid rows' threads with 128 exponentials each:
+        // the per-tile latency of that serial row, not HBM, then limits a CTA to ~21 GB/s.  Here the Q
+        // tile is replicated into every 8-row group (descriptor stride 0), so query r is S row 32 w + r
+        // in the lanes of EVERY softmax warp w, and warp w handles key columns [32 w, 32 w + 32) of it:
+        // 32 exponentials per thread.  The row maximum is exchanged through shared memory once per
+        // tile; each warp writes its 32 probabilities into its own rows of P and zeros elsewhere, so
+        // that the P V product leaves a partial O per warp in rows 32 w + r, summed in the epilogue.
+        colsplit_done = true;
+        float* xm = xchg;                 // [2 buffers][4 quarters][32 lanes] row maxima
+        float* xl = xchg + 256;           // [4 quarters][32 lanes] row sums
+        float* xmu = xchg + 384;          // [32 lanes] the running maximum each row ended with
+        float m_used = -1e30f, l = 0.f;
+        bool ok = true;
+        const uint32_t s_addr = lane_addr + S_COL0;
+        // No thread leaves this loop between the 128-thread barriers except right after one, where
+        // all of them see the same abort flag (every failed wait raises it).
+        for (int j = 0; j < n_blocks; ++j) {
+          ok = mbar_wait(&s_full[0], (uint32_t)(j & 1), abort_flag, p.err, 307);
+          ok = __all_sync(0xffffffffu, ok);
+          uint32_t sr[32];
+          float* slot = xm + (j & 1) * 128;
+          if (ok) {
+            tc_fence_after();
+            tmem_ld_32x32(s_addr + q * 32, sr);
+            tmem_wait_ld();
+            const int kv0 = (j_begin + j) * FA_BKV + q * 32;
+            if (kv0 + 32 > kv_end) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (kv0 + i >= kv_len) sr[i] = __float_as_uint(-1e30f);
+            }
+            float mx0 = -1e30f, mx1 = -1e30f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])));
+              mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])));
+            }
+            slot[q * 32 + lane] = fmaxf(mx0, mx1);
+          }
+          asm volatile("bar.sync 2, 128;" ::: "memory");        // the four softmax warps
+          if (*abort_flag) { ok = false; break; }
+          const float m_blk = fmaxf(fmaxf(slot[lane], slot[32 + lane]), fmaxf(slot[64 + lane], slot[96 + lane])) * p.scale_log2;
+          float alpha = 1.f;
+          bool rescale = false;
+          if (j == 0 || lane >= p.group) {
+            m_used = m_blk;          // first block; or a padding row, whose values nobody reads
+          } else if (m_blk - m_used > 8.0f) {
+            alpha = fast_exp2(m_used - m_blk);
+            m_used = m_blk;
+            rescale = true;
+          }
+          // the four threads of a row see the same maxima, hence take the same decision; warps may
+          // differ in whether ANY of their rows rescales, which only affects their own O rows
+          if (__any_sync(0xffffffffu, rescale)) {
+            ok = mbar_wait(o_done, (uint32_t)((j - 1) & 1), abort_flag, p.err, 308);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) continue;     // the abort flag is up: everybody leaves after the next barrier
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st_32x32(lane_addr + O_COL0 + c * 32, orr);
+            }
+            l *= alpha;
+          }
+          // P row: this warp's 32 probabilities in packed columns [16 q, 16 q + 16), zeros in the rest
+          float sum0 = 0.f, sum1 = 0.f;
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), p.scale_log2, -m_used));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), p.scale_log2, -m_used));
+            sum0 += p0;
+            sum1 += p1;
+            __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+            pk[i] = *reinterpret_cast<uint32_t*>(&v);
+          }
+          l += sum0 + sum1;
+          uint32_t zero[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) zero[i] = 0u;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_st_32x16(s_addr + c * 16, c == q ? pk : zero);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_ready[0]);
+        }
+        if (ok) {
+          ok = mbar_wait(o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, p.err, 309);
+          ok = __all_sync(0xffffffffu, ok);
+        }
+        // Epilogue: sum the four partial O rows and row sums of every query through shared memory
+        // (the K/V ring is idle now: every tile has landed and every MMA has completed).
+        float* osum = reinterpret_cast<float*>(ring);        // [4 quarters][8 rows][D]
+        if (ok) {
+          tc_fence_after();
+          xl[q * 32 + lane] = l;
+          if (q == 0) xmu[lane] = m_used;   // identical in the four threads of a row
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld_32x32(lane_addr + O_COL0 + c * 32, orr);
+            tmem_wait_ld();
+            if (lane < p.group) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                *reinterpret_cast<float4*>(osum + (q * 8 + lane) * D + c * 32 + g * 4) =
+                    make_float4(__uint_as_float(orr[g * 4]), __uint_as_float(orr[g * 4 + 1]), __uint_as_float(orr[g * 4 + 2]),
+                                __uint_as_float(orr[g * 4 + 3]));
+            }
+          }
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ok && *abort_flag == 0) {
+          // 128 threads: thread t handles query row t / 16 (8 rows) and D/16 consecutive columns
+          const int t = (warp - 2) * 32 + lane;
+          const int r = t >> 4, cw = D / 16, c0 = (t & 15) * cw;
+          if (r < p.group) {
+            const float lsum = xl[r] + xl[32 + r] + xl[64 + r] + xl[96 + r];
+            float acc[D / 16];
+#pragma unroll
+            for (int i = 0; i < cw; ++i)
+              acc[i] = osum[(0 * 8 + r) * D + c0 + i] + osum[(1 * 8 + r) * D + c0 + i] + osum[(2 * 8 + r) * D + c0 + i] +
+                       osum[(3 * 8 + r) * D + c0 + i];
+            if (p.direct) {
+              const float inv_l = 1.0f / lsum;
+              __nv_bfloat16* orow = p.o + (int64_t)b * p.so_b + (int64_t)(hk * p.group + r) * p.so_h + c0;
+#pragma unroll
+              for (int i = 0; i < cw; i += 2) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(acc[i] * inv_l, acc[i + 1] * inv_l);
+                *reinterpret_cast<__nv_bfloat162*>(orow + i) = v;
+              }
+            } else {
+              const int64_t slot_o = (((int64_t)b * p.Hkv + hk) * p.splits + blockIdx.x) * p.group + r;
+              if ((t & 15) == 0) {
+                p.part_ml[slot_o * 2] = xmu[r];
+                p.part_ml[slot_o * 2 + 1] = lsum;
+              }
+              float* prow = p.part_o + slot_o * D + c0;
+#pragma unroll
+              for (int i = 0; i < cw; ++i) prow[i] = acc[i];
+            }
+          }
+        }
+      }
+    }
+    if (!colsplit_done) {
     float m_used = -1e30f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
@@ -619,6 +778,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         }
       }
     }
+    }   // !colsplit_done
   }
 
   tc_fence_before();
@@ -822,6 +982,9 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   p.part_o = static_cast<float*>(scratch);
   p.part_ml = p.part_o + (size_t)B * Hkv * splits * group * D;
   // one split and a 16-byte aligned output: the attention kernel writes the result itself
+  // column-split softmax: the Q tile is replicated into every 8-row group, so at most 8 query heads per KV head
+  static const bool no_colsplit = [] { const char* e = getenv("KD_DECODE_NO_COLSPLIT"); return e && e[0] == '1'; }();
+  p.colsplit = (group <= 8 && !no_colsplit) ? 1 : 0;
   p.direct = (splits == 1 && (reinterpret_cast<uintptr_t>(po) & 15) == 0 && out->strides[0] % 8 == 0 && out->strides[1] % 8 == 0) ? 1 : 0;
   p.o = static_cast<__nv_bfloat16*>(po);
   p.so_b = out->strides[0]; p.so_h = out->strides[1]; p.so_s = out->strides[2];
