@@ -27,7 +27,10 @@
 // sequentially in double are exact integers here (they agree to ~1e-13, which can only matter when
 // a cumulative sum equals top_p or r to 13 digits); the top-10 list the reference returns for display
 // is not produced.  Bound: L2/HBM, two streaming passes, four radix passes when a filter is active
-// (warp-aggregated histogram updates), and two passes in which every thread walks its own segment.
+// (warp-aggregated histogram updates), and two passes in which every warp walks its own chunk; a
+// cluster of four CTAs shares one sequence so that four SMs' worth of loads are in flight per row.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -126,10 +129,19 @@ __device__ __forceinline__ void warp_hist_add_u32(unsigned int* hist, unsigned i
   if (d < 256u && (threadIdx.x & 31) == (unsigned)(__ffs(m) - 1)) atomicAdd(&hist[d], (unsigned int)__popc(m));
 }
 
+// One sequence = one thread-block cluster of NC CTAs (NC = 1: a single CTA).  CTA `rank` owns the
+// contiguous quarter [v0, v1) of the row; block-wide results are published in the CTA's shared memory,
+// one 16-byte slot per exchange site, and read by the other CTAs of the cluster through distributed
+// shared memory after a cluster barrier.  A slot is written once per launch, so one barrier per
+// exchange suffices; the histograms ping-pong between two sets for the same reason.
+template <int NC>
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
-  __shared__ unsigned long long hist_w[256];   // top-p walk: per-digit probability mass (fixed point)
-  __shared__ unsigned int hist_pc[256];        // top-p walk: per-digit element count
-  __shared__ unsigned int hist_kc[256];        // top-k walk: per-digit element count
+  namespace cg = cooperative_groups;
+  __shared__ unsigned long long hist_w[2][256];   // top-p walk: per-digit probability mass (fixed point)
+  __shared__ unsigned int hist_pc[2][256];        // top-p walk: per-digit element count
+  __shared__ unsigned int hist_kc[2][256];        // top-k walk: per-digit element count
+  __shared__ unsigned long long m_w[256];         // the histograms summed over the cluster
+  __shared__ unsigned int m_pc[256], m_kc[256];
   __shared__ double sh_d[32];
   __shared__ float sh_f[32];
   __shared__ unsigned long long sh_u[32];
@@ -138,10 +150,25 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
   __shared__ unsigned long long s_pw[2];       // remaining mass, mass of the chosen digit
   __shared__ unsigned int s_p[4];              // digit, elements above, elements in the digit, reached flag
   __shared__ int s_found;
+  __shared__ __align__(16) unsigned long long xs[12][2];   // exchange slots (two 8-byte words each)
 
-  const int row = blockIdx.x, tid = threadIdx.x, V = p.V;
+  const int tid = threadIdx.x, V = p.V;
+  int rank = 0;
+  if constexpr (NC > 1) rank = (int)cg::this_cluster().block_rank();
+  const int row = (int)blockIdx.x / NC;
+  auto cluster_sync = [&]() {
+    if constexpr (NC > 1) cg::this_cluster().sync();
+    else __syncthreads();
+  };
+  // word `w` of slot `site` as published by CTA `r` of the cluster
+  auto peer = [&](int site, int w, int r) -> unsigned long long {
+    if constexpr (NC > 1) return cg::this_cluster().map_shared_rank(&xs[site][w], r)[0];
+    else return xs[site][w];
+  };
   const float* lg = p.logits + (int64_t)row * p.ld;
   float* pr = p.probs + (int64_t)row * V;
+  const int Vq = (((V + NC - 1) / NC) + 3) & ~3;
+  const int v0 = min(V, rank * Vq), v1 = min(V, v0 + Vq), nv = v1 - v0;
   const bool greedy = !p.do_sample;
   const bool scale = !greedy && p.temperature != 1.0;
   const bool vec = (V % 4 == 0) && ((reinterpret_cast<uintptr_t>(lg) | reinterpret_cast<uintptr_t>(pr)) & 15) == 0;
@@ -150,14 +177,17 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
   // ---- pass 1: maximum (of the raw logits for greedy, of the scaled ones for sampling)
   float mx = -INFINITY;
   if (vec) {
-    for (int i = tid; i < V / 4; i += SMP_THREADS) {
+    for (int i = v0 / 4 + tid; i < v1 / 4; i += SMP_THREADS) {
       const float4 v = reinterpret_cast<const float4*>(lg)[i];
       mx = fmaxf(fmaxf(mx, fmaxf(scaled(v.x), scaled(v.y))), fmaxf(scaled(v.z), scaled(v.w)));
     }
   } else {
-    for (int i = tid; i < V; i += SMP_THREADS) mx = fmaxf(mx, scaled(lg[i]));
+    for (int i = v0 + tid; i < v1; i += SMP_THREADS) mx = fmaxf(mx, scaled(lg[i]));
   }
   mx = block_max(mx, sh_f);
+  if (tid == 0) xs[0][0] = __float_as_uint(mx);
+  cluster_sync();
+  for (int r = 0; r < NC; ++r) mx = fmaxf(mx, __uint_as_float((unsigned int)peer(0, 0, r)));
   // ---- pass 2: e_i = fl32(exp(.)) kept in `pr`; sum of the FLOAT values in double (the reference
   // sums the stored floats sequentially; the fixed tree order here differs by ~1e-16 relative)
   auto expo = [&](float x) {
@@ -166,7 +196,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
   };
   double sum_local = 0.0;
   if (vec) {
-    for (int i = tid; i < V / 4; i += SMP_THREADS) {
+    for (int i = v0 / 4 + tid; i < v1 / 4; i += SMP_THREADS) {
       const float4 v = reinterpret_cast<const float4*>(lg)[i];
       float4 e;
       e.x = expo(v.x); e.y = expo(v.y); e.z = expo(v.z); e.w = expo(v.w);
@@ -174,20 +204,24 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
       sum_local += (double)e.x + (double)e.y + (double)e.z + (double)e.w;
     }
   } else {
-    for (int i = tid; i < V; i += SMP_THREADS) {
+    for (int i = v0 + tid; i < v1; i += SMP_THREADS) {
       const float e = expo(lg[i]);
       pr[i] = e;
       sum_local += (double)e;
     }
   }
-  const double sum_exp = block_sum(sum_local, sh_d);
+  sum_local = block_sum(sum_local, sh_d);
+  if (tid == 0) xs[1][0] = (unsigned long long)__double_as_longlong(sum_local);
+  cluster_sync();
+  double sum_exp = 0.0;
+  for (int r = 0; r < NC; ++r) sum_exp += __longlong_as_double((long long)peer(1, 0, r));   // rank order: deterministic
   auto prob = [&](float e) { return (float)((double)e / sum_exp); };   // p_i = fl32(e_i / sum)
 
   if (greedy) {
     // argmax with the lowest index on ties = first element of the stable descending sort
     uint32_t bk = 0;
     int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += SMP_THREADS) {
+    for (int i = v0 + tid; i < v1; i += SMP_THREADS) {
       const uint32_t k = order_key(lg[i]);
       if (k > bk || (k == bk && i < bi)) { bk = k; bi = i; }
     }
@@ -205,21 +239,32 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
         const int i2 = sh_i[w];
         if (k2 > bk || (k2 == bk && i2 < bi)) { bk = k2; bi = i2; }
       }
-      p.out_ids[row] = bi;
-      if (p.out_logprob) p.out_logprob[row] = (float)log((double)prob(pr[bi]) + 1e-10);
+      xs[2][0] = bk;
+      xs[2][1] = (unsigned long long)(unsigned int)bi;
     }
+    cluster_sync();
+    if (tid == 0 && rank == 0) {
+      for (int r = 0; r < NC; ++r) {
+        const uint32_t k2 = (uint32_t)peer(2, 0, r);
+        const int i2 = (int)(unsigned int)peer(2, 1, r);
+        if (k2 > bk || (k2 == bk && i2 < bi)) { bk = k2; bi = i2; }
+      }
+      p.out_ids[row] = bi;
+      if (p.out_logprob) p.out_logprob[row] = (float)log((double)prob(__ldcg(pr + bi)) + 1e-10);
+    }
+    cluster_sync();      // nobody leaves while its shared memory may still be read
     return;
   }
 
   // ---- pass 3: p_i = fl32(e_i / sum)
   if (vec) {
-    for (int i = tid; i < V / 4; i += SMP_THREADS) {
+    for (int i = v0 / 4 + tid; i < v1 / 4; i += SMP_THREADS) {
       float4 e = reinterpret_cast<float4*>(pr)[i];
       e.x = prob(e.x); e.y = prob(e.y); e.z = prob(e.z); e.w = prob(e.w);
       reinterpret_cast<float4*>(pr)[i] = e;
     }
   } else {
-    for (int i = tid; i < V; i += SMP_THREADS) pr[i] = prob(pr[i]);
+    for (int i = v0 + tid; i < v1; i += SMP_THREADS) pr[i] = prob(pr[i]);
   }
   __syncthreads();
 
@@ -233,15 +278,17 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
   unsigned int gt_k = 0, eq_k = 0, gt_p = 0, eq_p = 0;
   unsigned long long w_digit_p = 0ull;
   bool p_reached = use_p;     // false: the whole mass stays below top_p (rounding), top-p keeps everything
-  for (int shift = 24; shift >= 0 && (use_k || use_p); shift -= 8) {
-    if (tid < 256) { hist_w[tid] = 0ull; hist_pc[tid] = 0u; hist_kc[tid] = 0u; }
+  int level = 0;
+  for (int shift = 24; shift >= 0 && (use_k || use_p); shift -= 8, ++level) {
+    const int hs = level & 1;
+    if (tid < 256) { hist_w[hs][tid] = 0ull; hist_pc[hs][tid] = 0u; hist_kc[hs][tid] = 0u; }
     __syncthreads();
-    const int n_iter = (V + SMP_THREADS - 1) / SMP_THREADS;
+    const int n_iter = (nv + SMP_THREADS - 1) / SMP_THREADS;
     for (int it = 0; it < n_iter; ++it) {        // every lane of a warp takes part in the warp-wide adds
-      const int i = it * SMP_THREADS + tid;
+      const int i = v0 + it * SMP_THREADS + tid;
       unsigned int dk = 256u, dp = 256u;
       unsigned long long w = 0ull;
-      if (i < V) {
+      if (i < v1) {
         const uint32_t k = order_key(lg[i]);
         if (use_k && (k & mask) == prefix_k) dk = (k >> shift) & 255u;
         if (use_p && p_reached && (k & mask) == prefix_p) {
@@ -250,16 +297,32 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
         }
       }
       if (__all_sync(0xffffffffu, dk == 256u && dp == 256u)) continue;   // no candidate in this warp
-      if (use_k) warp_hist_add_u32(hist_kc, dk);
-      if (use_p && p_reached) warp_hist_add_both(hist_pc, hist_w, dp, w);
+      if (use_k) warp_hist_add_u32(hist_kc[hs], dk);
+      if (use_p && p_reached) warp_hist_add_both(hist_pc[hs], hist_w[hs], dp, w);
+    }
+    cluster_sync();
+    // every CTA sums the cluster's histograms (integers: order-independent) and walks them itself
+    if (tid < 256) {
+      unsigned long long w = 0ull;
+      unsigned int pc = 0u, kc = 0u;
+      for (int r = 0; r < NC; ++r) {
+        if constexpr (NC > 1) {
+          w += cg::this_cluster().map_shared_rank(&hist_w[hs][tid], r)[0];
+          pc += cg::this_cluster().map_shared_rank(&hist_pc[hs][tid], r)[0];
+          kc += cg::this_cluster().map_shared_rank(&hist_kc[hs][tid], r)[0];
+        } else {
+          w += hist_w[hs][tid]; pc += hist_pc[hs][tid]; kc += hist_kc[hs][tid];
+        }
+      }
+      m_w[tid] = w; m_pc[tid] = pc; m_kc[tid] = kc;
     }
     __syncthreads();
     if (tid == 0 && use_k) {
       unsigned int above = 0;
       int d = 255;
       for (; d > 0; --d) {
-        if (above + hist_kc[d] >= rem_c) break;
-        above += hist_kc[d];
+        if (above + m_kc[d] >= rem_c) break;
+        above += m_kc[d];
       }
       s_k[0] = (unsigned)d; s_k[1] = rem_c - above; s_k[2] = above;
     }
@@ -269,19 +332,19 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
       int d = 255;
       bool hit = false;
       for (; d >= 0; --d) {
-        if (above + hist_w[d] >= rem_w) { hit = true; break; }
-        above += hist_w[d];
-        above_c += hist_pc[d];
+        if (above + m_w[d] >= rem_w) { hit = true; break; }
+        above += m_w[d];
+        above_c += m_pc[d];
       }
       s_p[3] = hit ? 1u : 0u;
-      if (hit) { s_p[0] = (unsigned)d; s_p[1] = above_c; s_p[2] = hist_pc[d]; s_pw[0] = rem_w - above; s_pw[1] = hist_w[d]; }
+      if (hit) { s_p[0] = (unsigned)d; s_p[1] = above_c; s_p[2] = m_pc[d]; s_pw[0] = rem_w - above; s_pw[1] = m_w[d]; }
     }
     __syncthreads();
     if (use_k) {
       prefix_k |= s_k[0] << shift;
       rem_c = s_k[1];
       gt_k += s_k[2];
-      eq_k = hist_kc[s_k[0]];
+      eq_k = m_kc[s_k[0]];
     }
     if (use_p && p_reached) {
       if (!s_p[3]) p_reached = false;
@@ -317,23 +380,28 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
   const bool filtered = f_eq != 0xffffffffu;
   const bool partial_tie = filtered && f_eq < f_eq_total;   // only some of the ties survive: rank them by index
 
-  // From here on every WARP owns one contiguous chunk of the row (a multiple of 32 elements, read
-  // 32 at a time), so that ranks and running sums in INDEX order need one scan over the 32 warps.
+  // From here on every WARP owns one contiguous chunk of this CTA's part of the row (a multiple of
+  // 32 elements, read 32 at a time), so that ranks and running sums in INDEX order need one scan over
+  // the warps of the CTA and one over the CTAs of the cluster.
   const int warp = tid >> 5, lane = tid & 31;
-  const int C = ((V + 31) / 32 + 31) / 32 * 32;
-  const int c0 = min(V, warp * C), c1 = min(V, c0 + C);
+  const int C = ((nv + 31) / 32 + 31) / 32 * 32;
+  const int c0 = min(v1, v0 + warp * C), c1 = min(v1, c0 + C);
   const unsigned int lt_mask = (1u << lane) - 1u;
 
   // ---- pass A: zero everything outside the prefix (pr <- p_i or 0), sum the survivors
   int eq_before = 0;
-  if (partial_tie) {
+  if (partial_tie) {      // (uniform over the cluster: every CTA derived the same thresholds)
     int cnt = 0;
     for (int i = c0 + lane; i < c1; i += 32) cnt += order_key(lg[i]) == fkey;
     for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
     __syncthreads();
     if (lane == 0) sh_i[warp] = cnt;
     __syncthreads();
-    for (int w = 0; w < warp; ++w) eq_before += sh_i[w];
+    int cta_total = 0;
+    for (int w = 0; w < 32; ++w) { if (w < warp) eq_before += sh_i[w]; cta_total += sh_i[w]; }
+    if (tid == 0) xs[4][0] = (unsigned long long)(unsigned int)cta_total;
+    cluster_sync();
+    for (int r = 0; r < rank; ++r) eq_before += (int)(unsigned int)peer(4, 0, r);
   }
   unsigned long long kept_w = 0ull;
   for (int b0 = c0; b0 < c1; b0 += 32) {
@@ -354,6 +422,10 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
     }
   }
   kept_w = block_sum(kept_w, sh_u);
+  if (tid == 0) xs[5][0] = kept_w;
+  cluster_sync();
+  kept_w = 0ull;
+  for (int r = 0; r < NC; ++r) kept_w += peer(5, 0, r);
   const double prob_sum = (double)kept_w / SMP_FIX;
   auto renorm = [&](float pi) { return prob_sum > 0.0 ? (float)((double)pi / prob_sum) : pi; };   // :217-222
 
@@ -367,15 +439,41 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
     if (q > 0.f) last_nonzero = i;
   }
   for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);   // this warp's chunk total
+  for (int o = 16; o > 0; o >>= 1) last_nonzero = max(last_nonzero, __shfl_xor_sync(0xffffffffu, last_nonzero, o));
   __syncthreads();
-  if (lane == 0) sh_d[warp] = local;
+  if (lane == 0) { sh_d[warp] = local; sh_i[warp] = last_nonzero; }
   if (tid == 0) s_found = 0x7fffffff;
   __syncthreads();
-  double before = 0.0;
-  for (int w = 0; w < warp; ++w) before += sh_d[w];
-  if (lane == 0 && r < before + local) atomicMin(&s_found, warp);   // the first chunk whose end passes r holds the token
+  double before = 0.0, cta_total = 0.0;
+  int cta_last = -1;
+  for (int w = 0; w < 32; ++w) {
+    if (w < warp) before += sh_d[w];
+    cta_total += sh_d[w];
+    cta_last = max(cta_last, sh_i[w]);
+  }
+  if (tid == 0) {
+    xs[6][0] = (unsigned long long)__double_as_longlong(cta_total);
+    xs[6][1] = (unsigned long long)(unsigned int)cta_last;
+  }
+  cluster_sync();
+  // the CTA whose cumulative end first passes r owns the token; every CTA evaluates the same sums
+  double cta_before = 0.0, run = 0.0;
+  int owner = -1, cluster_last = -1;
+  for (int rr = 0; rr < NC; ++rr) {
+    const double tot = __longlong_as_double((long long)peer(6, 0, rr));
+    if (rr < rank) cta_before += tot;
+    if (owner < 0 && r < run + tot) owner = rr;
+    run += tot;
+    cluster_last = max(cluster_last, (int)(unsigned int)peer(6, 1, rr));
+  }
+  if (owner == rank) {
+    before += cta_before;
+    if (lane == 0 && r < before + local) atomicMin(&s_found, warp);   // the first chunk whose end passes r holds the token
+  }
   __syncthreads();
-  if (s_found == warp) {
+  if (owner == rank && s_found == 0x7fffffff && tid == 0) s_found = 31;   // summation noise at the CTA's end: its last chunk
+  __syncthreads();
+  if (owner == rank && s_found == warp) {
     int tok = -1;
     double base = before;
     for (int b0 = c0; b0 < c1 && tok < 0; b0 += 32) {
@@ -389,30 +487,19 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleParams p) {
       if (hit) tok = b0 + __ffs(hit) - 1;
       base += __shfl_sync(0xffffffffu, v, 31);
     }
-    if (tok < 0) {   // summation-order noise at the very end of the chunk: its last non-zero element
-      int t = last_nonzero;
-      for (int o = 16; o > 0; o >>= 1) t = max(t, __shfl_xor_sync(0xffffffffu, t, o));
-      tok = t >= 0 ? t : c0;
-    }
+    if (tok < 0) tok = cta_last >= 0 ? cta_last : v0;   // summation-order noise at the very end: the last non-zero element
     if (lane == 0) {
       p.out_ids[row] = tok;
       if (p.out_logprob) p.out_logprob[row] = (float)log((double)renorm(pr[tok]) + 1e-10);
     }
   }
-  if (s_found == 0x7fffffff) {
+  if (owner < 0 && rank == 0 && tid == 0) {
     // r beyond the total (rounding): the last token with a non-zero probability, else 0 (:300-306)
-    for (int o = 16; o > 0; o >>= 1) last_nonzero = max(last_nonzero, __shfl_xor_sync(0xffffffffu, last_nonzero, o));
-    __syncthreads();
-    if (lane == 0) sh_i[warp] = last_nonzero;
-    __syncthreads();
-    int t = sh_i[lane];
-    for (int o = 16; o > 0; o >>= 1) t = max(t, __shfl_xor_sync(0xffffffffu, t, o));
-    if (tid == 0) {
-      const int tk = t < 0 ? 0 : t;
-      p.out_ids[row] = tk;
-      if (p.out_logprob) p.out_logprob[row] = (float)log((double)renorm(pr[tk]) + 1e-10);
-    }
+    const int tk = cluster_last < 0 ? 0 : cluster_last;
+    p.out_ids[row] = tk;
+    if (p.out_logprob) p.out_logprob[row] = (float)log((double)renorm(__ldcg(pr + tk)) + 1e-10);
   }
+  cluster_sync();      // nobody leaves while its shared memory may still be read
 }
 
 }  // namespace kd
@@ -453,6 +540,22 @@ KD_API int kd_sample(const kd_tensor* logits, double temperature, int top_k, dou
   p.probs = static_cast<float*>(scratch);
   p.out_ids = static_cast<int64_t*>(po);
   p.out_logprob = static_cast<float*>(plp);
-  sample_kernel<<<(unsigned)B, SMP_THREADS, 0, ctx().stream>>>(p);
+  // a cluster of four CTAs per sequence when that still fits the machine; a single CTA otherwise
+  if (B * 4 <= 4 * (int64_t)ctx().sm_count && V >= 16384) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(B * 4));
+    cfg.blockDim = dim3(SMP_THREADS);
+    cfg.stream = ctx().stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 4;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    KD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, sample_kernel<4>, p));
+  } else {
+    sample_kernel<1><<<(unsigned)B, SMP_THREADS, 0, ctx().stream>>>(p);
+  }
   return after_launch("sample_kernel");
 }
