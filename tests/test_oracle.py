@@ -340,3 +340,36 @@ def test_whisper_decoder_restatement_against_float64(oracle):
         x = x + y @ W[p + "fc2.weight"].T + W[p + "fc2.bias"]
     ref = ln(x, "layer_norm") @ W["embed_tokens.weight"].T
     assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()
+
+
+def test_mel_filterbank_against_an_independent_slaney_formulation():
+    """melscale_fbanks_host (mirror of audio/functional/filterbank.ts:88-150) against the textbook
+    construction of Slaney-scale, area-normalised triangular filters in float64."""
+    from kandle_b200 import audio
+    n_freqs, n_mels, sr, f_max = 201, 80, 16000, 8000.0
+    fb = audio.melscale_fbanks_host(n_freqs, 0.0, f_max, n_mels, sr, "slaney", "slaney")
+
+    def hz_to_mel(f):
+        f = np.asarray(f, dtype=np.float64)
+        lin = f / (200.0 / 3.0)
+        log = 15.0 + np.log(np.maximum(f, 1e-10) / 1000.0) / (np.log(6.4) / 27.0)
+        return np.where(f >= 1000.0, log, lin)
+
+    def mel_to_hz(m):
+        m = np.asarray(m, dtype=np.float64)
+        return np.where(m >= 15.0, 1000.0 * np.exp((np.log(6.4) / 27.0) * (m - 15.0)), m * (200.0 / 3.0))
+
+    edges = mel_to_hz(np.linspace(hz_to_mel(0.0), hz_to_mel(f_max), n_mels + 2))
+    freqs = np.linspace(0.0, sr / 2, n_freqs)
+    lower = (freqs[:, None] - edges[None, :-2]) / (edges[1:-1] - edges[:-2])[None, :]
+    upper = (edges[None, 2:] - freqs[:, None]) / (edges[2:] - edges[1:-1])[None, :]
+    ref = np.maximum(0.0, np.minimum(lower, upper)) * (2.0 / (edges[2:] - edges[:-2]))[None, :]
+    assert fb.shape == ref.shape == (n_freqs, n_mels)
+    assert np.abs(fb - ref).max() <= 2e-6 * ref.max()          # the reference stores band edges in float32
+    w = audio.hann_window_host(400, periodic=True)
+    assert abs(w[200] - 1.0) < 1e-7 and abs(w[1] - w[399]) < 1e-7      # periodic form: w[n] = w[N - n]
+    basis = audio.dft_basis_host(400)
+    x = np.random.default_rng(3).standard_normal(400)
+    spec = np.fft.rfft(x)
+    got = x @ basis.astype(np.float64)
+    assert np.abs(got[:201] - spec.real).max() <= 1e-4 and np.abs(got[201:] - spec.imag).max() <= 1e-4
