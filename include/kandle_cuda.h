@@ -320,18 +320,6 @@ int kd_attention_decode(const kd_tensor* q, const kd_tensor* k_cache, const kd_t
 int kd_attention_decode_noalloc(const kd_tensor* q, const kd_tensor* k_cache, const kd_tensor* v_cache,
                                 const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
                                 const kd_tensor* out);
-/* The same decode attention with its producer folded in: instead of a Q tensor and a cache that
- * already holds the new token, it takes the split-K partial sums of the QKV projection
- * (qkv_partials fp32 [splits, B, (Hq+2Hkv)*D], as kd_linear_bf16_skinny / kd_decode_layer_chain write
- * them) and does what kd_qkv_norm_rope_cachewrite does -- q/k RMSNorm over head_dim, RoPE with the
- * cos/sin row [D/2] of the new position, bf16 rounding, K/V row written into the caches at `pos`
- * -- inside the attention kernel while its first key tiles are in flight
- * (packages/model-utils/src/attention/gqa.ts:246-330 + kv-cache.ts:164-212 + the attention call).
- * pos: device int32 scalar; the context length is pos + 1.  out [B,Hq,1,D] bf16. */
-int kd_attention_decode_qkv(const kd_tensor* qkv_partials, const kd_tensor* q_norm_weight, const kd_tensor* k_norm_weight,
-                            float eps, const kd_tensor* cos, const kd_tensor* sin, const kd_tensor* k_cache,
-                            const kd_tensor* v_cache, const kd_tensor* pos, float scale, int splits,
-                            const kd_tensor* out);
 /* Paged variant (no counterpart in the reference, which only has the contiguous static cache):
  * k_pool/v_pool [pages,Hkv,128,D]; block_table [B,max_pages] int32 names the page of each
  * 128-key tile of each sequence. */

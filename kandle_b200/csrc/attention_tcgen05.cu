@@ -94,147 +94,15 @@ struct FaParams {
   float* part_ml;              // [B, Hkv, splits, group, 2] (running max in the log2 domain, sum)
   int direct;                  // splits == 1: write O/l as bf16 straight to `o` (no combine kernel)
   int colsplit;                // decode, group <= 8: each softmax warp handles a quarter of the key columns (see kernel)
-  // Fused decode prologue (qkv_part != NULL): Q and the new token's K/V cache row are produced here
-  // from the split-K partial sums of the QKV projection: q/k RMSNorm over head_dim, RoPE, bf16.
-  const float* qkv_part;       // [qkv_splits][B][n_qkv] fp32, columns: q heads, k heads, v heads
-  int qkv_splits, n_qkv;
-  const __nv_bfloat16 *qw, *kw;   // q_norm / k_norm weights [D]
-  float eps;
-  const float *cos_t, *sin_t;  // [D/2] for the new token's position
-  const int* pos_ptr;          // device scalar: position of the new token; the context length is pos + 1
-  __nv_bfloat16 *k_cache, *v_cache;
-  int64_t kc_b, kc_h, kc_s;
-  int max_s;
 };
 
 constexpr int FA_BQ = 128;
-constexpr int FA_BKV = 128;
+constexpr int FA_BKV = 128;          // key tile of the prefill kernels
+constexpr int FA_DEC_BKV = 64;       // key tile of the decode kernel: six 64-key ring slots instead of three 128-key ones
+                                     // keep more loads in flight per CTA in the same shared memory
 constexpr int FA_THREADS = 192;           // decode: TMA warp, MMA warp, one softmax warpgroup
 constexpr int FA_THREADS_PREFILL = 320;   // prefill: two softmax warpgroups
 constexpr int FA_STAGES = 2;
-
-// Fused decode prologue, run by the four softmax warps (128 threads, `q` = warp & 3): the Q tile and
-// the new K/V cache row from the QKV partial sums.  Half a warp per head row, lane l holds 4 (2 for
-// head_dim 64) elements of the first half of the head and the elements D/2 further on (both members
-// of each rotation pair); arithmetic and its order are those of qkv_norm_rope_kernel.  Kept out of
-// line so that its registers do not weigh on the attention loop.
-template <int D>
-__device__ __noinline__ void decode_qkv_prologue(const FaParams& p, uint8_t* q_smem, int Q_SLAB, int QROWS, int b, int hk,
-                                                 int kv_len, int j_begin, int j_end, int q, int lane, uint64_t* q_full,
-                                                 uint64_t* kv_ready) {
-      // Q tile and the new K/V cache row from the QKV partial sums.  Half a warp per head row, lane l
-      // holds 4 elements of the first half of the head and the 4 elements D/2 further on (both members
-      // of each rotation pair), the arithmetic and its order being those of qkv_norm_rope_kernel.
-      constexpr int HALF = D / 2, VE = D / 32;
-      const int new_tile = (kv_len - 1) / FA_BKV;
-      const bool writer = new_tile >= j_begin && new_tile < j_end;
-      const int n_rows = p.group + (writer ? 2 : 0);        // the group's query heads, then k, then v
-      const int l16 = lane & 15;
-      const int e0 = VE * l16;
-      const int pos = kv_len - 1;
-      for (int r0 = q * 2; r0 < n_rows; r0 += 8) {
-        const int r = r0 + (lane >> 4);
-        const bool live = r < n_rows;
-        const int rr = live ? r : 0;
-        const bool is_q = rr < p.group, is_k = rr == p.group;
-        const int col = (is_q ? hk * p.group + rr : (is_k ? p.Hq + hk : p.Hq + p.Hkv + hk)) * D;
-        float x1[VE], x2[VE];
-#pragma unroll
-        for (int i = 0; i < VE; ++i) { x1[i] = 0.f; x2[i] = 0.f; }
-        // four splits per round: all their loads are in flight together (the sums keep split order)
-        for (int sp0 = 0; sp0 < p.qkv_splits; sp0 += 4) {
-          float a1[4][VE], a2[4][VE];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int sp = min(sp0 + u, p.qkv_splits - 1);
-            const float* src = p.qkv_part + ((int64_t)sp * p.B + b) * p.n_qkv + col;
-            if constexpr (VE == 4) {
-              const float4 a = *reinterpret_cast<const float4*>(src + e0);
-              const float4 c = *reinterpret_cast<const float4*>(src + HALF + e0);
-              a1[u][0] = a.x; a1[u][1] = a.y; a1[u][2] = a.z; a1[u][3] = a.w;
-              a2[u][0] = c.x; a2[u][1] = c.y; a2[u][2] = c.z; a2[u][3] = c.w;
-            } else {
-              const float2 a = *reinterpret_cast<const float2*>(src + e0);
-              const float2 c = *reinterpret_cast<const float2*>(src + HALF + e0);
-              a1[u][0] = a.x; a1[u][1] = a.y;
-              a2[u][0] = c.x; a2[u][1] = c.y;
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (sp0 + u < p.qkv_splits) {
-#pragma unroll
-              for (int i = 0; i < VE; ++i) { x1[i] += a1[u][i]; x2[i] += a2[u][i]; }
-            }
-          }
-        }
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < VE; ++i) ss += x1[i] * x1[i] + x2[i] * x2[i];
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // stays inside the 16-lane half
-        if (!live) continue;
-        if (is_q || is_k) {
-          const float sc = 1.0f / sqrtf(ss / (float)D + p.eps);
-          const __nv_bfloat16* w = is_q ? p.qw : p.kw;
-#pragma unroll
-          for (int i = 0; i < VE; ++i) {
-            const float y1 = (x1[i] * sc) * __bfloat162float(w[e0 + i]);
-            const float y2 = (x2[i] * sc) * __bfloat162float(w[HALF + e0 + i]);
-            const float cs = p.cos_t[e0 + i], sn = p.sin_t[e0 + i];
-            x1[i] = y1 * cs - y2 * sn;
-            x2[i] = y2 * cs + y1 * sn;
-          }
-        }
-        uint32_t o1[VE / 2], o2[VE / 2];
-#pragma unroll
-        for (int i = 0; i < VE; i += 2) {
-          __nv_bfloat162 t1 = __floats2bfloat162_rn(x1[i], x1[i + 1]), t2 = __floats2bfloat162_rn(x2[i], x2[i + 1]);
-          o1[i / 2] = *reinterpret_cast<uint32_t*>(&t1);
-          o2[i / 2] = *reinterpret_cast<uint32_t*>(&t2);
-        }
-        if (is_q) {
-          // row rr of the Q tile, 128-byte swizzle: 16-byte chunk c of a row sits at chunk (c ^ (row & 7))
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int d = half * HALF + e0;                       // first element this lane writes in this half
-            const int slab = d / 64, chunk = (d % 64) / 8, within = (d % 8) * 2;
-            uint8_t* dst = q_smem + slab * Q_SLAB + rr * 128 + ((chunk ^ (rr & 7)) * 16) + within;
-            const uint32_t* ov = half ? o2 : o1;
-#pragma unroll
-            for (int i = 0; i < VE / 2; ++i) reinterpret_cast<uint32_t*>(dst)[i] = ov[i];
-          }
-        } else if (pos >= 0 && pos < p.max_s) {
-          __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) + (int64_t)b * p.kc_b + (int64_t)hk * p.kc_h + (int64_t)pos * p.kc_s;
-#pragma unroll
-          for (int i = 0; i < VE / 2; ++i) {
-            reinterpret_cast<uint32_t*>(dst + e0)[i] = o1[i];
-            reinterpret_cast<uint32_t*>(dst + HALF + e0)[i] = o2[i];
-          }
-        } else if (l16 == 0 && atomicCAS(p.err, 0, 102) == 0) {   // never write outside the cache; report instead
-          p.err[1] = pos; p.err[2] = p.max_s;
-        }
-      }
-      // rows of the 16-row tile beyond the group are padding: zero them (TMA would have)
-      for (int i = threadIdx.x - 64; i < (QROWS - p.group) * (D * 2 / 16); i += 128) {
-        const int rrow = p.group + i / (D * 2 / 16), ch = i % (D * 2 / 16);
-        const int slab = ch / 8, chunk = ch % 8;
-        *reinterpret_cast<uint4*>(q_smem + slab * Q_SLAB + rrow * 128 + ((chunk ^ (rrow & 7)) * 16)) = make_uint4(0, 0, 0, 0);
-      }
-      fence_async_proxy();                                  // Q tile: generic writes -> tcgen05.mma reads
-      if (writer) {
-        // cache row: generic-proxy stores that a TMA load (async proxy, served from L2) of this CTA reads
-        // next: make them visible device-wide first, then order the two proxies
-        __threadfence();
-        asm volatile("fence.proxy.async;" ::: "memory");
-      }
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(q_full);
-        if (writer) mbar_arrive(kv_ready);
-      }
-}
 
 template <int D, bool DECODE>
 __global__ void __launch_bounds__(DECODE ? FA_THREADS : FA_THREADS_PREFILL, DECODE ? 2 : 1)
@@ -247,17 +115,19 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   constexpr int QROWS = DECODE ? 16 : FA_BQ;
   constexpr int Q_BYTES = QROWS * D * 2;
   constexpr int Q_SLAB = QROWS * 128;
-  constexpr int KV_BYTES = FA_BKV * D * 2;
-  constexpr int SLAB_BYTES = FA_BKV * 128;          // 128 rows x 128 B
-  // prefill: two S buffers (columns 0 and 128) + O at 256; decode: one S buffer + O at 128, one
-  // smem stage per operand, so that two CTAs fit on an SM and overlap each other's latencies
-  constexpr int NSBUF = DECODE ? 1 : 2;
+  constexpr int BKV = DECODE ? FA_DEC_BKV : FA_BKV;  // keys per tile
+  constexpr int KV_BYTES = BKV * D * 2;
+  constexpr int SLAB_BYTES = BKV * 128;             // BKV rows x 128 B
+  // Two S buffers of BKV columns each, then O: prefill S at columns 0 and 128, O at 256 (512 columns);
+  // decode S at 0 and 64, O at 128 (256 columns, so that two CTAs fit on an SM).  The next Q K^T is
+  // issued before the current block's softmax has finished.
+  constexpr int NSBUF = 2;
   constexpr int NWG = DECODE ? 1 : 2;   // softmax warpgroups
   // K and V tiles travel through one ring in the order K0 V0 K1 V1 ...: tile t uses slot t % NSLOT
-  constexpr int NSLOT = DECODE ? 3 : 2 * FA_STAGES;
+  constexpr int NSLOT = DECODE ? 6 : 2 * FA_STAGES;
   constexpr uint32_t TMEM_COLS = DECODE ? 256 : 512;
   constexpr uint32_t S_COL0 = 0, O_COL0 = DECODE ? 128 : 256;
-  constexpr uint32_t IDESC_QK = make_idesc_bf16(FA_BQ, FA_BKV, 0, 0);
+  constexpr uint32_t IDESC_QK = make_idesc_bf16(FA_BQ, BKV, 0, 0);
   constexpr uint32_t IDESC_PV = make_idesc_bf16(FA_BQ, D, 0, 1);
 
   extern __shared__ uint8_t smem_raw[];
@@ -266,13 +136,13 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   uint8_t* ring = q_smem + Q_BYTES;                         // [NSLOT][KV_BYTES]
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + NSLOT * KV_BYTES);
   uint64_t* q_full = bars;                 // 1
-  uint64_t* t_full = bars + 1;             // NSLOT (<= 4)
-  uint64_t* t_empty = bars + 5;            // NSLOT
-  uint64_t* s_full = bars + 9;             // 2
-  uint64_t* p_ready = bars + 11;           // 2
-  uint64_t* o_done = bars + 13;            // 1
-  uint64_t* x_bar = bars + 14;             // 2: row-maximum exchange between the softmax warpgroups
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* t_full = bars + 1;             // NSLOT (<= 6)
+  uint64_t* t_empty = bars + 7;            // NSLOT
+  uint64_t* s_full = bars + 13;            // 2
+  uint64_t* p_ready = bars + 15;           // 2
+  uint64_t* o_done = bars + 17;            // 1
+  uint64_t* x_bar = bars + 18;             // 2: row-maximum exchange between the softmax warpgroups
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xchg = reinterpret_cast<float*>(tmem_slot + 4);   // [2 buffers][2 warpgroups][128 rows]
 
@@ -284,10 +154,10 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     hk = blockIdx.y;
     h = hk;                     // Q tensor map is indexed by (row-in-group, kv head, batch)
     q0 = 0;
-    kv_len = p.qkv_part ? *p.pos_ptr + 1 : (p.ctx_ptr ? *p.ctx_ptr : p.Skv);
+    kv_len = p.ctx_ptr ? *p.ctx_ptr : p.Skv;
     kv_len = max(0, min(kv_len, p.Skv));
     kv_end = kv_len;
-    const int n_total = (kv_len + FA_BKV - 1) / FA_BKV;
+    const int n_total = (kv_len + BKV - 1) / BKV;
     const int per_split = (n_total + p.splits - 1) / p.splits;
     j_begin = (int)blockIdx.x * per_split;
     j_end = min(n_total, j_begin + per_split);
@@ -313,7 +183,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   const int n_blocks = j_end - j_begin;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, (DECODE && p.qkv_part) ? 4 : 1);   // fused prologue: the four softmax warps fill the Q tile
+    mbar_init(q_full, 1);
     for (int s = 0; s < NSLOT; ++s) { mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], 1); }
     for (int s = 0; s < NSBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4 * NWG); }
     for (int s = 0; s < 2; ++s) mbar_init(&x_bar[s], 4 * NWG);
@@ -336,24 +206,16 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 
   if (warp == 0) {
     if (lane == 0) {
-      const bool fused = DECODE && p.qkv_part != nullptr;
-      if (!fused) {
-        mbar_arrive_expect_tx(q_full, Q_BYTES);
+      mbar_arrive_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-        for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * Q_SLAB, &tmap_q, q_full, s * 64, q0, h, b);
-      }
-      const int new_tile = fused ? (kv_len - 1) / FA_BKV : -1;   // the tile that receives the new token's K/V row
+      for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * Q_SLAB, &tmap_q, q_full, s * 64, q0, h, b);
       for (int jj = 0; jj < n_blocks; ++jj) {
-        if (fused && j_begin + jj == new_tile) {
-          // the softmax warps of this CTA write that row (generic proxy) before TMA may read the tile
-          if (!mbar_wait(&x_bar[0], 0, abort_flag, p.err, 312)) break;
-          asm volatile("fence.proxy.async;" ::: "memory");
-        }
-        // key-tile coordinates: rows j*128.. of sequence b, or row 0 of the page the block table names
-        int row = (j_begin + jj) * FA_BKV, outer = b;
+        // key-tile coordinates: rows j*BKV.. of sequence b, or the matching rows of the 128-row page
+        // the block table names
+        int row = (j_begin + jj) * BKV, outer = b;
         if (DECODE && p.block_table) {
-          outer = p.block_table[(int64_t)b * p.max_pages + (j_begin + jj)];
-          row = 0;
+          outer = p.block_table[(int64_t)b * p.max_pages + row / 128];
+          row = row % 128;
         }
         const int tk = 2 * jj, tv = 2 * jj + 1;
         const int sk = tk % NSLOT, sv = tv % NSLOT;
@@ -379,7 +241,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         if (!mbar_wait(&t_full[stage], (uint32_t)((t / NSLOT) & 1), abort_flag, p.err, 304)) return false;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(ring + stage * KV_BYTES);
-        const uint32_t d_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
+        const uint32_t d_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * BKV);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t qoff = (uint32_t)((k / 4) * Q_SLAB + (k % 4) * 32);
@@ -404,10 +266,10 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         if (!mbar_wait(&t_full[stage], (uint32_t)((t / NSLOT) & 1), abort_flag, p.err, 306)) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(ring + stage * KV_BYTES);
-        const uint32_t p_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
+        const uint32_t p_tmem = tmem_base + S_COL0 + (uint32_t)((j % NSBUF) * BKV);
         const uint32_t o_tmem = tmem_base + O_COL0;
 #pragma unroll
-        for (int k = 0; k < FA_BKV / 16; ++k) {
+        for (int k = 0; k < BKV / 16; ++k) {
           // V tile is [kv rows][64-wide d slabs]: MN-major B; 16 kv rows = 2048 bytes per k step
           const uint64_t vdesc = make_smem_desc_sw128(v_addr + (uint32_t)(k * 2048), SLAB_BYTES, 1024);
           umma_ts(o_tmem, p_tmem + (uint32_t)(k * 8), vdesc, IDESC_PV, (j | k) != 0 ? 1u : 0u);
@@ -426,7 +288,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     // quarter, so the two threads that share a row sit in warps w and w+4).  They exchange the row
     // maximum through shared memory every block and the row sum once at the end; everything else
     // (P, the O rescale, the output store) is split by columns.  Decode runs one warpgroup.
-    constexpr int CW = FA_BKV / NWG;     // S columns per thread
+    constexpr int CW = BKV / NWG;        // S columns per thread
     constexpr int NCH = CW / 32;
     constexpr int DW = D / NWG;          // O columns per thread
     const int wg = (warp - 2) >> 2;
@@ -434,8 +296,6 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     const int row_in_tile = q * 32 + lane;
     const int row = q0 + row_in_tile;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    if (DECODE && p.qkv_part)
-      decode_qkv_prologue<D>(p, q_smem, Q_SLAB, QROWS, b, hk, kv_len, j_begin, j_end, q, lane, q_full, &x_bar[0]);
     bool colsplit_done = false;
     if constexpr (DECODE) {
       if (p.colsplit) {
@@ -448,32 +308,33 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         // tile; each warp writes its 32 probabilities into its own rows of P and zeros elsewhere, so
         // that the P V product leaves a partial O per warp in rows 32 w + r, summed in the epilogue.
         colsplit_done = true;
+        constexpr int QC = BKV / 4;        // key columns per warp and block (16)
         float* xm = xchg;                 // [2 buffers][4 quarters][32 lanes] row maxima
         float* xl = xchg + 256;           // [4 quarters][32 lanes] row sums
         float* xmu = xchg + 384;          // [32 lanes] the running maximum each row ended with
         float m_used = -1e30f, l = 0.f;
         bool ok = true;
-        const uint32_t s_addr = lane_addr + S_COL0;
         // No thread leaves this loop between the 128-thread barriers except right after one, where
         // all of them see the same abort flag (every failed wait raises it).
         for (int j = 0; j < n_blocks; ++j) {
-          ok = mbar_wait(&s_full[0], (uint32_t)(j & 1), abort_flag, p.err, 307);
+          const uint32_t s_addr = lane_addr + S_COL0 + (uint32_t)((j % NSBUF) * BKV);
+          ok = mbar_wait(&s_full[j % NSBUF], (uint32_t)((j / NSBUF) & 1), abort_flag, p.err, 307);
           ok = __all_sync(0xffffffffu, ok);
-          uint32_t sr[32];
+          uint32_t sr[QC];
           float* slot = xm + (j & 1) * 128;
           if (ok) {
             tc_fence_after();
-            tmem_ld_32x32(s_addr + q * 32, sr);
+            tmem_ld_32x16(s_addr + q * QC, sr);
             tmem_wait_ld();
-            const int kv0 = (j_begin + j) * FA_BKV + q * 32;
-            if (kv0 + 32 > kv_end) {
+            const int kv0 = (j_begin + j) * BKV + q * QC;
+            if (kv0 + QC > kv_end) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
+              for (int i = 0; i < QC; ++i)
                 if (kv0 + i >= kv_len) sr[i] = __float_as_uint(-1e30f);
             }
             float mx0 = -1e30f, mx1 = -1e30f;
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
+            for (int i = 0; i < QC; i += 4) {
               mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])));
               mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])));
             }
@@ -509,11 +370,11 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
             }
             l *= alpha;
           }
-          // P row: this warp's 32 probabilities in packed columns [16 q, 16 q + 16), zeros in the rest
+          // P row: this warp's QC probabilities in packed columns [QC/2 q, QC/2 (q+1)), zeros in the rest
           float sum0 = 0.f, sum1 = 0.f;
-          uint32_t pk[16];
+          uint32_t pk[QC / 2];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < QC / 2; ++i) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), p.scale_log2, -m_used));
             const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), p.scale_log2, -m_used));
             sum0 += p0;
@@ -522,15 +383,15 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
             pk[i] = *reinterpret_cast<uint32_t*>(&v);
           }
           l += sum0 + sum1;
-          uint32_t zero[16];
+          uint32_t zero[QC / 2];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) zero[i] = 0u;
+          for (int i = 0; i < QC / 2; ++i) zero[i] = 0u;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_st_32x16(s_addr + c * 16, c == q ? pk : zero);
+          for (int c = 0; c < 4; ++c) tmem_st_32x8(s_addr + c * (QC / 2), c == q ? pk : zero);
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&p_ready[0]);
+          if (lane == 0) mbar_arrive(&p_ready[j % NSBUF]);
         }
         if (ok) {
           ok = mbar_wait(o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, p.err, 309);
@@ -599,15 +460,15 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + S_COL0 + (uint32_t)((j % NSBUF) * FA_BKV);
+      const uint32_t s_addr = lane_addr + S_COL0 + (uint32_t)((j % NSBUF) * BKV);
       uint32_t sr[NCH][32];
 #pragma unroll
       for (int c = 0; c < NCH; ++c) tmem_ld_32x32(s_addr + wg * CW + c * 32, sr[c]);
       tmem_wait_ld();
-      const int kv0 = (j_begin + j) * FA_BKV;
+      const int kv0 = (j_begin + j) * BKV;
       // Only the diagonal block of a causal tile and the last (ragged) key block need masking;
       // the test is hoisted so that the common path carries no per-element predicates.
-      if ((kv0 + FA_BKV > kv_end) || (p.causal && kv0 + FA_BKV - 1 > q0)) {
+      if ((kv0 + BKV > kv_end) || (p.causal && kv0 + BKV - 1 > q0)) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
 #pragma unroll
@@ -792,7 +653,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 
 template <int D, bool DECODE>
 static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid) {
-  constexpr int SMEM = (DECODE ? 16 : FA_BQ) * D * 2 + (DECODE ? 3 : 2 * FA_STAGES) * FA_BKV * D * 2 + 1024 + 256 + 2048;
+  constexpr int SMEM = (DECODE ? 16 : FA_BQ) * D * 2 + (DECODE ? 6 * FA_DEC_BKV : 2 * FA_STAGES * FA_BKV) * D * 2 + 1024 + 256 + 2048;
   static bool configured = false;
   if (!configured) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(flash_attention_tcgen05_kernel<D, DECODE>,
@@ -907,13 +768,10 @@ size_t attention_decode_scratch_bytes(int B, int Hkv, int group, int splits, int
 // with block_table [B,max_pages]; out [B,Hq,1,D].  `scratch` holds the split partials.
 int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
                      const int* ctx_dev, int ctx_host, const int* block_table, int max_pages, int splits,
-                     void* scratch, size_t scratch_bytes, const DecodeQkvSource* qkv) {
-  // with a QKV source there is no Q tensor: `out` [B,Hq,1,D] stands in for its shape
-  if (qkv) q = out;
+                     void* scratch, size_t scratch_bytes) {
   KD_REQUIRE(q->ndim == 4 && k->ndim == 4 && v->ndim == 4 && out->ndim == 4, "attention_decode: operands must be 4-D");
   KD_REQUIRE(q->dtype == KD_BF16 && k->dtype == KD_BF16 && v->dtype == KD_BF16 && out->dtype == KD_BF16,
              "attention_decode: bf16 tensors required");
-  KD_REQUIRE(!qkv || (!block_table && ctx_dev == nullptr), "attention_decode: the fused QKV source needs the contiguous cache and takes the context from the position");
   const int B = (int)q->shape[0], Hq = (int)q->shape[1], D = (int)q->shape[3];
   const int Hkv = (int)k->shape[1];
   KD_REQUIRE(q->shape[2] == 1 && out->shape[2] == 1, "attention_decode: exactly one query position per sequence");
@@ -926,13 +784,13 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   const int group = Hq / Hkv;
   int Skv;
   if (block_table) {
-    KD_REQUIRE(k->shape[2] == FA_BKV, "attention_decode: paged cache needs pages of %d rows", FA_BKV);
-    Skv = max_pages * FA_BKV;
+    KD_REQUIRE(k->shape[2] == 128, "attention_decode: paged cache needs pages of 128 rows");
+    Skv = max_pages * 128;
   } else {
     KD_REQUIRE(k->shape[0] == B, "attention_decode: cache batch differs from the query batch");
     Skv = (int)k->shape[2];
   }
-  if (!ctx_dev && !qkv) KD_REQUIRE(ctx_host >= 1 && ctx_host <= Skv, "attention_decode: context length %d outside [1,%d]", ctx_host, Skv);
+  if (!ctx_dev) KD_REQUIRE(ctx_host >= 1 && ctx_host <= Skv, "attention_decode: context length %d outside [1,%d]", ctx_host, Skv);
   KD_REQUIRE(q->strides[3] == 1 && k->strides[3] == 1 && v->strides[3] == 1 && out->strides[3] == 1,
              "attention_decode: unit stride along head_dim required");
   for (int i = 0; i < 3; ++i)
@@ -952,25 +810,11 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   const int64_t sq[3] = {q->strides[0], q->strides[1] * group, q->strides[1]};
   const int64_t ek[4] = {k->shape[0], Hkv, k->shape[2], D};
   CUtensorMap tq, tk, tv;
-  KD_TRY(make_tmap_bhsd(&tk, pk, ek, k->strides, FA_BKV));
-  if (qkv) tq = tk;   // unused by the kernel in this mode
-  else KD_TRY(make_tmap_bhsd(&tq, pq, eq, sq, 16));
-  KD_TRY(make_tmap_bhsd(&tv, pv, ek, v->strides, FA_BKV));
+  KD_TRY(make_tmap_bhsd(&tq, pq, eq, sq, 16));
+  KD_TRY(make_tmap_bhsd(&tk, pk, ek, k->strides, FA_DEC_BKV));
+  KD_TRY(make_tmap_bhsd(&tv, pv, ek, v->strides, FA_DEC_BKV));
   FaParams p{};
-  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = group; p.Skv = (ctx_dev || qkv) ? Skv : ctx_host;
-  if (qkv) {
-    KD_REQUIRE(qkv->splits >= 1 && qkv->n_qkv == (Hq + 2 * Hkv) * D, "attention_decode: QKV partials must have (Hq + 2 Hkv) * D columns");
-    KD_REQUIRE((reinterpret_cast<uintptr_t>(qkv->partials) & 15) == 0 && k->strides[2] % 2 == 0 && v->strides[2] % 2 == 0,
-               "attention_decode: QKV partials / cache rows must be 16- / 4-byte aligned");
-    KD_REQUIRE(v->strides[0] == k->strides[0] && v->strides[1] == k->strides[1] && v->strides[2] == k->strides[2],
-               "attention_decode: K and V caches must share their strides");
-    p.qkv_part = qkv->partials; p.qkv_splits = qkv->splits; p.n_qkv = qkv->n_qkv;
-    p.qw = static_cast<const __nv_bfloat16*>(qkv->q_norm_w); p.kw = static_cast<const __nv_bfloat16*>(qkv->k_norm_w);
-    p.eps = qkv->eps; p.cos_t = qkv->cos_t; p.sin_t = qkv->sin_t; p.pos_ptr = qkv->pos_dev;
-    p.k_cache = static_cast<__nv_bfloat16*>(pk); p.v_cache = static_cast<__nv_bfloat16*>(pv);
-    p.kc_b = k->strides[0]; p.kc_h = k->strides[1]; p.kc_s = k->strides[2];
-    p.max_s = Skv;
-  }
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = group; p.Skv = ctx_dev ? Skv : ctx_host;
   p.causal = 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = ctx().error_flag;
@@ -1024,7 +868,7 @@ int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_ten
   KD_REQUIRE(q && k && q->ndim == 4 && k->ndim == 4, "decode attention operands must be 4-D");
   const int B = (int)q->shape[0], Hq = (int)q->shape[1], Hkv = (int)k->shape[1], D = (int)q->shape[3];
   KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "bad head counts");
-  const int max_blocks = (int)((k->shape[2] + FA_BKV - 1) / FA_BKV);
+  const int max_blocks = (int)((k->shape[2] + FA_DEC_BKV - 1) / FA_DEC_BKV);
   if (splits <= 0) {
     const int pairs = B * Hkv > 0 ? B * Hkv : 1;
     splits = (2 * ctx().sm_count) / pairs;   // two CTAs fit per SM: stay within one wave

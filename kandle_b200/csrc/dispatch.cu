@@ -82,7 +82,7 @@ static int decode_common(const kd_tensor* q, const kd_tensor* k, const kd_tensor
   const int B = (int)q->shape[0], Hq = (int)q->shape[1], Hkv = (int)k->shape[1], D = (int)q->shape[3];
   KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "bad head counts");
   const int max_keys = table ? max_pages * 128 : (int)k->shape[2];
-  const int max_blocks = (max_keys + 127) / 128;
+  const int max_blocks = (max_keys + 63) / 64;     // 64-key tiles
   if (splits <= 0) {
     // one wave of CTAs (2 per SM), never more splits than key tiles
     const int pairs = B * Hkv > 0 ? B * Hkv : 1;
@@ -100,44 +100,6 @@ KD_API int kd_attention_decode(const kd_tensor* q, const kd_tensor* k_cache, con
                                const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
                                const kd_tensor* out) {
   return decode_common(q, k_cache, v_cache, nullptr, ctx_len, ctx_len_host, scale, splits, out);
-}
-
-KD_API int kd_attention_decode_qkv(const kd_tensor* qkv_partials, const kd_tensor* q_norm_weight, const kd_tensor* k_norm_weight,
-                                   float eps, const kd_tensor* cos, const kd_tensor* sin, const kd_tensor* k_cache,
-                                   const kd_tensor* v_cache, const kd_tensor* pos, float scale, int splits,
-                                   const kd_tensor* out) {
-  KD_TRY(require_init());
-  KD_REQUIRE(qkv_partials && q_norm_weight && k_norm_weight && cos && sin && k_cache && v_cache && pos && out, "null tensor");
-  KD_REQUIRE(out->ndim == 4 && k_cache->ndim == 4 && out->shape[2] == 1, "out must be [B,Hq,1,D], caches [B,Hkv,maxS,D]");
-  const int B = (int)out->shape[0], Hq = (int)out->shape[1], D = (int)out->shape[3], Hkv = (int)k_cache->shape[1];
-  KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "bad head counts");
-  const int64_t n_qkv = (int64_t)(Hq + 2 * Hkv) * D;
-  KD_REQUIRE(qkv_partials->dtype == KD_F32 && is_contiguous(qkv_partials) && numel(qkv_partials) > 0 &&
-                 numel(qkv_partials) % ((int64_t)B * n_qkv) == 0,
-             "qkv_partials must be contiguous fp32 [splits, B, (Hq+2Hkv)*D]");
-  KD_REQUIRE(q_norm_weight->dtype == KD_BF16 && k_norm_weight->dtype == KD_BF16 && is_contiguous(q_norm_weight) &&
-                 is_contiguous(k_norm_weight) && numel(q_norm_weight) == D && numel(k_norm_weight) == D,
-             "q/k norm weights must be contiguous bf16 [D]");
-  KD_REQUIRE(cos->dtype == KD_F32 && sin->dtype == KD_F32 && is_contiguous(cos) && is_contiguous(sin) && numel(cos) == D / 2 &&
-                 numel(sin) == D / 2,
-             "cos / sin must be contiguous fp32 [D/2] tables of the new token's position");
-  KD_REQUIRE(pos->dtype == KD_I32 && numel(pos) == 1, "pos must be a device int32 scalar");
-  void *pp, *pqw, *pkw, *pc, *ps, *ppos;
-  KD_TRY(tensor_ptr(qkv_partials, &pp)); KD_TRY(tensor_ptr(q_norm_weight, &pqw)); KD_TRY(tensor_ptr(k_norm_weight, &pkw));
-  KD_TRY(tensor_ptr(cos, &pc)); KD_TRY(tensor_ptr(sin, &ps)); KD_TRY(tensor_ptr(pos, &ppos));
-  DecodeQkvSource src{static_cast<const float*>(pp), (int)(numel(qkv_partials) / ((int64_t)B * n_qkv)), (int)n_qkv, pqw, pkw, eps,
-                      static_cast<const float*>(pc), static_cast<const float*>(ps), static_cast<const int*>(ppos)};
-  const int max_blocks = (int)((k_cache->shape[2] + 127) / 128);
-  if (splits <= 0) {
-    const int pairs = B * Hkv > 0 ? B * Hkv : 1;
-    splits = (2 * ctx().sm_count) / pairs;   // two CTAs fit per SM: stay within one wave
-    if (splits > max_blocks) splits = max_blocks;
-    if (splits < 1) splits = 1;
-  }
-  const size_t need = attention_decode_scratch_bytes(B, Hkv, Hq / Hkv, splits, D);
-  void* scratch = nullptr;
-  KD_TRY(get_workspace(need, &scratch));
-  return attention_decode(nullptr, k_cache, v_cache, out, scale, nullptr, 0, nullptr, 0, splits, scratch, need, &src);
 }
 
 KD_API int kd_attention_decode_paged(const kd_tensor* q, const kd_tensor* k_pool, const kd_tensor* v_pool,

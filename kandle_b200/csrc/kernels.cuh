@@ -37,19 +37,9 @@ int gemm_skinny_auto_splits(int N, int K);
 int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int Mb, int N, int K, int splits,
                      float* out_f32, void* out_bf16, int swiglu);
 size_t attention_decode_scratch_bytes(int B, int Hkv, int group, int splits, int D);
-// Fused prologue of the decode attention: Q and the new K/V cache row come from the QKV projection's
-// split-K partial sums (q/k RMSNorm, RoPE) instead of a Q tensor and a cache written beforehand.
-struct DecodeQkvSource {
-  const float* partials;      // [splits][B][n_qkv]
-  int splits, n_qkv;
-  const void *q_norm_w, *k_norm_w;   // bf16 [D]
-  float eps;
-  const float *cos_t, *sin_t;        // [D/2]
-  const int* pos_dev;                // device scalar: position of the new token
-};
 int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
                      const int* ctx_dev, int ctx_host, const int* block_table, int max_pages, int splits,
-                     void* scratch, size_t scratch_bytes, const DecodeQkvSource* qkv = nullptr);
+                     void* scratch, size_t scratch_bytes);
 
 int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
                             const int* ctx_dev, int ctx_host, int splits);

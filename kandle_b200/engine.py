@@ -3,13 +3,13 @@ tcgen05 flash attention, split-KV decode attention and a CUDA-graph decode step.
 
 It computes what `Qwen3ForCausalLM.forwardWithKVCache` + greedy argmax compute on the eager path
 (packages/model-utils/src/qwen3/for_causal_lm.ts:170-194,475-508), with the ~41 backend calls per
-layer collapsed into 7 (prefill) / 2 (decode) kernels and no intermediate copies:
+layer collapsed into 7 (prefill) / 3 (decode) kernels and no intermediate copies:
 
   prefill, per layer     rms_norm -> QKV GEMM (epilogue: q/k-norm+RoPE+cache write) -> flash attention ->
                          o_proj GEMM (+residual) -> rms_norm -> gate/up GEMM (SiLU*up epilogue) ->
                          down GEMM (+residual)
-  decode step, per layer split-KV attention whose prologue sums the QKV split-K partials and does q/k-norm,
-                         RoPE and the cache write -> one persistent kernel: o_proj -> residual+rms_norm -> gate/up with SiLU*up
+  decode step, per layer norm+RoPE+cache write (sums the QKV split-K partials) -> split-KV attention ->
+                         one persistent kernel: o_proj -> residual+rms_norm -> gate/up with SiLU*up
                          -> down -> residual+rms_norm -> the NEXT layer's QKV partials
                          (tensor parallel: the same steps as separate kernels, with all-reduces)
   The decode step reads the write position / context length from device memory, so one captured
@@ -96,7 +96,6 @@ class Qwen3Engine:
         # decode: run o_proj .. next layer's QKV as one persistent kernel per layer (kd_decode_layer_chain);
         # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
         self.use_chain = self.tp == 1 and self.H <= 4096
-        self.fuse_rope_into_attention = True
         self.sampler = None   # None: greedy argmax; else dict(temperature, top_k, top_p, rng), see set_sampler
 
     # ------------------------------------------------------------------ helpers
@@ -296,14 +295,9 @@ class Qwen3Engine:
             vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
             if li == 0 or not d["chain"]:
                 lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wqkv"]), 0, _r(d["qkv_p"]))
-            if d["chain"] and self.fuse_rope_into_attention:
-                # q/k-norm + RoPE + cache write happen inside the attention kernel, under its first key tiles
-                lib.call("kd_attention_decode_qkv", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
-                         _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), ctypes.c_float(self.scale), 0, _r(o_bh1d))
-            else:
-                lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
-                         _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
-                lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
+            lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
+                     _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
+            lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
             nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
             if d["chain"]:
                 last = li + 1 == self.L

@@ -139,7 +139,6 @@ _SIGNATURES = {
     "kd_swiglu": [_T, _T],
     "kd_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
     "kd_increment_i32": [_T, ctypes.c_int],
-    "kd_attention_decode_qkv": [_T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, ctypes.c_float, ctypes.c_int, _T],
     "kd_stft_frames": [_T, _T, ctypes.c_int, ctypes.c_int, ctypes.c_int, _T],
     "kd_power_spectrum": [_T, _T],
     "kd_whisper_log_mel_norm": [_T, _T],

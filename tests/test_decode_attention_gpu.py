@@ -88,65 +88,3 @@ def test_decode_attention_rejects_bad_arguments(backend):
     with pytest.raises(lib.KandleCudaError):      # fp32 query
         q32 = Tensor(synth.normal("q", (1, 4, 1, 128)))
         lib.call("kd_attention_decode", _ref(q32), _ref(kc), _ref(kc), None, 8, ctypes.c_float(0.1), 0, _ref(out))
-
-
-@pytest.mark.parametrize("b,hq,hkv,max_s,pos,d,splits,qkv_splits", [
-    (32, 16, 8, 384, 300, 128, 0, 4),     # the benchmark's head layout, new token in the last (third) key tile
-    (3, 16, 8, 512, 255, 128, 2, 2),      # new token is the last row of a tile; two KV splits, second one owns it
-    (2, 4, 4, 256, 0, 128, 1, 1),         # first token of a sequence: the tile holds nothing but the new row
-    (2, 12, 12, 640, 129, 64, 3, 3),      # head_dim 64, one query head per KV head
-    (1, 32, 2, 384, 128, 128, 0, 1),      # 16 query heads per KV head: the whole 16-row Q tile is real
-])
-def test_decode_attention_with_fused_qkv_prologue(backend, b, hq, hkv, max_s, pos, d, splits, qkv_splits):
-    """kd_attention_decode_qkv = kd_qkv_norm_rope_cachewrite + kd_attention_decode: the cache rows it
-    writes must equal the two-kernel sequence bit for bit, its output up to the compiler's choice of
-    fused multiply-adds in the two copies of the q-norm/RoPE arithmetic (a last-bit difference in one
-    head's scale can flip the bf16 rounding of a query element: measured, one output row in 512)."""
-    n_qkv = (hq + 2 * hkv) * d
-    part = synth.normal("fq-part", (qkv_splits, b, n_qkv), 0.7)
-    qw = lib.round_to_bf16(1.0 + synth.normal("fq-qw", (d,), 0.1))
-    kw = lib.round_to_bf16(1.0 + synth.normal("fq-kw", (d,), 0.1))
-    kc0 = lib.round_to_bf16(synth.normal("fq-kc", (b, hkv, max_s, d)))
-    vc0 = lib.round_to_bf16(synth.normal("fq-vc", (b, hkv, max_s, d)))
-    ang = synth.normal("fq-ang", (1, d // 2), 2.0)
-    cos, sin = Tensor(np.cos(ang).astype(np.float32)), Tensor(np.sin(ang).astype(np.float32))
-    tpart, tqw, tkw = Tensor(part), Tensor(qw, dtype="bfloat16"), Tensor(kw, dtype="bfloat16")
-    tpos = Tensor(np.array([pos], np.int32))
-    tctx = Tensor(np.array([pos + 1], np.int32))
-    scale = ctypes.c_float(1.0 / math.sqrt(d))
-    eps = ctypes.c_float(1e-6)
-    # two kernels
-    k1, v1 = Tensor(kc0, dtype="bfloat16"), Tensor(vc0, dtype="bfloat16")
-    q1 = core.empty((b, 1, hq, d), "bfloat16")
-    lib.call("kd_qkv_norm_rope_cachewrite", _ref(tpart), _ref(tqw), _ref(tkw), eps, _ref(cos), _ref(sin), _ref(k1), _ref(v1),
-             _ref(tpos), 0, _ref(q1))
-    o1 = core.empty((b, hq, 1, d), "bfloat16")
-    q1v = q1.permute([0, 2, 1, 3])
-    lib.call("kd_attention_decode", _ref(q1v), _ref(k1), _ref(v1), _ref(tctx), 0, scale, splits, _ref(o1))
-    # one kernel
-    k2, v2 = Tensor(kc0, dtype="bfloat16"), Tensor(vc0, dtype="bfloat16")
-    o2 = core.empty((b, hq, 1, d), "bfloat16")
-    lib.call("kd_attention_decode_qkv", _ref(tpart), _ref(tqw), _ref(tkw), eps, _ref(cos), _ref(sin), _ref(k2), _ref(v2),
-             _ref(tpos), scale, splits, _ref(o2))
-    backend.synchronize()
-    assert np.array_equal(k2.dataAsync(), k1.dataAsync()) and np.array_equal(v2.dataAsync(), v1.dataAsync())
-    assert not np.array_equal(k2.dataAsync()[:, :, pos], kc0[:, :, pos])        # the row was really written
-    a, c = o2.dataAsync(), o1.dataAsync()
-    rows_differ = (np.abs(a - c).max(-1) > 0).mean()
-    assert np.abs(a - c).max() <= 2.0 ** -7 * np.abs(c).max() and rows_differ <= 0.01
-
-
-def test_fused_qkv_prologue_reports_a_position_outside_the_cache(backend):
-    b, hq, hkv, max_s, d = 1, 4, 2, 128, 128
-    part = Tensor(synth.normal("fq-bad", (1, b, (hq + 2 * hkv) * d), 0.5))
-    w = Tensor(np.ones(d, np.float32), dtype="bfloat16")
-    cs = Tensor(np.ones((1, d // 2), np.float32))
-    kc, vc = core.zeros((b, hkv, max_s, d), "bfloat16"), core.zeros((b, hkv, max_s, d), "bfloat16")
-    out = core.empty((b, hq, 1, d), "bfloat16")
-    bad = core.empty((b, hq, 1, d), "float32")
-    with pytest.raises(lib.KandleCudaError):       # output must be bf16
-        lib.call("kd_attention_decode_qkv", _ref(part), _ref(w), _ref(w), ctypes.c_float(1e-6), _ref(cs), _ref(cs), _ref(kc), _ref(vc),
-                 _ref(Tensor(np.array([5], np.int32))), ctypes.c_float(0.1), 0, _ref(bad))
-    with pytest.raises(lib.KandleCudaError):       # partial sums of the wrong width
-        lib.call("kd_attention_decode_qkv", _ref(Tensor(np.zeros((1, b, 100), np.float32))), _ref(w), _ref(w), ctypes.c_float(1e-6),
-                 _ref(cs), _ref(cs), _ref(kc), _ref(vc), _ref(Tensor(np.array([5], np.int32))), ctypes.c_float(0.1), 0, _ref(out))
