@@ -335,9 +335,9 @@ def run_ours(a) -> None:
         ach = alg_bytes / (us * 1e-6) / 1e9
         roofline = {"kernel": "flash_attention_tcgen05_kernel<decode> (+ decode_combine_kernel when the keys are split)", "bound": "hbm", "achieved": ach,
                     "peak": hbm_peak, "peak_source": hbm_src, "unit": "GB/s", "frac": ach / hbm_peak,
-                    # dram__bytes_read+write of one ncu capture at B=32, Hkv=8, ctx=2176 (290.1 MB for 285.2 MB
+                    # dram__bytes_read+write of one ncu capture at B=32, Hkv=8, ctx=2176 (289.4 MB for 285.2 MB
                     # algorithmic); traffic is proportional to the keys read, so other shapes are scaled
-                    "traffic": alg_bytes * (290.1e6 / 285.212672e6),
+                    "traffic": alg_bytes * (289.37e6 / 285.212672e6),
                     "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": us, "context": ctx_mean}
         if d.get("chain") and n_l > 1:
             # the per-layer chain kernel (o_proj .. next QKV), one launch per layer so that weights stream from HBM
