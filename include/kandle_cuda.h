@@ -240,6 +240,15 @@ typedef enum kd_epilogue {
  * composite.ts:62-70 passes it), out [tokens,N] (or [tokens,N/2] for SWIGLU) bf16 or fp32. */
 int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* residual, int epilogue,
                    const kd_tensor* out);
+typedef enum kd_activation { KD_ACT_NONE = 0, KD_ACT_GELU = 1 } kd_activation;
+/* out = residual + act(x W^T + bias): `linear` with its bias (composite.ts:55-77), the `gelu` that
+ * follows fc1 in the Whisper block (packages/model-utils/src/whisper/block.ts:150-200; tanh form with
+ * the +-20 clamp of packages/backend-webgpu/src/kernels/pointwise/ops.ts:301) and the residual `add`,
+ * all in the GEMM epilogue on the fp32 accumulator.  bias [N] and residual [tokens,N] are optional
+ * (NULL); everything is bf16 and contiguous, weight rows may be strided (a row slice of a packed
+ * in_proj_weight, MultiheadAttention.ts:333-348). */
+int kd_linear_bf16_bias(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* bias,
+                        const kd_tensor* residual, int activation, const kd_tensor* out);
 
 /* `linear` for 1..128 activation rows (decode): weights are streamed once from HBM with the
  * operands swapped so that weight rows fill the MMA's M dimension.  The shape and dtype of `out`

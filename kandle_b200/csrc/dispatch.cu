@@ -15,6 +15,24 @@ KD_API int kd_matmul(const kd_matmul_cfg* cfg, const kd_tensor* a, const kd_tens
   int handled = 0;
   KD_TRY(matmul_tc_try(cfg, a, b, c, out, &handled));
   if (handled) return KD_OK;
+  // bf16 activations whose leading dimensions do not collapse into one row stride (the (L,N,E) view
+  // of a batch-first tensor that nn.MultiheadAttention projects,
+  // packages/core/src/nn/modules/attention/MultiheadAttention.ts:302-348): one strided copy into a
+  // dense temporary costs a few bytes per element, the general fp32-accumulate kernel costs two
+  // orders of magnitude more than the tensor-core GEMM that the copy makes possible.
+  if (a->dtype == KD_BF16 && b->dtype == KD_BF16 && b->ndim == 2 && a->ndim >= 3 && !cfg->transpose_a && !is_contiguous(a) &&
+      numel(a) >= (1 << 16)) {
+    kd_tensor dense = *a;
+    int64_t st = 1;
+    for (int d = a->ndim - 1; d >= 0; --d) { dense.strides[d] = st; st *= a->shape[d]; }
+    dense.offset = 0;
+    KD_TRY(kd_storage_alloc((uint64_t)numel(a) * 2, 0, &dense.storage));
+    int rc = kd_copy(&dense, a);
+    if (rc == KD_OK) rc = matmul_tc_try(cfg, &dense, b, c, out, &handled);
+    if (rc == KD_OK && !handled) rc = matmul_f32_dispatch(cfg, &dense, b, c, out);
+    kd_storage_release(dense.storage);   // stream-ordered: later users of the block queue behind the GEMM
+    return rc;
+  }
   return matmul_f32_dispatch(cfg, a, b, c, out);
 }
 
@@ -54,6 +72,36 @@ KD_API int kd_linear_bf16(const kd_tensor* x, const kd_tensor* weight, const kd_
     KD_TRY(tensor_ptr(residual, &pr));
   }
   return gemm_bf16(px, K, pw, weight->strides[0], po, n_out, out->dtype == KD_F32, pr, N, (int)M, (int)N, (int)K, epilogue);
+}
+
+KD_API int kd_linear_bf16_bias(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* bias, const kd_tensor* residual,
+                               int activation, const kd_tensor* out) {
+  KD_TRY(require_init());
+  KD_REQUIRE(x && weight && out, "null tensor");
+  KD_REQUIRE(activation == KD_ACT_NONE || activation == KD_ACT_GELU, "unknown activation %d", activation);
+  KD_REQUIRE(x->dtype == KD_BF16 && weight->dtype == KD_BF16 && out->dtype == KD_BF16, "kd_linear_bf16_bias needs bf16 tensors");
+  KD_REQUIRE(x->ndim >= 1 && weight->ndim == 2 && weight->strides[1] == 1, "weight must be [N,K] with unit K stride");
+  KD_REQUIRE(is_contiguous(x) && is_contiguous(out), "kd_linear_bf16_bias needs contiguous activations and output");
+  const int64_t K = x->shape[x->ndim - 1], N = weight->shape[0];
+  KD_REQUIRE(weight->shape[1] == K, "weight has K=%lld, activations have K=%lld", (long long)weight->shape[1], (long long)K);
+  const int64_t M = K ? numel(x) / K : 0;
+  KD_REQUIRE(numel(out) == M * N, "output has %lld elements, expected %lld", (long long)numel(out), (long long)(M * N));
+  if (M == 0) return KD_OK;
+  void *px = nullptr, *pw = nullptr, *pb = nullptr, *pr = nullptr, *po = nullptr;
+  KD_TRY(tensor_ptr(x, &px));
+  KD_TRY(tensor_ptr(weight, &pw));
+  KD_TRY(tensor_ptr(out, &po));
+  if (bias) {
+    KD_REQUIRE(bias->dtype == KD_BF16 && is_contiguous(bias) && numel(bias) == N, "bias must be contiguous bf16 [N]");
+    KD_TRY(tensor_ptr(bias, &pb));
+  }
+  if (residual) {
+    KD_REQUIRE(residual->dtype == KD_BF16 && is_contiguous(residual) && numel(residual) == M * N,
+               "residual must be contiguous bf16 of the output's shape");
+    KD_TRY(tensor_ptr(residual, &pr));
+  }
+  return gemm_bf16_bias_act(px, K, pw, weight->strides[0], po, N, 0, pr, N, (int)M, (int)N, (int)K, residual ? KD_EPI_RESIDUAL : KD_EPI_NONE,
+                            pb, activation);
 }
 
 static int decode_common(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* block_table,

@@ -88,6 +88,8 @@ struct GemmParams {
   const void* resid;      // bf16 when the output is bf16, fp32 when the output is fp32
   int64_t ldr;
   int epi;
+  const __nv_bfloat16* bias;   // [N] added to the accumulator before the activation and the residual, or null
+  int act;                     // 0 none, 1 GELU (tanh form) after the bias
   int num_m_tiles, num_n_tiles;
   int* err;
   // epi == 3: the columns are (Hq + 2 Hkv) heads of 128; q/k heads get RMSNorm over the head + RoPE,
@@ -114,6 +116,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+// GELU as the reference's shader writes it (packages/backend-webgpu/src/kernels/pointwise/ops.ts:301):
+// 0.5 x (1 + tanh(clamp(0.7978845608 (x + 0.044715 x^3), +-20))), with tanh(u) = 1 - 2 / (1 + exp(2u)).
+__device__ __forceinline__ float gelu_f(float x) {
+  const float u = fminf(fmaxf(0.7978845608f * (x + 0.044715f * x * x * x), -20.f), 20.f);
+  return x - __fdividef(x, 1.f + __expf(2.f * u));
+}
 __device__ __forceinline__ float silu_f(float x) {
   return x / (1.0f + __expf(-fminf(fmaxf(x, -88.f), 88.f)));
 }
@@ -308,6 +316,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tmem_wait_ld();
           if (row_ok) {
             const int col0 = n_tile * BLOCK_N + c0;
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col0 + j * 8 + 8 <= p.N) {
+                  const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col0 + j * 8);
+                  const uint32_t* bb = reinterpret_cast<const uint32_t*>(&bv);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    r[j * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e]) + bf16_lo(bb[e]));
+                    r[j * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e + 1]) + bf16_hi(bb[e]));
+                  }
+                }
+              }
+            }
+            if (p.act == 1) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(gelu_f(__uint_as_float(r[i])));
+            }
             if (p.epi == 1) {
               if (p.out_f32) {
                 const float* rrow = static_cast<const float*>(p.resid) + (int64_t)row * p.ldr + col0;
@@ -402,7 +428,14 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
 // out[M, N or N/2] = epilogue(A[M,K] * W[N,K]^T).  Pointers are device pointers; ld* in elements.
 int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out, int64_t ldo, int out_f32,
               const void* resid, int64_t ldr, int M, int N, int K, int epi) {
+  return gemm_bf16_bias_act(A, lda, W, ldw, out, ldo, out_f32, resid, ldr, M, N, K, epi, nullptr, 0);
+}
+
+int gemm_bf16_bias_act(const void* A, int64_t lda, const void* W, int64_t ldw, void* out, int64_t ldo, int out_f32,
+                       const void* resid, int64_t ldr, int M, int N, int K, int epi, const void* bias, int act) {
   KD_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem");
+  KD_REQUIRE((bias == nullptr && act == 0) || epi == 0 || epi == 1, "gemm: bias / activation combine only with the plain and residual epilogues");
+  KD_REQUIRE((reinterpret_cast<uintptr_t>(bias) & 15) == 0, "gemm: bias must be 16-byte aligned");
   KD_REQUIRE(K % 8 == 0, "gemm: K=%d must be a multiple of 8 for the tensor-core path", K);
   const int n_out = epi == 2 ? N / 2 : N;
   KD_REQUIRE(n_out % 8 == 0 && ldo % (out_f32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
@@ -416,6 +449,8 @@ int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out,
   p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
   p.resid = resid; p.ldr = ldr;
   p.epi = epi;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.act = act;
   p.err = ctx().error_flag;
   CUtensorMap ta, tb;
   KD_TRY(make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GEMM_BM, GEMM_BK));

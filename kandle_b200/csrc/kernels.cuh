@@ -25,6 +25,8 @@ int attention_f32_dispatch(const kd_tensor* q, const kd_tensor* k, const kd_tens
 // out[M, N or N/2] = epilogue(A[M,K] * W[N,K]^T) on tcgen05; device pointers, ld* in elements.
 int gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* out, int64_t ldo, int out_f32,
               const void* resid, int64_t ldr, int M, int N, int K, int epi);
+int gemm_bf16_bias_act(const void* A, int64_t lda, const void* W, int64_t ldw, void* out, int64_t ldo, int out_f32,
+              const void* resid, int64_t ldr, int M, int N, int K, int epi, const void* bias, int act);
 // Tensor-core attention; sets *handled = 1 when it took the call.
 int attention_tc_try(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out,
                      const AttnParams& p, int* handled);
