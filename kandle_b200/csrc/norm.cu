@@ -146,6 +146,98 @@ __global__ void __launch_bounds__(THREADS) norm_kernel(const void* __restrict__ 
   }
 }
 
+// bf16 rows of up to 2048 elements, dense: one warp per row, the row held in registers between the
+// statistics and the write (one read of x, 16-byte accesses).  Same arithmetic as norm_kernel.
+template <int MODE, int NV>
+__global__ void __launch_bounds__(256) norm_rows_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                            const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                            int64_t rows, int n, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int nvec = n >> 3;
+  for (int64_t row = warp0; row < rows; row += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * n);
+    float v[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      const int vi = lane + t * 32;
+      if (vi < nvec) {
+        const uint4 u = xr[vi];
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          v[t][e] = __bfloat162float(h[e]);
+          s += MODE == NORM_RMS ? v[t][e] * v[t][e] : v[t][e];
+        }
+      }
+    }
+    s = warp_sum(s);
+    float mean = 0.f, sc;
+    if (MODE == NORM_RMS) {
+      sc = 1.0f / sqrtf(s / (float)n + eps);
+    } else {
+      mean = s / (float)n;
+      float q = 0.f;
+#pragma unroll
+      for (int t = 0; t < NV; ++t) {
+        if (lane + t * 32 < nvec) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float d = v[t][e] - mean;
+            q += d * d;
+          }
+        }
+      }
+      q = warp_sum(q);
+      sc = 1.0f / sqrtf(q / (float)n + eps);
+    }
+    uint4* yr = reinterpret_cast<uint4*>(y + row * n);
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      const int vi = lane + t * 32;
+      if (vi < nvec) {
+        float wv[8], bv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { wv[e] = 1.f; bv[e] = 0.f; }
+        if (w) {
+          const uint4 u = reinterpret_cast<const uint4*>(w)[vi];
+          const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) wv[e] = __bfloat162float(h[e]);
+        }
+        if (MODE == NORM_LAYER && b) {
+          const uint4 u = reinterpret_cast<const uint4*>(b)[vi];
+          const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) bv[e] = __bfloat162float(h[e]);
+        }
+        uint4 o;
+        __nv_bfloat16* ho = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float r = (v[t][e] - mean) * sc;
+          if (w) r = r * wv[e];
+          if (MODE == NORM_LAYER && b) r = r + bv[e];
+          ho[e] = __float2bfloat16_rn(r);
+        }
+        yr[vi] = o;
+      }
+    }
+  }
+}
+
+template <int MODE, int NV>
+static void launch_norm_rows_bf16(const void* x, const void* w, const void* b, void* y, int64_t rows, int n, float eps) {
+  int64_t blocks = (rows + 7) / 8;
+  const int64_t cap = (int64_t)ctx().sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  norm_rows_bf16_kernel<MODE, NV><<<(int)blocks, 256, 0, ctx().stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(b),
+      static_cast<__nv_bfloat16*>(y), rows, n, eps);
+}
+
 template <int MODE>
 static int launch_norm(const kd_tensor* x, const kd_tensor* w, const kd_tensor* b, float eps, const kd_tensor* out,
                        const char* name) {
@@ -169,6 +261,17 @@ static int launch_norm(const kd_tensor* x, const kd_tensor* w, const kd_tensor* 
   const int sms = ctx().sm_count;
   cudaStream_t st = ctx().stream;
   const int dw = w ? w->dtype : KD_F32, db = b ? b->dtype : KD_F32;
+  if (MODE != NORM_SOFTMAX && x->dtype == KD_BF16 && out->dtype == KD_BF16 && is_contiguous(x) && n % 8 == 0 && n <= 2048 &&
+      (!w || w->dtype == KD_BF16) && (!b || b->dtype == KD_BF16) &&
+      ((reinterpret_cast<uintptr_t>(px) | reinterpret_cast<uintptr_t>(py) | reinterpret_cast<uintptr_t>(pw) |
+        reinterpret_cast<uintptr_t>(pb)) & 15) == 0) {
+    constexpr int M2 = MODE == NORM_SOFTMAX ? NORM_RMS : MODE;   // the softmax instantiation is never launched
+    if (n <= 256) launch_norm_rows_bf16<M2, 1>(px, pw, pb, py, rows, (int)n, eps);
+    else if (n <= 512) launch_norm_rows_bf16<M2, 2>(px, pw, pb, py, rows, (int)n, eps);
+    else if (n <= 1024) launch_norm_rows_bf16<M2, 4>(px, pw, pb, py, rows, (int)n, eps);
+    else launch_norm_rows_bf16<M2, 8>(px, pw, pb, py, rows, (int)n, eps);
+    return after_launch(name);
+  }
   if (n <= 512) {
     constexpr int T = 256;
     int64_t blocks = (rows + (T / 32) - 1) / (T / 32);
