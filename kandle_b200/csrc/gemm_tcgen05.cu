@@ -90,6 +90,8 @@ struct GemmParams {
   int epi;
   const __nv_bfloat16* bias;   // [N] added to the accumulator before the activation and the residual, or null
   int act;                     // 0 none, 1 GELU (tanh form) after the bias
+  int wide_store;              // bf16 output rows start on 32-byte boundaries: 32-byte vector stores
+  int wide_f32, wide_resid;    // the same for an fp32 output and for the residual operand
   int num_m_tiles, num_n_tiles;
   int* err;
   // epi == 3: the columns are (Hq + 2 Hkv) heads of 128; q/k heads get RMSNorm over the head + RoPE,
@@ -117,10 +119,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 // GELU as the reference's shader writes it (packages/backend-webgpu/src/kernels/pointwise/ops.ts:301):
-// 0.5 x (1 + tanh(clamp(0.7978845608 (x + 0.044715 x^3), +-20))), with tanh(u) = 1 - 2 / (1 + exp(2u)).
+// 0.5 x (1 + tanh(clamp(u, +-20))), u = 0.7978845608 (x + 0.044715 x^3), evaluated as
+// x / (1 + exp(-2u)) (the same function; tanh(+-20) is +-1 in fp32, so the clamp changes nothing).
+// The epilogue is bound by the special-function unit (a quarter-rate pipe shared by the four
+// epilogue warps of an SM), so this form spends exactly two such operations per element, ex2 and
+// rcp, and four FMA-pipe instructions: a = -2 u log2(e) = x (c1 + c2 x^2).
 __device__ __forceinline__ float gelu_f(float x) {
-  const float u = fminf(fmaxf(0.7978845608f * (x + 0.044715f * x * x * x), -20.f), 20.f);
-  return x - __fdividef(x, 1.f + __expf(2.f * u));
+  const float a = x * fmaf(x * x, -0.1029432394f, -2.3022081983f);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
 }
 __device__ __forceinline__ float silu_f(float x) {
   return x / (1.0f + __expf(-fminf(fmaxf(x, -88.f), 88.f)));
@@ -226,6 +235,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tc_fence_after();
       const int row = m_tile * GEMM_BM + q * 32 + lane;
       const bool row_ok = row < p.M;
+      bool released = false;   // accumulator already handed back inside the branch
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N);
       if (BLOCK_N == 256 && p.epi == 3) {
         // q/k-norm + RoPE + cache write (see fused.cu for the stand-alone kernel and the reference
@@ -279,12 +289,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const int hk = is_k ? head - p.Hq : head - p.Hq - p.Hkv;
             dst = (is_k ? p.k_cache : p.v_cache) + (int64_t)b_idx * p.kc_b + (int64_t)hk * p.kc_h + (int64_t)(p.pos0 + s_idx) * p.kc_s;
           }
+          if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
 #pragma unroll
-          for (int g = 0; g < 16; ++g)
-            reinterpret_cast<uint4*>(dst)[g] = make_uint4(pack_bf16(__uint_as_float(x[g * 8 + 0]), __uint_as_float(x[g * 8 + 1])),
-                                                          pack_bf16(__uint_as_float(x[g * 8 + 2]), __uint_as_float(x[g * 8 + 3])),
-                                                          pack_bf16(__uint_as_float(x[g * 8 + 4]), __uint_as_float(x[g * 8 + 5])),
-                                                          pack_bf16(__uint_as_float(x[g * 8 + 6]), __uint_as_float(x[g * 8 + 7])));
+            for (int g = 0; g < 8; ++g) {
+              uint32_t v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = pack_bf16(__uint_as_float(x[g * 16 + 2 * e]), __uint_as_float(x[g * 16 + 2 * e + 1]));
+              st_global_v8(dst + g * 16, v);
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 16; ++g)
+              reinterpret_cast<uint4*>(dst)[g] = make_uint4(pack_bf16(__uint_as_float(x[g * 8 + 0]), __uint_as_float(x[g * 8 + 1])),
+                                                            pack_bf16(__uint_as_float(x[g * 8 + 2]), __uint_as_float(x[g * 8 + 3])),
+                                                            pack_bf16(__uint_as_float(x[g * 8 + 4]), __uint_as_float(x[g * 8 + 5])),
+                                                            pack_bf16(__uint_as_float(x[g * 8 + 6]), __uint_as_float(x[g * 8 + 7])));
+          }
         }
       } else if (p.epi == 2) {
         // SiLU(gate) * up.  Weight rows interleave 16 gate rows with the 16 matching up rows, so each
@@ -304,16 +324,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               const float a1 = silu_f(__uint_as_float(r[2 * e + 1])) * __uint_as_float(r[16 + 2 * e + 1]);
               o[e] = pack_bf16(a0, a1);
             }
-            *reinterpret_cast<uint4*>(orow + c0 / 2) = make_uint4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<uint4*>(orow + c0 / 2 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+            if (p.wide_store) {
+              st_global_v8(orow + c0 / 2, o);
+            } else {
+              *reinterpret_cast<uint4*>(orow + c0 / 2) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(orow + c0 / 2 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+            }
           }
         }
       } else {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c0, r);
-          tmem_wait_ld();
+        // Two register buffers: the TMEM load of the next 32 columns is in flight while the current
+        // 32 are biased, activated, added to the residual, converted and stored; the accumulator is
+        // handed back to the MMA warp as soon as its last column has been read.
+        auto process = [&](uint32_t (&r)[32], const int c0) {
           if (row_ok) {
             const int col0 = n_tile * BLOCK_N + c0;
             if (p.bias != nullptr) {
@@ -337,6 +360,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (p.epi == 1) {
               if (p.out_f32) {
                 const float* rrow = static_cast<const float*>(p.resid) + (int64_t)row * p.ldr + col0;
+                if (p.wide_resid && col0 + 32 <= p.N) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    uint32_t v[8];
+                    ld_global_v8(rrow + j * 8, v);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) r[j * 8 + e] = __float_as_uint(__uint_as_float(r[j * 8 + e]) + __uint_as_float(v[e]));
+                  }
+                } else
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                   if (col0 + j * 4 + 4 <= p.N) {
@@ -349,6 +381,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
               } else {
                 const __nv_bfloat16* rrow = static_cast<const __nv_bfloat16*>(p.resid) + (int64_t)row * p.ldr + col0;
+                if (p.wide_resid && col0 + 32 <= p.N) {
+#pragma unroll
+                  for (int j = 0; j < 2; ++j) {
+                    uint32_t v[8];
+                    ld_global_v8(rrow + j * 16, v);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                      r[j * 16 + 2 * e] = __float_as_uint(__uint_as_float(r[j * 16 + 2 * e]) + bf16_lo(v[e]));
+                      r[j * 16 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[j * 16 + 2 * e + 1]) + bf16_hi(v[e]));
+                    }
+                  }
+                } else
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   if (col0 + j * 8 + 8 <= p.N) {
@@ -365,6 +409,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
             if (p.out_f32) {
               float* orow = static_cast<float*>(p.out) + (int64_t)row * p.ldo + col0;
+              if (p.wide_f32 && col0 + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint32_t v[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] = r[j * 8 + e];
+                  st_global_v8(orow + j * 8, v);
+                }
+              } else
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 if (col0 + j * 4 + 4 <= p.N)
@@ -374,6 +427,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               }
             } else {
               __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + col0;
+              if (p.wide_store && col0 + 32 <= p.N) {
+                // 32-byte stores: every store instruction fills whole 32-byte sectors of its 32 rows
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  uint32_t v[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] = pack_bf16(__uint_as_float(r[j * 16 + 2 * e]), __uint_as_float(r[j * 16 + 2 * e + 1]));
+                  st_global_v8(orow + j * 16, v);
+                }
+              } else
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 if (col0 + j * 8 + 8 <= p.N) {
@@ -387,11 +450,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               }
             }
           }
+        };
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BLOCK_N; c0 += 64) {
+          tmem_wait_ld();
+          tmem_ld_32x32(t_row + c0 + 32, rb);
+          process(ra, c0);
+          tmem_wait_ld();
+          if (c0 + 64 < BLOCK_N) {
+            tmem_ld_32x32(t_row + c0 + 64, ra);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            released = true;
+          }
+          process(rb, c0 + 32);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (!released) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -451,6 +534,9 @@ int gemm_bf16_bias_act(const void* A, int64_t lda, const void* W, int64_t ldw, v
   p.epi = epi;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.act = act;
+  p.wide_store = !out_f32 && ldo % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 31) == 0;
+  p.wide_f32 = out_f32 && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 31) == 0;
+  p.wide_resid = resid != nullptr && ldr % (out_f32 ? 8 : 16) == 0 && (reinterpret_cast<uintptr_t>(resid) & 31) == 0;
   p.err = ctx().error_flag;
   CUtensorMap ta, tb;
   KD_TRY(make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GEMM_BM, GEMM_BK));
