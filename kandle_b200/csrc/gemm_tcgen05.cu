@@ -131,8 +131,13 @@ __device__ __forceinline__ float gelu_f(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
   return x * r;
 }
+// x / (1 + exp(-clamp(x, +-88))) (packages/backend-webgpu/src/kernels/pointwise/ops.ts:299) as
+// x * rcp(1 + ex2(-x log2 e)): beyond the clamp the quotient is x or (-)0 to fp32 precision either way.
 __device__ __forceinline__ float silu_f(float x) {
-  return x / (1.0f + __expf(-fminf(fmaxf(x, -88.f), 88.f)));
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
 }
 
 template <int BLOCK_N, int STAGES>
@@ -310,11 +315,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         // SiLU(gate) * up.  Weight rows interleave 16 gate rows with the 16 matching up rows, so each
         // 32-column chunk of the accumulator holds 16 (gate, up) pairs and yields 16 outputs.
         __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + (int64_t)n_tile * (BLOCK_N / 2);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c0, r);
-          tmem_wait_ld();
+        auto process = [&](uint32_t (&r)[32], const int c0) {
           const int col = n_tile * (BLOCK_N / 2) + c0 / 2;
           if (row_ok && col + 16 <= p.N / 2) {
             uint32_t o[8];
@@ -331,6 +332,25 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               *reinterpret_cast<uint4*>(orow + c0 / 2 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
             }
           }
+        };
+        // same two-buffer schedule as the plain epilogue below
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BLOCK_N; c0 += 64) {
+          tmem_wait_ld();
+          tmem_ld_32x32(t_row + c0 + 32, rb);
+          process(ra, c0);
+          tmem_wait_ld();
+          if (c0 + 64 < BLOCK_N) {
+            tmem_ld_32x32(t_row + c0 + 64, ra);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            released = true;
+          }
+          process(rb, c0 + 32);
         }
       } else {
         // Two register buffers: the TMEM load of the next 32 columns is in flight while the current
