@@ -249,6 +249,16 @@ typedef enum kd_activation { KD_ACT_NONE = 0, KD_ACT_GELU = 1 } kd_activation;
  * in_proj_weight, MultiheadAttention.ts:333-348). */
 int kd_linear_bf16_bias(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* bias,
                         const kd_tensor* residual, int activation, const kd_tensor* out);
+/* conv1d on token-major activations for the Whisper stem (packages/model-utils/src/whisper/encoder.ts:
+ * 202-215: conv1 -> gelu -> conv2 -> gelu -> permute(0,2,1) -> + embed_positions): input [B,L,Cin],
+ * weight_kc [Cout, ksz*Cin] = the reference's [Cout,Cin,ksz] weight with the tap index moved in
+ * front of the channel index, out [B,Wout,Cout] = the reference's conv1d output already permuted to
+ * (0,2,1).  A vectorised im2col (three input rows side by side per output row) feeds the tensor-core
+ * GEMM; bias, GELU and an optional residual [B,Wout,Cout] (the position table repeated per clip) are
+ * applied in its epilogue.  All bf16, contiguous, channel counts multiples of 8. */
+int kd_conv1d_tokens_bf16(const kd_tensor* input, const kd_tensor* weight_kc, const kd_tensor* bias,
+                          const kd_tensor* residual, int activation, int ksz, int stride, int padding,
+                          const kd_tensor* out);
 
 /* `linear` for 1..128 activation rows (decode): weights are streamed once from HBM with the
  * operands swapped so that weight rows fill the MMA's M dimension.  The shape and dtype of `out`

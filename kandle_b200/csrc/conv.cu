@@ -44,9 +44,81 @@ __global__ void bias_transpose_kernel(const void* __restrict__ tmp, int dt_t, co
   }
 }
 
+// Token-major im2col: x [B, L, C] bf16 (C % 8 == 0) -> col [B*Wout, ksz*C], row (b,t) = the ksz input
+// rows t*stride - pad .. + ksz - 1 side by side (zeros outside the sequence).  16-byte copies,
+// coalesced on both sides.
+__global__ void im2col_tokens_bf16_kernel(const uint4* __restrict__ x, uint4* __restrict__ col, int B, int L, int cvec, int Wout,
+                                          int ksz, int stride, int pad) {
+  const int64_t rowvec = (int64_t)ksz * cvec;
+  const int64_t total = (int64_t)B * Wout * rowvec;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int64_t row = i / rowvec;
+    const int rem = (int)(i - row * rowvec);
+    const int j = rem / cvec, cv = rem - j * cvec;
+    const int b = (int)(row / Wout), t = (int)(row - (int64_t)b * Wout);
+    const int pos = t * stride - pad + j;
+    col[i] = (pos >= 0 && pos < L) ? x[((int64_t)b * L + pos) * cvec + cv] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 }  // namespace kd
 
 using namespace kd;
+
+KD_API int kd_conv1d_tokens_bf16(const kd_tensor* input, const kd_tensor* weight_kc, const kd_tensor* bias,
+                                 const kd_tensor* residual, int activation, int ksz, int stride, int padding,
+                                 const kd_tensor* out) {
+  KD_TRY(require_init());
+  KD_REQUIRE(input && weight_kc && out, "null tensor");
+  KD_REQUIRE(input->ndim == 3 && weight_kc->ndim == 2 && out->ndim == 3, "conv1d_tokens: input/output must be 3-D, the weight 2-D");
+  KD_REQUIRE(input->dtype == KD_BF16 && weight_kc->dtype == KD_BF16 && out->dtype == KD_BF16, "conv1d_tokens needs bf16 tensors");
+  KD_REQUIRE(is_contiguous(input) && is_contiguous(weight_kc) && is_contiguous(out), "conv1d_tokens needs contiguous tensors");
+  KD_REQUIRE(ksz >= 1 && stride >= 1 && padding >= 0, "conv1d_tokens: bad kernel size/stride/padding");
+  KD_REQUIRE(activation == KD_ACT_NONE || activation == KD_ACT_GELU, "unknown activation %d", activation);
+  const int B = (int)input->shape[0], L = (int)input->shape[1], C = (int)input->shape[2];
+  const int Cout = (int)weight_kc->shape[0];
+  KD_REQUIRE(C % 8 == 0 && Cout % 8 == 0, "conv1d_tokens: channel counts must be multiples of 8");
+  KD_REQUIRE(weight_kc->shape[1] == (int64_t)ksz * C, "conv1d_tokens: weight must be [Cout, ksz*Cin] with the tap index major");
+  const int Wout = (L + 2 * padding - ksz) / stride + 1;
+  KD_REQUIRE(Wout > 0, "conv1d_tokens: empty output");
+  KD_REQUIRE(out->shape[0] == B && out->shape[1] == Wout && out->shape[2] == Cout, "conv1d_tokens: output must be [%d,%d,%d]", B, Wout,
+             Cout);
+  void *px = nullptr, *pw = nullptr, *pb = nullptr, *pr = nullptr, *po = nullptr, *pcol = nullptr;
+  KD_TRY(tensor_ptr(input, &px));
+  KD_TRY(tensor_ptr(weight_kc, &pw));
+  KD_TRY(tensor_ptr(out, &po));
+  if (bias) {
+    KD_REQUIRE(bias->dtype == KD_BF16 && numel(bias) == Cout && is_contiguous(bias), "conv1d_tokens: bias must be contiguous bf16 [%d]", Cout);
+    KD_TRY(tensor_ptr(bias, &pb));
+  }
+  const int64_t rows = (int64_t)B * Wout, Kc = (int64_t)ksz * C;
+  if (residual) {
+    KD_REQUIRE(residual->dtype == KD_BF16 && is_contiguous(residual) && numel(residual) == rows * Cout,
+               "conv1d_tokens: residual must be contiguous bf16 of the output's shape");
+    KD_TRY(tensor_ptr(residual, &pr));
+  }
+  KD_REQUIRE((reinterpret_cast<uintptr_t>(px) & 15) == 0, "conv1d_tokens: input must be 16-byte aligned");
+  uint64_t col_s = 0;
+  KD_TRY(kd_storage_alloc((uint64_t)rows * Kc * 2, 0, &col_s));
+  kd_tensor col{};
+  col.storage = col_s; col.dtype = KD_BF16; col.ndim = 2; col.shape[0] = rows; col.shape[1] = Kc; col.strides[0] = Kc; col.strides[1] = 1;
+  int st = tensor_ptr(&col, &pcol);
+  if (st == KD_OK) {
+    const int64_t total = rows * (Kc / 8);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = (int64_t)ctx().sm_count * 32;
+    if (blocks > cap) blocks = cap;
+    im2col_tokens_bf16_kernel<<<(int)blocks, 256, 0, ctx().stream>>>(static_cast<const uint4*>(px), static_cast<uint4*>(pcol), B, L, C / 8,
+                                                                    Wout, ksz, stride, padding);
+    st = after_launch("im2col_tokens_bf16_kernel");
+  }
+  if (st == KD_OK)
+    st = gemm_bf16_bias_act(pcol, Kc, pw, Kc, po, Cout, 0, pr, Cout, (int)rows, Cout, (int)Kc, residual ? KD_EPI_RESIDUAL : KD_EPI_NONE, pb,
+                            activation);
+  kd_storage_release(col_s);
+  return st;
+}
 
 KD_API int kd_conv1d(const kd_tensor* input, const kd_tensor* weight, const kd_tensor* bias, int stride, int padding,
                      const kd_tensor* out) {

@@ -131,6 +131,7 @@ _SIGNATURES = {
     "kd_event_elapsed_ms": [_u64, _u64, ctypes.POINTER(ctypes.c_float)],
     "kd_event_destroy": [_u64],
     "kd_linear_bf16": [_T, _T, _T, ctypes.c_int, _T],
+    "kd_conv1d_tokens_bf16": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _T],
     "kd_linear_bf16_bias": [_T, _T, _T, _T, ctypes.c_int, _T],
     "kd_linear_bf16_skinny": [_T, _T, ctypes.c_int, _T],
     "kd_linear_bf16_skinny_splits": [ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)],

@@ -5,6 +5,7 @@
     python -m kandle_b200.microbench decode_attn --b 32 --hq 16 --hkv 8 --ctx 2176 --d 128
     python -m kandle_b200.microbench skinny --m 32 --n 151936 --k 1024
     python -m kandle_b200.microbench chain --m 32 --hidden 1024 --attn 2048 --inter 3072 --qkv 4096
+    python -m kandle_b200.microbench whisper_encoder --clips 64 [--eager]
 
 Each run prints one JSON line with the average launch time, the algorithmic work per launch and
 the achieved rate.  Inputs are seeded normal values (constant fills would flatter the power
@@ -132,6 +133,30 @@ def bench_chain(a) -> dict:
             "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
 
 
+def bench_whisper_encoder(a) -> dict:
+    """Whisper-small audio encoder (80 mel bins x 3000 frames -> 1500 x 768, 12 layers, 12 heads of
+    64) over a batch of clips in bf16 with seeded random weights: the fused fast path
+    (kandle_b200/whisper_engine.py), or with --eager the operator-by-operator module.
+    Algorithmic work: 344.2 GFLOP per clip (conv stems 6.4, per layer 21.2 linear + 6.9 attention)."""
+    from kandle_b200 import synth
+    from kandle_b200.model_utils import WhisperAudioEncoder, WhisperConfig
+    from kandle_b200.whisper_engine import WhisperEncoderEngine
+    w = synth.whisper_encoder_weights(n_mels=80, state=768, layers=a.layers, n_ctx=1500, std=0.02)
+    w = {k: lib.round_to_bf16(v) for k, v in w.items()}
+    cfg = WhisperConfig(nMels=80, nAudioCtx=1500, nAudioState=768, nAudioHead=12, nAudioLayer=a.layers, dtype="bfloat16")
+    enc = WhisperAudioEncoder(cfg)
+    enc.loadStateDict(w)
+    mel = _rand_bf16((a.clips, 80, 3000), 7)
+    run_enc = enc if a.eager else WhisperEncoderEngine(enc)
+
+    def run():
+        run_enc.forward(mel).dispose()
+    ms = _time(run, a.iters, a.warmup)
+    flops = a.clips * (6.4e9 + a.layers * 28.15e9)
+    return {"kernel": "whisper_encoder_" + ("eager" if a.eager else "engine"), "clips": a.clips, "layers": a.layers, "ms": ms,
+            "clips_per_s": a.clips / ms * 1e3, "flops": flops, "tflops": flops / ms / 1e9}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="which", required=True)
@@ -166,13 +191,17 @@ def main() -> None:
     ch.add_argument("--inter", type=int, default=3072)
     ch.add_argument("--qkv", type=int, default=4096)
     ch.add_argument("--sets", type=int, default=8)
-    for p in (g, t, dd, sk, ch):
+    we = sub.add_parser("whisper_encoder")
+    we.add_argument("--clips", type=int, default=64)
+    we.add_argument("--layers", type=int, default=12)
+    we.add_argument("--eager", action="store_true")
+    for p in (g, t, dd, sk, ch, we):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     kandle_b200.init(0)
     res = {"gemm": bench_gemm, "attn": bench_attn, "decode_attn": bench_decode_attn, "skinny": bench_skinny,
-           "chain": bench_chain}[a.which](a)
+           "chain": bench_chain, "whisper_encoder": bench_whisper_encoder}[a.which](a)
     print(json.dumps(res))
 
 

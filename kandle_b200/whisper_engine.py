@@ -14,9 +14,13 @@ strided [N,H,L,D] views of that one buffer and writes its output straight into [
 the tanh-form GELU and the residual adds run in the GEMM epilogue on the fp32 accumulator, so the
 activations are rounded to bf16 once per GEMM instead of once per operator.
 
-The convolution stem, the position table and the final LayerNorm go through the same operator
-kernels as the eager module.  The engine borrows the parameters of a loaded `WhisperAudioEncoder`
-(no copies) and needs bf16 storage; anything else raises.
+The convolution stem runs token-major: the mel input is transposed once to [N,L,nMels], each
+conv1d is a vectorised im2col (three input rows side by side) plus a GEMM against the tap-major
+weight with bias and GELU in the epilogue, and the second one also adds the position table, so its
+output is the [N,T,E] stream the blocks work on (no channel-first intermediate, no transposes).
+The final LayerNorm goes through the same operator kernel as the eager module.  The engine borrows
+the parameters of a loaded `WhisperAudioEncoder` (only the two conv weights are re-laid out) and
+needs bf16 storage; anything else raises.
 """
 from __future__ import annotations
 
@@ -45,6 +49,34 @@ class WhisperEncoderEngine:
         if self.D not in (64, 128) or self.E % 8:
             raise ValueError(f"head_dim {self.D} is not handled by the tensor-core attention kernel (64 or 128)")
         self.scale = 1.0 / math.sqrt(self.D)       # scaledDotProductAttention's default, composite.ts:272-275
+        if cfg.nMels % 8:
+            raise ValueError("the token-major stem needs a multiple of 8 mel bins")
+        # conv weights [Cout, Cin, 3] -> [Cout, 3*Cin] with the tap index in front of the channel index
+        self.w1 = self._tap_major(encoder.conv1.weight)
+        self.w2 = self._tap_major(encoder.conv2.weight)
+        self._pos = None                           # (B, T, tensor): the position table repeated per clip
+
+    @staticmethod
+    def _tap_major(w: Tensor) -> Tensor:
+        p = w.permute([0, 2, 1])
+        c = core.contiguous(p)
+        out = c.view(w.shape[0], w.shape[1] * w.shape[2])   # keeps the storage alive
+        p.dispose()
+        c.dispose()
+        return out
+
+    def _positions(self, B: int, T: int) -> Tensor:
+        """embed_positions[:T] repeated B times, [B,T,E]: the residual operand of the conv2 GEMM."""
+        if self._pos is not None and self._pos[0] == B and self._pos[1] == T:
+            return self._pos[2]
+        if self._pos is not None:
+            self._pos[2].dispose()
+        pos = self.enc.embed_positions.weight.slice([slice(0, T), slice(None)])
+        out = core.empty((B, T, self.E), "bfloat16")
+        core.copy_(out, pos)                       # broadcast copy
+        pos.dispose()
+        self._pos = (B, T, out)
+        return out
 
     # ------------------------------------------------------------------ one block
     def _block(self, blk, x: Tensor) -> Tensor:
@@ -82,17 +114,19 @@ class WhisperEncoderEngine:
         if mel.dtype != "bfloat16":
             raise ValueError("WhisperEncoderEngine.forward needs a bfloat16 mel tensor")
         enc = self.enc
-        c1 = enc.conv1(mel)
-        g1 = core.gelu(c1)
-        c2 = enc.conv2(g1)
-        g2 = core.gelu(c2)
-        xt = g2.permute([0, 2, 1])
-        T = xt.shape[1]
+        B, _, L = mel.shape
+        E = self.E
+        T = (L + 2 - 3) // 2 + 1                   # conv2: kernel 3, stride 2, padding 1
         if T > enc.config.nAudioCtx:
             raise ValueError(f"{T} frames exceed the encoder context of {enc.config.nAudioCtx}")
-        pos = enc.embed_positions.weight.slice([slice(0, T), slice(None)])
-        x = core.add(xt, pos)                      # contiguous [B,T,E]
-        for t in (c1, g1, c2, g2, xt, pos):
+        mt = mel.permute([0, 2, 1])
+        mel_t = core.contiguous(mt)                # [B, L, nMels]
+        h1 = core.empty((B, L, E), "bfloat16")
+        lib.call("kd_conv1d_tokens_bf16", _r(mel_t), _r(self.w1), _r(enc.conv1.bias), None, KD_ACT_GELU, 3, 1, 1, _r(h1))
+        x = core.empty((B, T, E), "bfloat16")
+        pos = self._positions(B, T)
+        lib.call("kd_conv1d_tokens_bf16", _r(h1), _r(self.w2), _r(enc.conv2.bias), _r(pos), KD_ACT_GELU, 3, 2, 1, _r(x))
+        for t in (mt, mel_t, h1):
             t.dispose()
         for blk in enc.layers:
             x2 = self._block(blk, x)
