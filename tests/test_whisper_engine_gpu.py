@@ -73,6 +73,38 @@ def test_linear_bias_takes_a_row_slice_of_a_packed_weight_and_rejects_bad_operan
         lib.call("kd_linear_bf16_bias", _r(tx), _r(w1), _r(b1), None, 7, _r(out))
 
 
+@pytest.mark.parametrize("B,Cin,L,Cout,ksz,stride,pad,act,resid", [
+    (2, 80, 300, 768, 3, 1, 1, 1, False),      # Whisper conv1 form (bias + GELU)
+    (3, 64, 101, 96, 3, 2, 1, 1, True),        # conv2 form: stride 2, odd length, position residual
+    (1, 8, 16, 8, 1, 1, 0, 0, False),          # pointwise conv, one clip, narrow GEMM tile
+    (2, 16, 37, 40, 5, 3, 2, 0, True),         # wider kernel, stride 3, padding 2
+])
+def test_conv1d_tokens_against_the_channel_first_oracle(backend, oracle, B, Cin, L, Cout, ksz, stride, pad, act, resid):
+    """kd_conv1d_tokens_bf16 = the reference's conv1d (im2col.ts:124-268) on a permuted layout: feed the
+    oracle the channel-first tensors, compare with its output permuted to (0,2,1)."""
+    x = _rb(synth.normal(f"ct-x{Cin}", (B, Cin, L)))
+    w = _rb(synth.normal(f"ct-w{Cout}", (Cout, Cin, ksz), 0.1))
+    b = _rb(synth.normal(f"ct-b{Cout}", (Cout,), 0.5))
+    ref = oracle.conv1d(x, w, b, stride, pad)                     # [B, Cout, Wout]
+    Wout = ref.shape[2]
+    if act:
+        ref = oracle.unary("gelu", ref)
+    ref = np.ascontiguousarray(ref.transpose(0, 2, 1))
+    r = _rb(synth.normal(f"ct-r{Cout}", (B, Wout, Cout))) if resid else None
+    if r is not None:
+        ref = ref + r
+    bf = lambda a: Tensor(np.ascontiguousarray(a), dtype="bfloat16") if a is not None else None  # noqa: E731
+    tx = bf(x.transpose(0, 2, 1))                                 # [B, L, Cin]
+    tw = bf(w.transpose(0, 2, 1).reshape(Cout, ksz * Cin))        # tap index in front of the channel index
+    tb, tr = bf(b), bf(r)
+    out = core.empty((B, Wout, Cout), "bfloat16")
+    lib.call("kd_conv1d_tokens_bf16", _r(tx), _r(tw), _r(tb), _r(tr), act, ksz, stride, pad, _r(out))
+    err = np.abs(out.dataAsync().astype(np.float64) - ref)
+    assert (err <= np.abs(ref) * 2.0 ** -8 + 1e-5 * np.abs(ref).max()).all(), err.max()
+    with pytest.raises(lib.KandleCudaError):                      # weight of the wrong width
+        lib.call("kd_conv1d_tokens_bf16", _r(tx), _r(tw), _r(tb), None, act, ksz + 1, stride, pad, _r(out))
+
+
 def _build(oracle, *, n_mels, state, heads, layers, n_ctx, std):
     w = synth.whisper_encoder_weights(n_mels=n_mels, state=state, layers=layers, n_ctx=n_ctx, std=std)
     w = {k: lib.round_to_bf16(v) for k, v in w.items()}
