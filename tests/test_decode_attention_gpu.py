@@ -33,8 +33,13 @@ def _decode(q, kc, vc, ctx, splits=0, ctx_on_device=False, table=None):
 
 
 def _check(got, ref, rel=2e-2):
-    err = np.abs(got - ref).max()
-    assert err <= rel * np.abs(ref).max(), f"{err:.3e} > {rel * np.abs(ref).max():.3e}"
+    err = np.abs(got - ref)
+    bound = rel * np.abs(ref).max()
+    if not (err.max() <= bound):
+        bad = np.argwhere(~(err <= bound))
+        rows = sorted({(int(i[0]), int(i[1])) for i in bad})      # (sequence, query head) pairs that are off
+        raise AssertionError(f"{np.nanmax(err):.3e} > {bound:.3e}; {len(bad)} elements off ({int(np.isnan(got).sum())} NaN) "
+                             f"in {len(rows)} (sequence, head) rows, first {rows[:8]}")
 
 
 @pytest.mark.parametrize("b,hq,hkv,max_s,ctx,d,splits", [
