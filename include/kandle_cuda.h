@@ -318,7 +318,9 @@ int kd_graph_destroy(uint64_t graph);
  * `ctx_len` (device int32 scalar, so a captured graph can be replayed as the sequence grows) or,
  * when that is NULL, from ctx_len_host.  splits = 0 picks the split-KV factor automatically.
  * Scratch for the split partials is library-owned and grows on demand (the first call at a larger
- * size allocates, so make that call before capturing a graph). */
+ * size allocates, so make that call before capturing a graph).  Whole 64-row key tiles are loaded:
+ * cache rows between ctx and the end of the last tile get probability 0 but are multiplied in, so
+ * they must hold finite values (the reference's cache is created from zeros, kv-cache.ts:123-130). */
 int kd_attention_decode(const kd_tensor* q, const kd_tensor* k_cache, const kd_tensor* v_cache,
                         const kd_tensor* ctx_len, int ctx_len_host, float scale, int splits,
                         const kd_tensor* out);
