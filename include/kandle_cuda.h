@@ -103,6 +103,15 @@ int kd_host_alloc_pinned(uint64_t bytes, void** host_out);
 int kd_host_free_pinned(void* host);
 /* Allocator statistics: bytes handed out, bytes cached in free lists, bytes obtained from CUDA. */
 int kd_memory_stats(uint64_t* in_use, uint64_t* cached, uint64_t* reserved);
+/* Size of the library-owned scratch buffer (split-KV partials, split-K partials, sampling state).  It
+ * is obtained straight from CUDA, outside the allocator above, and only ever grows.  No counterpart
+ * in the reference (its kernels create their own temporaries,
+ * packages/backend-webgpu/src/kernels/normalize/executor.ts:120-122). */
+int kd_workspace_bytes(uint64_t* bytes_out);
+/* Test support, no counterpart in the reference: overwrites that scratch buffer and the built-in
+ * buffer of kd_attention_decode_noalloc with `byte_value` (stream-ordered), so that a test can tell
+ * a kernel that read a slot it never wrote (0xFF gives NaN patterns) from one that did not. */
+int kd_debug_fill_scratch(int byte_value);
 int kd_empty_cache(void);
 
 /* ---------------------------------------------------------------------------------------------

@@ -142,7 +142,12 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   uint64_t* p_ready = bars + 15;           // 2
   uint64_t* o_done = bars + 17;            // 1
   uint64_t* x_bar = bars + 18;             // 2: row-maximum exchange between the softmax warpgroups
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  // Completion of the LAST P V product.  It cannot be read off o_done: with two S buffers Q K^T of
+  // block j+1 is issued before P V of block j, so when the softmax warps have finished the last
+  // block the tensor pipe is only known to have completed P V of block n-3; o_done may then still be
+  // two phases behind, and a parity wait cannot tell "phase n-1 complete" from "phase n-3 complete".
+  uint64_t* o_final = bars + 20;           // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xchg = reinterpret_cast<float*>(tmem_slot + 4);   // [2 buffers][2 warpgroups][128 rows]
 
@@ -162,7 +167,12 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     j_begin = (int)blockIdx.x * per_split;
     j_end = min(n_total, j_begin + per_split);
     if (j_begin >= j_end) {     // nothing for this split: publish an empty partial and leave
-      if ((int)threadIdx.x < p.group) {
+      if (p.direct) {
+        // a single split without any key (context length 0 read from device memory): attention over
+        // no keys is defined here as a zero row, so that `out` never keeps stale contents
+        for (int i = threadIdx.x; i < p.group * D; i += blockDim.x)
+          p.o[(int64_t)b * p.so_b + (int64_t)(hk * p.group + i / D) * p.so_h + (i % D)] = __float2bfloat16_rn(0.f);
+      } else if ((int)threadIdx.x < p.group) {
         const int64_t slot = (((int64_t)b * p.Hkv + hk) * p.splits + blockIdx.x) * p.group + threadIdx.x;
         p.part_ml[slot * 2] = -1e30f;
         p.part_ml[slot * 2 + 1] = 0.f;
@@ -188,6 +198,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     for (int s = 0; s < NSBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4 * NWG); }
     for (int s = 0; s < 2; ++s) mbar_init(&x_bar[s], 4 * NWG);
     mbar_init(o_done, 1);
+    mbar_init(o_final, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmap_q);
@@ -276,6 +287,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
         }
         umma_commit(&t_empty[stage]);
         umma_commit(o_done);
+        if (j + 1 == n_blocks) umma_commit(o_final);
         // one S buffer: the next QK^T overwrites P, so it is issued after PV (in-order pipe)
         if (NSBUF == 1 && j + 1 < n_blocks) {
           if (!issue_qk(j + 1)) break;
@@ -394,7 +406,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
           if (lane == 0) mbar_arrive(&p_ready[j % NSBUF]);
         }
         if (ok) {
-          ok = mbar_wait(o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, p.err, 309);
+          ok = mbar_wait(o_final, 0, abort_flag, p.err, 309);
           ok = __all_sync(0xffffffffu, ok);
         }
         // Epilogue: sum the four partial O rows and row sums of every query through shared memory
@@ -551,7 +563,7 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
       if (lane == 0) mbar_arrive(&p_ready[j % NSBUF]);
     }
     if (ok) {
-      ok = mbar_wait(o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, p.err, 309);
+      ok = mbar_wait(o_final, 0, abort_flag, p.err, 309);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok && NWG == 2) {
@@ -750,7 +762,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
       if (d < D) acc[i] += w * po[d];
     }
   }
-  const float inv = 1.0f / denom;
+  const float inv = denom > 0.f ? 1.0f / denom : 0.f;   // no key at all (context length 0): a zero row
   __nv_bfloat16* orow = out + (int64_t)b * so_b + (int64_t)h * so_h;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -849,10 +861,9 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
 constexpr size_t STATIC_SCRATCH_BYTES = 8u << 20;
 static __device__ __align__(256) unsigned char g_decode_static_scratch[STATIC_SCRATCH_BYTES];
 
-int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
-                            const int* ctx_dev, int ctx_host, int splits) {
-  // In host code the array's name is only a handle for the symbol, not a device address: the
-  // address the kernels may use has to be asked for, once per device, with that device current.
+// In host code the array's name is only a handle for the symbol, not a device address: the
+// address the kernels may use has to be asked for, once per device, with that device current.
+static int static_scratch_address(void** out) {
   static void* scratch_ptr[64] = {nullptr};
   const int dev = ctx().device;
   KD_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
@@ -865,6 +876,22 @@ int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_ten
     }
     scratch_ptr[dev] = p;
   }
+  *out = scratch_ptr[dev];
+  return KD_OK;
+}
+
+// Test support: overwrite the built-in scratch with a byte pattern (stream-ordered).
+int attention_decode_static_fill(int byte_value) {
+  void* p = nullptr;
+  KD_TRY(static_scratch_address(&p));
+  KD_CUDA_CHECK(cudaMemsetAsync(p, byte_value, STATIC_SCRATCH_BYTES, ctx().stream));
+  return KD_OK;
+}
+
+int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
+                            const int* ctx_dev, int ctx_host, int splits) {
+  void* scratch = nullptr;
+  KD_TRY(static_scratch_address(&scratch));
   KD_REQUIRE(q && k && q->ndim == 4 && k->ndim == 4, "decode attention operands must be 4-D");
   const int B = (int)q->shape[0], Hq = (int)q->shape[1], Hkv = (int)k->shape[1], D = (int)q->shape[3];
   KD_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "bad head counts");
@@ -881,7 +908,7 @@ int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_ten
                 "kd_attention_decode_noalloc: batch %d x %d kv heads x %d splits needs %zu bytes of scratch, the built-in "
                 "buffer holds %zu; lower `splits` or use kd_attention_decode",
                 B, Hkv, splits, need, STATIC_SCRATCH_BYTES);
-  return attention_decode(q, k, v, out, scale, ctx_dev, ctx_host, nullptr, 0, splits, scratch_ptr[dev], STATIC_SCRATCH_BYTES);
+  return attention_decode(q, k, v, out, scale, ctx_dev, ctx_host, nullptr, 0, splits, scratch, STATIC_SCRATCH_BYTES);
 }
 
 }  // namespace kd

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "kernels.cuh"
 
 namespace kd {
 
@@ -395,6 +396,20 @@ KD_API int kd_memory_stats(uint64_t* in_use, uint64_t* cached, uint64_t* reserve
   if (cached) *cached = g_alloc.cached;
   if (reserved) *reserved = g_alloc.reserved;
   return KD_OK;
+}
+
+KD_API int kd_workspace_bytes(uint64_t* bytes_out) {
+  KD_TRY(require_init());
+  if (!bytes_out) return fail(KD_ERR_INVALID, "null argument");
+  *bytes_out = ctx().workspace_bytes;
+  return KD_OK;
+}
+
+KD_API int kd_debug_fill_scratch(int byte_value) {
+  KD_TRY(require_init());
+  Context& c = ctx();
+  if (c.workspace) KD_CUDA_CHECK(cudaMemsetAsync(c.workspace, byte_value, c.workspace_bytes, c.stream));
+  return attention_decode_static_fill(byte_value);
 }
 
 KD_API int kd_empty_cache(void) {

@@ -46,4 +46,6 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
 int attention_decode_static(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v, const kd_tensor* out, float scale,
                             const int* ctx_dev, int ctx_host, int splits);
 
+int attention_decode_static_fill(int byte_value);
+
 }  // namespace kd

@@ -114,6 +114,8 @@ _SIGNATURES = {
     "kd_host_free_pinned": [ctypes.c_void_p],
     "kd_memory_stats": [ctypes.POINTER(_u64), ctypes.POINTER(_u64), ctypes.POINTER(_u64)],
     "kd_empty_cache": [],
+    "kd_workspace_bytes": [ctypes.POINTER(_u64)],
+    "kd_debug_fill_scratch": [ctypes.c_int],
     "kd_flash_attention": [_T, _T, _T, _T, ctypes.c_float, ctypes.c_int],
     "kd_matmul": [ctypes.POINTER(kd_matmul_cfg), _T, _T, _T, _T],
     "kd_rms_norm": [_T, _T, ctypes.c_float, _T],
