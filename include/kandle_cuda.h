@@ -182,6 +182,19 @@ int kd_copy(const kd_tensor* dst, const kd_tensor* src);
 int kd_fill(const kd_tensor* dst, double value);
 /* Key `arange` (packages/backend-webgpu/src/kernels/factory/index.ts:27): dst[i] = start+i*step. */
 int kd_arange(const kd_tensor* dst, double start, double step);
+/* Key `randn` (packages/backend-webgpu/src/kernels/random/shaderBuilder.ts:140-185 with the
+ * Philox4x32-10 generator of random/philox.wgsl.ts:17-155 and the counter / key rule of
+ * random/executor.ts:31-49): element i of the tensor takes member i % 2 of pair i / 2, whose counter
+ * is [i / 2 + base_offset (mod 2^32), 0, 0, 0] under the key (seed & 0xffffffff, seed >> 32);
+ * uniform = (word >> 8) * 2^-24; cosine branch of Box-Muller with u1 clamped to 1e-10;
+ * out = mean + stddev * z.  `seed` and `base_offset` are what the reference's RandomState hands its
+ * kernel (packages/types/src/random.ts:77-96); the binding keeps that state.
+ * full_cols <= 0: `out` is a whole contiguous tensor numbered in row-major order (row0 = col0 = 0).
+ * full_cols  > 0: `out` is the [rows, cols] slice at (row0, col0) of a row-major matrix with
+ * full_cols columns and receives exactly the numbers that matrix would hold there, which is how a
+ * tensor-parallel rank initialises its share of a weight (no counterpart in the reference). */
+int kd_randn(const kd_tensor* out, uint64_t seed, uint32_t base_offset, float mean, float stddev, int64_t row0,
+             int64_t col0, int64_t full_cols);
 /* Key `argmax` over the last dimension, int32 or int64 output; lowest index wins ties:
  * packages/backend-webgpu/src/kernels/reduction/argShaderBuilder.ts:29-247. */
 int kd_argmax(const kd_tensor* x, const kd_tensor* out);

@@ -381,6 +381,19 @@ def empty(shape, dtype: str = "float32") -> Tensor:
     return Tensor(_handle=_new(shape, dtype))
 
 
+def manualSeed(seed: int) -> None:
+    """Seeds the generator behind `randn` (packages/types/src/random.ts:52-60)."""
+    from .kernels import RandomState
+    RandomState.manual_seed(seed)
+
+
+def randn(shape, dtype: str = "float32") -> Tensor:
+    """N(0,1) numbers from the device generator (packages/core/src/generated/internal/randn.ts)."""
+    out = _new(shape, dtype)
+    _kernel("randn")(TensorIterator([], [out]))
+    return Tensor(_handle=out)
+
+
 def arange(start, end=None, step=1, dtype: str = "int32") -> Tensor:
     if end is None:
         start, end = 0, start

@@ -46,10 +46,23 @@ def interleave_gate_up(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     return np.stack([gate.reshape(I // 16, 16, K), up.reshape(I // 16, 16, K)], axis=1).reshape(2 * I, K)
 
 
+class RandomInit:
+    """Stands in for a weight dictionary: every linear / embedding weight is drawn N(0, std) on the
+    device by the `randn` kernel (Philox4x32-10 keyed by `seed`), RMSNorm weights are ones as the
+    modules construct them (packages/core/src/nn/modules/normalization/RMSNorm.ts:85).  Each tensor
+    of the FULL model owns a fixed range of the generator's counter space, and a tensor-parallel
+    rank draws exactly the rows / columns it owns, so every rank count sees the same model and no
+    weight ever exists on the host."""
+
+    def __init__(self, seed: int = 1234, std: float = 0.02):
+        self.seed, self.std = int(seed), float(std)
+
+
 class Qwen3Engine:
-    def __init__(self, cfg: Qwen3Config, weights: dict, max_batch: int, max_seq_len: int, tp_size: int = 1):
-        """weights: HuggingFace-style names -> float32 arrays (rounded to bf16 on upload).  With
-        tp_size > 1 `weights` is this rank's tensor-parallel slice (parallel.shard_qwen3_weights), cfg
+    def __init__(self, cfg: Qwen3Config, weights, max_batch: int, max_seq_len: int, tp_size: int = 1, tp_rank: int = 0):
+        """weights: HuggingFace-style names -> float32 arrays (rounded to bf16 on upload), or a
+        RandomInit.  With tp_size > 1 a weight dictionary is this rank's tensor-parallel slice
+        (parallel.shard_qwen3_weights; a RandomInit draws rank `tp_rank`'s slice itself), cfg
         describes the FULL model, and the library's communicator must have been initialised: the
         partial outputs of o_proj and down_proj are all-reduced before the residual add."""
         self.cfg = cfg
@@ -66,10 +79,13 @@ class Qwen3Engine:
             raise ValueError("the fused engine supports head_dim 64 or 128")
         self.nqkv = (self.Hq + 2 * self.Hkv) * self.D
         bf = lambda a: Tensor(np.ascontiguousarray(a, dtype=np.float32), dtype="bfloat16")  # noqa: E731
-        self.embed = bf(weights["model.embed_tokens.weight"])
-        self.final_norm = bf(weights["model.norm.weight"])
         self.layers = []
-        for i in range(self.L):
+        if isinstance(weights, RandomInit):
+            self._random_weights(weights, int(tp_rank))
+        else:
+            self.embed = bf(weights["model.embed_tokens.weight"])
+            self.final_norm = bf(weights["model.norm.weight"])
+        for i in range(self.L if not isinstance(weights, RandomInit) else 0):
             p = f"model.layers.{i}."
             self.layers.append({
                 "in_norm": bf(weights[p + "input_layernorm.weight"]),
@@ -97,6 +113,42 @@ class Qwen3Engine:
         # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
         self.use_chain = self.tp == 1 and self.H <= 4096
         self.sampler = None   # None: greedy argmax; else dict(temperature, top_k, top_p, rng), see set_sampler
+
+    def _random_weights(self, init: RandomInit, rank: int) -> None:
+        c, tp, D = self.cfg, self.tp, self.D
+        Hq_full, Hkv_full, I_full, H = c.numAttentionHeads, c.numKeyValueHeads, c.intermediateSize, self.H
+        state = {"offset": 0}
+
+        def draw(out: Tensor, full_rows: int, full_cols: int, row0: int = 0, col0: int = 0, reserve: bool = True) -> None:
+            """`out` = the [rows, cols] block at (row0, col0) of a full_rows x full_cols weight whose
+            numbers start at the current generator offset."""
+            lib.call("kd_randn", _r(out), ctypes.c_uint64(init.seed), ctypes.c_uint32(state["offset"] & 0xFFFFFFFF),
+                     ctypes.c_float(0.0), ctypes.c_float(init.std), row0, col0, full_cols)
+            if reserve:
+                state["offset"] += (full_rows * full_cols + 1) // 2
+
+        e = lambda *shape: core.empty(shape, "bfloat16")  # noqa: E731
+        self.embed = e(self.V, H)
+        draw(self.embed, self.V, H)
+        self.final_norm = core.ones((H,), "bfloat16")
+        for _ in range(self.L):
+            wqkv = e(self.nqkv, H)
+            r0 = 0
+            for heads_full, heads_local in ((Hq_full, self.Hq), (Hkv_full, self.Hkv), (Hkv_full, self.Hkv)):   # q, k, v
+                part = wqkv.slice([slice(r0, r0 + heads_local * D), slice(None)])
+                draw(part, heads_full * D, H, row0=rank * heads_local * D)
+                part.dispose()
+                r0 += heads_local * D
+            wo = e(H, self.Hq * D)
+            draw(wo, H, Hq_full * D, col0=rank * self.Hq * D)
+            wgu = e(2 * self.I, H)            # drawn directly in the interleaved row order (16 gate rows, 16 up rows)
+            draw(wgu, 2 * I_full, H, row0=rank * 2 * self.I)
+            wdown = e(H, self.I)
+            draw(wdown, H, I_full, col0=rank * self.I)
+            self.layers.append({
+                "in_norm": core.ones((H,), "bfloat16"), "post_norm": core.ones((H,), "bfloat16"), "wqkv": wqkv,
+                "q_norm": core.ones((D,), "bfloat16"), "k_norm": core.ones((D,), "bfloat16"), "wo": wo, "wgu": wgu, "wdown": wdown,
+            })
 
     # ------------------------------------------------------------------ helpers
     def _linear(self, x, w, out, resid=None, epi=0):
@@ -241,6 +293,7 @@ class Qwen3Engine:
     def _decode_state(self, B: int) -> dict:
         if self._decode is not None and self._decode["B"] == B:
             return self._decode
+        self.dispose()        # another batch size: the captured graph of the old state goes with it
         def splits(n, k):
             s = ctypes.c_int(0)
             lib.call("kd_linear_bf16_skinny_splits", ctypes.c_int64(n), ctypes.c_int64(k), ctypes.byref(s))

@@ -108,6 +108,32 @@ def _arange(it: TensorIterator) -> None:
              ctypes.c_double(float(s.get("step", 1))))
 
 
+class RandomState:
+    """Global generator state the random kernels draw from (packages/types/src/random.ts:20-104):
+    a 64-bit seed that becomes the Philox key and an offset that advances by the number of Philox
+    calls each operation consumes, so that consecutive operations give different numbers."""
+    seed = 0
+    offset = 0
+
+    @classmethod
+    def manual_seed(cls, seed: int) -> None:
+        cls.seed, cls.offset = int(seed) & 0xFFFFFFFFFFFFFFFF, 0
+
+    @classmethod
+    def consume_offset(cls, count: int) -> int:
+        cur = cls.offset
+        cls.offset += int(count)
+        return cur
+
+
+def _randn(it: TensorIterator) -> None:
+    """Key `randn`: N(0,1) into the pre-allocated output (executor.ts:31-49: numel / 2 Philox calls)."""
+    out = it.output()
+    base = RandomState.consume_offset((out.numel + 1) // 2)
+    lib.call("kd_randn", _ref(out), ctypes.c_uint64(RandomState.seed), ctypes.c_uint32(base & 0xFFFFFFFF), ctypes.c_float(0.0),
+             ctypes.c_float(1.0), 0, 0, 0)
+
+
 def _argmax(it: TensorIterator) -> None:
     lib.call("kd_argmax", _ref(it.input(0)), _ref(it.output()))
 
@@ -178,6 +204,7 @@ def register_cuda_kernels(ops) -> None:
     ops.register("full", _fill(None))
     ops.register("empty", _empty)
     ops.register("arange", _arange)
+    ops.register("randn", _randn)
     ops.register("argmax", _argmax)
     ops.register("matmul", _matmul)
     ops.register("rms_norm", _rms_norm)

@@ -127,6 +127,7 @@ _SIGNATURES = {
     "kd_fill": [_T, ctypes.c_double],
     "kd_arange": [_T, ctypes.c_double, ctypes.c_double],
     "kd_argmax": [_T, _T],
+    "kd_randn": [_T, _u64, ctypes.c_uint32, ctypes.c_float, ctypes.c_float, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64],
     "kd_conv1d": [_T, _T, _T, ctypes.c_int, ctypes.c_int, _T],
     "kd_event_create": [ctypes.POINTER(_u64)],
     "kd_event_record": [_u64],

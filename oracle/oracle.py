@@ -222,6 +222,48 @@ def embedding(w: np.ndarray, ids: np.ndarray) -> np.ndarray:
     return out.reshape(*ids.shape, w.shape[1])
 
 
+_PHILOX_M0, _PHILOX_M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+_PHILOX_W0, _PHILOX_W1 = 0x9E3779B9, 0xBB67AE85
+
+
+def philox4x32_10(counter: np.ndarray, key0: int, key1: int) -> np.ndarray:
+    """Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3",
+    SC'11) as the reference states it in WGSL
+    (packages/backend-webgpu/src/kernels/random/philox.wgsl.ts:33-113): counter [n,4] uint32 ->
+    [n,4] uint32.  Round: (hi1 ^ c1 ^ k0, lo1, hi0 ^ c3 ^ k1, lo0) with (hi0,lo0) = M0*c0,
+    (hi1,lo1) = M1*c2; the key grows by (W0, W1) between rounds, not after the last."""
+    c = np.array(counter, dtype=np.uint32).reshape(-1, 4).copy()
+    k0, k1 = int(key0) & 0xFFFFFFFF, int(key1) & 0xFFFFFFFF
+    for _ in range(10):
+        p0 = _PHILOX_M0 * c[:, 0].astype(np.uint64)
+        p1 = _PHILOX_M1 * c[:, 2].astype(np.uint64)
+        n0 = (p1 >> np.uint64(32)).astype(np.uint32) ^ c[:, 1] ^ np.uint32(k0)
+        n2 = (p0 >> np.uint64(32)).astype(np.uint32) ^ c[:, 3] ^ np.uint32(k1)
+        c = np.stack([n0, p1.astype(np.uint32), n2, p0.astype(np.uint32)], axis=1)
+        k0, k1 = (k0 + _PHILOX_W0) & 0xFFFFFFFF, (k1 + _PHILOX_W1) & 0xFFFFFFFF
+    return c
+
+
+def randn(numel: int, seed: int, base_offset: int = 0, first: int = 0) -> np.ndarray:
+    """Elements [first, first + numel) of the reference's `randn` stream
+    (packages/backend-webgpu/src/kernels/random/shaderBuilder.ts:140-185): element i is member i % 2
+    of pair i // 2, counter [pair + base_offset mod 2^32, 0, 0, 0], key = (seed low word, seed high
+    word) (random/executor.ts:31-49, packages/types/src/random.ts:77-81); member 0 uses output words
+    (x, y), member 1 (z, w); uniform = (w >> 8) * 2^-24 (philox.wgsl.ts:126-129); z = sqrt(-2 ln
+    max(u1, 1e-10)) * cos(2 pi u2) in float32 (philox.wgsl.ts:146-154)."""
+    i = np.arange(first, first + numel, dtype=np.uint64)
+    ctr = np.zeros((numel, 4), np.uint32)
+    ctr[:, 0] = ((i >> np.uint64(1)) + np.uint64(base_offset & 0xFFFFFFFF)).astype(np.uint32)   # wraps mod 2^32
+    r = philox4x32_10(ctr, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    odd = (i & np.uint64(1)).astype(bool)
+    w1 = np.where(odd, r[:, 2], r[:, 0])
+    w2 = np.where(odd, r[:, 3], r[:, 1])
+    u1 = np.maximum((w1 >> np.uint32(8)).astype(np.float32) * np.float32(5.9604644775390625e-8), np.float32(1e-10))
+    u2 = (w2 >> np.uint32(8)).astype(np.float32) * np.float32(5.9604644775390625e-8)
+    rad = np.sqrt(np.float32(-2.0) * np.log(u1, dtype=np.float32), dtype=np.float32)
+    return (rad * np.cos(np.float32(6.283185307179586) * u2, dtype=np.float32)).astype(np.float32)
+
+
 def argmax_rows(x: np.ndarray) -> np.ndarray:
     x = _f32(x)
     n = x.shape[-1]

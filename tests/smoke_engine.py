@@ -4,9 +4,9 @@ from __future__ import annotations
 
 import numpy as np
 
-from . import synth
-from .core import Tensor
-from .model_utils import Qwen3Config, Qwen3ForCausalLM
+from kandle_b200 import synth
+from kandle_b200.core import Tensor
+from kandle_b200.model_utils import Qwen3Config, Qwen3ForCausalLM
 
 
 def run(backend, orc) -> None:
@@ -29,8 +29,8 @@ def run(backend, orc) -> None:
     print(f"smoke: tiny Qwen3 fp32 prefill error {err:.2e}, 4 greedy steps identical to the oracle")
 
     # fused bf16 engine (tensor-core GEMMs, tcgen05 attention, split-KV decode, graph replay)
-    from . import lib
-    from .engine import Qwen3Engine
+    from kandle_b200 import lib
+    from kandle_b200.engine import Qwen3Engine
     dims = dict(vocab=512, hidden=256, inter=512, layers=2, heads=4, kv_heads=2, head_dim=128)
     wb = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(std=0.04, **dims).items()}
     cfg = Qwen3Config(vocabSize=512, hiddenSize=256, intermediateSize=512, numHiddenLayers=2, numAttentionHeads=4,

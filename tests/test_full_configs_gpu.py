@@ -40,7 +40,10 @@ def test_config2_qwen3_0p6b_fp32_prefill_512(backend, oracle):
     assert np.array_equal(got.argmax(-1), ref.argmax(-1))
 
 
-def test_config3_qwen3_0p6b_bf16_engine(backend, oracle):
+@pytest.fixture(scope="module")
+def config3_run(backend, oracle):
+    """One sequence x 512 prompt tokens + 8 greedy steps of the 0.6B bf16 engine and the figures every
+    config-3 test below looks at (the model is built once)."""
     w = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(**DIMS).items()}
     cfg = Qwen3Config(dtype="bfloat16")
     eng = Qwen3Engine(cfg, w, 8, 640)
@@ -50,23 +53,48 @@ def test_config3_qwen3_0p6b_bf16_engine(backend, oracle):
     ref = om.logits(ids)
     got = logits.dataAsync()
     err = np.abs(got - ref)
-    assert np.quantile(err, 0.999) <= 2e-2 and err.max() <= 3.5e-2, (err.max(), np.quantile(err, 0.999))
-    # With random-init weights the 151 936 logits of a position are nearly flat: the oracle's own
-    # top-2 gap is below the 2e-2 logit tolerance on ~15 % of positions, where bf16 cannot decide the
-    # argmax.  Measured: 97.7 % identical over all positions, 100 % where the gap exceeds 2e-2.
     same = got.reshape(-1, 151936).argmax(-1) == ref.reshape(-1, 151936).argmax(-1)
     top2 = np.partition(ref.reshape(-1, 151936), -2, axis=-1)[:, -2:]
     decidable = (top2[:, 1] - top2[:, 0]) > 2e-2
-    assert same[decidable].mean() >= 0.995 and same.mean() >= 0.95, (same[decidable].mean(), same.mean(), decidable.mean())
     steps = 8
     toks = eng.generate(ids, steps)
     seq = np.concatenate([ids, toks[:, :-1].astype(np.int32)], axis=1)
     picks = om.logits(seq)[:, 511:].argmax(-1)          # teacher-forced on the engine's own tokens
-    assert (picks == toks).mean() >= 0.75, (picks, toks)
-    # independence of sequences at batch 8: identical prompts -> identical rows == the single-sequence run
     t8 = eng.generate(np.repeat(ids, 8, axis=0), steps)
-    assert (t8 == t8[0]).all() and np.array_equal(t8[:1], toks)
     eng.dispose()
+    r = dict(err_max=float(err.max()), err_p999=float(np.quantile(err, 0.999)), err_rms=float(np.sqrt((err ** 2).mean())),
+             ref_absmax=float(np.abs(ref).max()), argmax_same=float(same.mean()), argmax_same_decidable=float(same[decidable].mean()),
+             decidable=float(decidable.mean()), decode_same=float((picks == toks).mean()), toks=toks, t8=t8)
+    print("config 3 bf16 vs fp32 oracle: " + ", ".join(f"{k}={v:.4g}" for k, v in r.items() if not isinstance(v, np.ndarray)))
+    return r
+
+
+def test_config3_qwen3_0p6b_bf16_engine(config3_run):
+    """Regression guard at the figures this build reaches (see the next test for the stated bar)."""
+    r = config3_run
+    assert r["err_p999"] <= 2e-2 and r["err_max"] <= 3.5e-2, (r["err_max"], r["err_p999"])
+    # With random-init weights the 151 936 logits of a position are nearly flat: the oracle's own
+    # top-2 gap is below the 2e-2 logit tolerance on ~15 % of positions, where bf16 cannot decide the
+    # argmax.  Measured: 97.7 % identical over all positions, 100 % where the gap exceeds 2e-2.
+    assert r["argmax_same_decidable"] >= 0.995 and r["argmax_same"] >= 0.95, (r["argmax_same_decidable"], r["argmax_same"], r["decidable"])
+    assert r["decode_same"] >= 0.75
+    # independence of sequences at batch 8: identical prompts -> identical rows == the single-sequence run
+    assert (r["t8"] == r["t8"][0]).all() and np.array_equal(r["t8"][:1], r["toks"])
+
+
+@pytest.mark.xfail(strict=True, reason="bf16 activations on random-init (nearly flat) logits: measured max-abs 2.0-2.3e-2 and "
+                   "97.7 % identical argmax; the figures are printed by the fixture")
+def test_config3_literal_north_star_bar(config3_run):
+    """The stated bar, asserted literally: max-abs <= 2e-2 on the logits and identical greedy argmax
+    on >= 99 % of the positions, all positions counted.  Kept as an expected failure so that the gap
+    stays visible: the per-layer rounding of bf16 activations (16-bit storage, fp32 compute, one
+    rounding per operator output, packages/backend-webgpu/src/kernels/matrix/builder.ts:68-78) leaves
+    an rms logit error of 4e-3 whatever the depth, its maximum over 7.8e7 logits is 5.5 sigma, and the
+    oracle's own top-2 gap is below that error on one position in seven."""
+    r = config3_run
+    assert r["err_max"] <= 2e-2, f"max-abs logit error {r['err_max']:.3e} (p99.9 {r['err_p999']:.3e}, rms {r['err_rms']:.3e})"
+    assert r["argmax_same"] >= 0.99, f"identical argmax on {r['argmax_same']:.4f} of positions ({r['argmax_same_decidable']:.4f} of the decidable ones)"
+    assert r["decode_same"] >= 0.99, f"teacher-forced decode agreement {r['decode_same']:.3f}"
 
 
 def test_config5_whisper_small_encoder_fp32_12_layers(backend, oracle):

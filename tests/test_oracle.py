@@ -373,3 +373,25 @@ def test_mel_filterbank_against_an_independent_slaney_formulation():
     spec = np.fft.rfft(x)
     got = x @ basis.astype(np.float64)
     assert np.abs(got[:201] - spec.real).max() <= 1e-4 and np.abs(got[201:] - spec.imag).max() <= 1e-4
+
+
+def test_philox4x32_10_known_answer_vectors():
+    """The generator under the reference's `randn` key is Philox4x32-10; its authors' known-answer
+    vectors (Random123 kat_vectors, philox4x32 with 10 rounds) pin the restatement bit for bit."""
+    from oracle import oracle as orc
+    kat = [((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+           ((0xffffffff,) * 4, (0xffffffff, 0xffffffff), (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+           ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0), (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1))]
+    for ctr, key, want in kat:
+        got = orc.philox4x32_10(np.array([ctr], np.uint32), key[0], key[1])[0]
+        assert tuple(int(x) for x in got) == want
+
+
+def test_randn_stream_is_normal_and_windows_agree():
+    from oracle import oracle as orc
+    z = orc.randn(400000, 77, base_offset=5)
+    assert abs(float(z.mean())) < 5e-3 and abs(float(z.std()) - 1.0) < 5e-3
+    assert abs(float((z ** 3).mean())) < 2e-2 and abs(float((z ** 4).mean()) - 3.0) < 5e-2
+    # a window of the stream equals the same elements of the whole stream; the offset shifts pairs
+    assert np.array_equal(orc.randn(1000, 77, base_offset=5, first=1235), z[1235:2235])
+    assert np.array_equal(orc.randn(1000, 77, base_offset=6), z[2:1002])
