@@ -393,6 +393,32 @@ int kd_decode_layer_chain(const kd_tensor* attn, const kd_tensor* w_o, const kd_
                           const kd_tensor* resid_mid, const kd_tensor* resid_out, const kd_tensor* x_out,
                           const kd_tensor* act, const kd_tensor* qkv_partials);
 int kd_decode_layer_chain_splits(int64_t N, int64_t K, int* splits_out);
+/* The same stretch of a decode step in FOUR dependent phases, and further: up to and including the
+ * next layer's q_norm / k_norm, rotary embedding and KV-cache write
+ * (packages/model-utils/src/attention/gqa.ts:274-322, rope.ts:546-644, kv-cache.ts:164-212), so that
+ * a decode step is two launches per layer (this one and kd_attention_decode).
+ *   h1 = resid_in + attn W_o^T                 split-K; the CTA that finishes a 128-row tile last sums
+ *                                              the splits in split order and adds the residual
+ *   act = silu(rs1 (x1 Wg^T)) * (rs1 (x1 Wu^T))  x1 = bf16(h1 * post_norm_w), rs1 = 1/sqrt(mean(h1^2)+eps):
+ *                                              RMSNorm's per-sequence scale is applied to the fp32
+ *                                              accumulator instead of to the activations
+ *   resid_out = h1 + act W_down^T              split-K as above; x2 = bf16(resid_out * next_norm_w)
+ *   qkv = rs2 (x2 W_qkv_next^T)                split-K; the CTA that completes a head's 128 rows does that
+ *                                              head's RMSNorm (q_norm_w / k_norm_w), the rotation by
+ *                                              cos/sin [1,64] and stores q into q_out [Mb,1,Hq,128] or
+ *                                              k / v into row *pos of the next layer's caches
+ * With w_qkv_next == NULL (after the last layer) the launch ends with
+ * x_final = bf16(resid_out * rs2 * next_norm_w), the lm_head's input, and the arguments from
+ * q_norm_w to q_out are ignored.  head_dim 128 only; 1 <= Mb <= 128; resid_out may be resid_in.
+ * A cache row outside [0, maxS) is not written and reports KD_ERR_DEVICE code 102, a wait that runs
+ * out codes 521-528.  Results are bit-identical from launch to launch. */
+int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
+                          const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
+                          const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
+                          const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
+                          const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
+                          const kd_tensor* v_cache_next, const kd_tensor* q_out, const kd_tensor* resid_out,
+                          const kd_tensor* x_final);
 
 /* ---------------------------------------------------------------------------------------------
  * Tensor-parallel collectives (no counterpart in the reference, which is single-device).  One

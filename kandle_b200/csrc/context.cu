@@ -173,7 +173,7 @@ static void release_retired_workspaces() {
 
 }  // namespace kd
 
-namespace kd { int decode_chain_reset_counters(); }
+namespace kd { int decode_chain_reset_counters(); int decode_layer_reset_counters(); }
 
 using namespace kd;
 
@@ -252,6 +252,7 @@ static int check_device_flag() {
   if (h[0] != 0) {
     cudaMemsetAsync(c.error_flag, 0, sizeof(h), c.stream);
     decode_chain_reset_counters();
+    decode_layer_reset_counters();
     return fail(KD_ERR_DEVICE, "a kernel reported error code %d (detail %d, %d, %d)", h[0], h[1], h[2], h[3]);
   }
   return KD_OK;

@@ -33,6 +33,7 @@
 // consumer spins (bounded, ~1 s, then error 5xx and the CTA drains) on ld.acquire until the counter
 // reaches gridDim.  The last CTA to leave zeroes the counters for the next launch.
 // Roofline: HBM, the bytes of the four weight matrices per launch.
+#include "chain_common.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
 #include "sm100.cuh"
@@ -84,40 +85,6 @@ struct ChainMaps {
   CUtensorMap w[4];
   CUtensorMap x[4];
 };
-
-__device__ __forceinline__ float chain_silu(float x) {
-  const float c = fminf(fmaxf(x, -88.f), 88.f);   // the reference clamps before exp
-  return __fdividef(x, 1.f + __expf(-c));
-}
-
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Bounded wait until counter >= target.
-__device__ __forceinline__ bool counter_wait(const unsigned* cnt, unsigned target, volatile int* abort_flag, int* err, int code) {
-  if (ld_acquire_u32(cnt) >= target) return true;
-  const long long t0 = clock64();
-  int spins = 0;
-  while (ld_acquire_u32(cnt) < target) {
-    if (((++spins) & 15) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_CYCLE_LIMIT) {
-        *abort_flag = 1;
-        if (atomicCAS(err, 0, code) == 0) { err[1] = (int)blockIdx.x; err[2] = (int)threadIdx.x; err[3] = (int)target; }
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // phase p: 0 G0, 1 N0, 2 G1, 3 G2, 4 N1, 5 G3
 __device__ __forceinline__ int phase_gemm_index(int p) { return p == 0 ? 0 : (p == 2 ? 1 : (p == 3 ? 2 : (p == 5 ? 3 : -1))); }

@@ -112,6 +112,9 @@ class Qwen3Engine:
         # decode: run o_proj .. next layer's QKV as one persistent kernel per layer (kd_decode_layer_chain);
         # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
         self.use_chain = self.tp == 1 and self.H <= 4096
+        # ... and further, through the next layer's q/k-norm + RoPE + cache write, in four phases
+        # (kd_decode_layer_fused): two launches per layer and decode step
+        self.use_fused_layer = self.tp == 1 and self.D == 128 and self.H <= 8192
         self.sampler = None   # None: greedy argmax; else dict(temperature, top_k, top_p, rng), see set_sampler
 
     def _random_weights(self, init: RandomInit, rank: int) -> None:
@@ -305,7 +308,7 @@ class Qwen3Engine:
             lib.call("kd_decode_layer_chain_splits", ctypes.c_int64(n), ctypes.c_int64(k), ctypes.byref(s))
             return s.value
         d = {
-            "B": B, "graph": None, "chain": self.use_chain,
+            "B": B, "graph": None, "chain": self.use_chain, "fused": self.use_fused_layer,
             "scalars": core.zeros((2,), "int32"),           # [write position, context length]
             "ids": core.zeros((B,), "int64"), "emb": e(B, self.H), "h": f(B, self.H), "h1": f(B, self.H), "x": e(B, self.H),
             # a projection whose suggested split factor is 1 writes bf16 directly, otherwise fp32 partials
@@ -316,7 +319,7 @@ class Qwen3Engine:
             "down_p": f(splits(self.H, self.I), B, self.H), "logits": f(1, B, self.V),
             "cos": f(1, self.D // 2), "sin": f(1, self.D // 2), "uniforms": core.zeros((B,), "float32"),
         }
-        if self.use_chain:
+        if self.use_chain and not self.use_fused_layer:
             d["qkv_p"].dispose()
             d["qkv_p"] = f(chain_splits(self.nqkv, self.H), B, self.nqkv)
         d["pos"] = d["scalars"].slice([slice(0, 1)])
@@ -346,12 +349,29 @@ class Qwen3Engine:
         for li, lw in enumerate(self.layers):
             kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
             vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
-            if li == 0 or not d["chain"]:
+            if li == 0 or not (d["chain"] or d["fused"]):
                 lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wqkv"]), 0, _r(d["qkv_p"]))
-            lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
-                     _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
+            if li == 0 or not d["fused"]:
+                lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
+                         _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
             lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
             nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
+            if d["fused"]:
+                if li + 1 < self.L:
+                    nl = self.layers[li + 1]
+                    kn = self.k_cache[li + 1].slice([slice(0, B), slice(None), slice(None), slice(None)])
+                    vn = self.v_cache[li + 1].slice([slice(0, B), slice(None), slice(None), slice(None)])
+                    lib.call("kd_decode_layer_fused", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
+                             _r(lw["wdown"]), _r(nxt), eps, _r(nl["wqkv"]), _r(nl["q_norm"]), _r(nl["k_norm"]), _r(d["cos"]),
+                             _r(d["sin"]), _r(d["pos"]), _r(kn), _r(vn), _r(d["q"]), _r(h), None)
+                    kn.dispose()
+                    vn.dispose()
+                else:
+                    lib.call("kd_decode_layer_fused", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
+                             _r(lw["wdown"]), _r(nxt), eps, None, None, None, None, None, None, None, None, None, _r(h), _r(d["x"]))
+                kc.dispose()
+                vc.dispose()
+                continue
             if d["chain"]:
                 last = li + 1 == self.L
                 lib.call("kd_decode_layer_chain", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),

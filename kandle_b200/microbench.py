@@ -5,6 +5,7 @@
     python -m kandle_b200.microbench decode_attn --b 32 --hq 16 --hkv 8 --ctx 2176 --d 128
     python -m kandle_b200.microbench skinny --m 32 --n 151936 --k 1024
     python -m kandle_b200.microbench chain --m 32 --hidden 1024 --attn 2048 --inter 3072 --qkv 4096
+    python -m kandle_b200.microbench layer --m 32 --hidden 1024 --attn 2048 --inter 3072 --hq 16 --hkv 8
     python -m kandle_b200.microbench whisper_encoder --clips 64 [--eager]
 
 Each run prints one JSON line with the average launch time, the algorithmic work per launch and
@@ -133,6 +134,36 @@ def bench_chain(a) -> dict:
             "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
 
 
+def bench_layer(a) -> dict:
+    """kd_decode_layer_fused over several weight sets visited round-robin (see bench_chain)."""
+    m, H, Ko, I, hq, hkv = a.m, a.hidden, a.attn, a.inter, a.hq, a.hkv
+    Nq = (hq + 2 * hkv) * 128
+    sets = []
+    for i in range(a.sets):
+        sets.append({"wo": _rand_bf16((H, Ko), 10 + i, 0.03), "wgu": _rand_bf16((2 * I, H), 20 + i, 0.03),
+                     "wd": _rand_bf16((H, I), 30 + i, 0.03), "wq": _rand_bf16((Nq, H), 40 + i, 0.03),
+                     "kc": core.zeros((m, hkv, 64, 128), "bfloat16"), "vc": core.zeros((m, hkv, 64, 128), "bfloat16")})
+    attn = _rand_bf16((m, Ko), 1)
+    post, nxt, qw, kw = _rand_bf16((H,), 2), _rand_bf16((H,), 3), _rand_bf16((128,), 4), _rand_bf16((128,), 5)
+    h = Tensor(np.zeros((m, H), np.float32))
+    h2 = core.empty((m, H), "float32")
+    cos, sin = Tensor(np.ones((1, 64), np.float32)), Tensor(np.zeros((1, 64), np.float32))
+    pos = Tensor(np.array([3], np.int32))
+    q = core.empty((m, 1, hq, 128), "bfloat16")
+    r = lambda t: ctypes.byref(t._handle.c())  # noqa: E731
+    state = {"i": 0}
+
+    def run():
+        w = sets[state["i"] % a.sets]
+        state["i"] += 1
+        lib.call("kd_decode_layer_fused", r(attn), r(w["wo"]), r(h), r(post), r(w["wgu"]), r(w["wd"]), r(nxt), ctypes.c_float(1e-6),
+                 r(w["wq"]), r(qw), r(kw), r(cos), r(sin), r(pos), r(w["kc"]), r(w["vc"]), r(q), r(h2), None)
+    ms = _time(run, a.iters, a.warmup)
+    nbytes = 2.0 * (H * Ko + 2 * I * H + H * I + Nq * H)
+    return {"kernel": "decode_layer_kernel", "m": m, "hidden": H, "attn": Ko, "inter": I, "qkv": Nq, "weight_sets": a.sets,
+            "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+
+
 def bench_whisper_encoder(a) -> dict:
     """Whisper-small audio encoder (80 mel bins x 3000 frames -> 1500 x 768, 12 layers, 12 heads of
     64) over a batch of clips in bf16 with seeded random weights: the fused fast path
@@ -191,17 +222,25 @@ def main() -> None:
     ch.add_argument("--inter", type=int, default=3072)
     ch.add_argument("--qkv", type=int, default=4096)
     ch.add_argument("--sets", type=int, default=8)
+    ly = sub.add_parser("layer")
+    ly.add_argument("--m", type=int, default=32)
+    ly.add_argument("--hidden", type=int, default=1024)
+    ly.add_argument("--attn", type=int, default=2048)
+    ly.add_argument("--inter", type=int, default=3072)
+    ly.add_argument("--hq", type=int, default=16)
+    ly.add_argument("--hkv", type=int, default=8)
+    ly.add_argument("--sets", type=int, default=8)
     we = sub.add_parser("whisper_encoder")
     we.add_argument("--clips", type=int, default=64)
     we.add_argument("--layers", type=int, default=12)
     we.add_argument("--eager", action="store_true")
-    for p in (g, t, dd, sk, ch, we):
+    for p in (g, t, dd, sk, ch, ly, we):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     kandle_b200.init(0)
     res = {"gemm": bench_gemm, "attn": bench_attn, "decode_attn": bench_decode_attn, "skinny": bench_skinny,
-           "chain": bench_chain, "whisper_encoder": bench_whisper_encoder}[a.which](a)
+           "chain": bench_chain, "layer": bench_layer, "whisper_encoder": bench_whisper_encoder}[a.which](a)
     print(json.dumps(res))
 
 

@@ -97,6 +97,73 @@ def test_config3_literal_north_star_bar(config3_run):
     assert r["decode_same"] >= 0.99, f"teacher-forced decode agreement {r['decode_same']:.3f}"
 
 
+def test_config3_stated_sizes_one_sequence_2048_prompt_and_decode_beyond_2048(backend, oracle):
+    """One sequence of the benchmark's batch at its stated sizes: a 2048-token prompt (sixteen 128-row
+    query tiles, causal) and 16 cached decode steps at context lengths 2049..2064 (split-KV decode
+    attention whose last key tile is ragged), through the bf16 engine sized like the benchmark's
+    (cache of 2320 positions), against the fp32 oracle on the same bf16-rounded weights."""
+    w = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(**DIMS).items()}
+    eng = Qwen3Engine(Qwen3Config(dtype="bfloat16"), w, 2, 2320)
+    ids = synth.token_ids("c3.ids.full", (1, 2048), 151936)
+    om = _oracle_model(oracle, w)
+    steps = 17
+    toks = eng.generate(ids, steps)
+    # last-position logits of the prefill as the engine computed them (fp32, [1, B, V])
+    seq = np.concatenate([ids, toks[:, :-1].astype(np.int32)], axis=1)            # teacher-forced on the engine's tokens
+    ref = om.logits(seq)[:, 2047:]                                                 # [1, steps, V]
+    picks = ref.argmax(-1)
+    top2 = np.partition(ref.reshape(-1, 151936), -2, axis=-1)[:, -2:]
+    gap = top2[:, 1] - top2[:, 0]
+    # where the engine picked another token than the oracle, the oracle's logit of that token must be
+    # within the bf16 tolerance of its maximum (a near-tie of the flat random-init distribution)
+    chosen = np.take_along_axis(ref, toks[:, :, None], axis=-1)[..., 0]
+    short = (ref.max(-1) - chosen).max()
+    print(f"config 3 at 2048+16: token agreement {(picks == toks).mean():.3f}, worst shortfall of a picked token {short:.3e}, "
+          f"smallest oracle top-2 gap {gap.min():.3e}")
+    assert short <= 4e-2, short
+    assert (picks == toks)[gap.reshape(1, -1) > 4e-2].all()
+    eng.dispose()
+
+
+def test_config4_qwen3_4b_layer_shapes_two_layers_one_gpu(backend, oracle):
+    """The layer shapes of the 4B configuration (hidden 2560, 32 query / 8 KV heads x 128, MLP 9728) on
+    one GPU: prefill logits and cached decode against the oracle.  The tensor-parallel runs of the same
+    shapes are in test_tp_gpu.py."""
+    dims = dict(vocab=4096, hidden=2560, inter=9728, layers=2, heads=32, kv_heads=8, head_dim=128)
+    w = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(**dims).items()}
+    cfg = Qwen3Config(vocabSize=4096, hiddenSize=2560, intermediateSize=9728, numHiddenLayers=2, numAttentionHeads=32,
+                      numKeyValueHeads=8, headDim=128, dtype="bfloat16")
+    eng = Qwen3Engine(cfg, w, 2, 288)
+    ocfg = oracle.Qwen3Config(vocab_size=4096, hidden_size=2560, intermediate_size=9728, num_hidden_layers=2,
+                              num_attention_heads=32, num_key_value_heads=8, head_dim=128)
+    om = oracle.Qwen3Oracle(ocfg, w)
+    ids = synth.token_ids("c4.ids", (2, 200), 4096)
+    tok, logits = eng.prefill(ids, all_logits=True)
+    ref = om.logits(ids)
+    err = np.abs(logits.dataAsync() - ref)
+    print(f"config 4 layer shapes: logits max err {err.max():.3e}, p99.9 {np.quantile(err, 0.999):.3e}, |ref| max {np.abs(ref).max():.2f}")
+    assert np.quantile(err, 0.999) <= 2e-2 * max(1.0, np.abs(ref).max() / 3) and err.max() <= 3e-2 * max(1.0, np.abs(ref).max() / 3)
+    toks = eng.generate(ids, 6)
+    t_ref = om.greedy_generate(ids, 6, max_seq_len=288).astype(np.int64)
+    assert (toks == t_ref).mean() >= 0.8, (toks, t_ref)
+    eng.dispose()
+
+
+def test_config5_whisper_small_encoder_bf16_engine_12_layers(backend, oracle):
+    """The bf16 fast path of the Whisper-small encoder at its full depth on one 30 s clip."""
+    from kandle_b200.whisper_engine import WhisperEncoderEngine
+    w = {k: lib.round_to_bf16(v) for k, v in synth.whisper_encoder_weights(n_mels=80, state=768, layers=12, n_ctx=1500).items()}
+    enc = WhisperAudioEncoder(WhisperConfig(dtype="bfloat16"))
+    enc.loadStateDict(w)
+    mel = lib.round_to_bf16(synth.normal("c5.mel", (1, 80, 3000), 0.5))
+    y = WhisperEncoderEngine(enc).forward(Tensor(mel, dtype="bfloat16")).dataAsync()
+    ref = oracle.WhisperEncoderOracle(oracle.WhisperEncoderConfig(), w).forward(mel)
+    err = np.abs(y.astype(np.float64) - ref)
+    scale = np.abs(ref).max()
+    print(f"config 5 bf16 engine, 12 layers: max err {err.max() / scale:.3e} of |ref| max, p99.9 {np.quantile(err, 0.999) / scale:.3e}")
+    assert np.quantile(err, 0.999) <= 2e-2 * scale and err.max() <= 6e-2 * scale
+
+
 def test_config5_whisper_small_encoder_fp32_12_layers(backend, oracle):
     w = synth.whisper_encoder_weights(n_mels=80, state=768, layers=12, n_ctx=1500)
     enc = WhisperAudioEncoder(WhisperConfig())

@@ -1,5 +1,8 @@
-"""Tensor-parallel engine on 2 GPUs (NCCL all-reduce after o_proj and down_proj) against the CPU
-oracle of the unsharded model.  Needs two GPUs; on a single-GPU box the test is skipped."""
+"""Tensor-parallel engine on 2 / 4 / 8 GPUs (all-reduce after o_proj and down_proj) against the CPU
+oracle of the unsharded model, at a toy shape and at the layer shapes of the Qwen3-4B configuration
+(hidden 2560, 32 query / 8 KV heads, MLP 9728).  Each case needs that many GPUs and is skipped on
+a smaller box; the single-GPU engine at the same 4B layer shapes is checked in
+test_full_configs_gpu.py."""
 import os
 import subprocess
 import sys
@@ -10,13 +13,23 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_tensor_parallel_two_ranks_match_oracle():
+def _run(world: int, which: str, port: int):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29533", os.path.join(ROOT, "tests", "tp_worker.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py"), which]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "TP2: logits max err" in r.stdout
+    assert f"TP{world}: logits max err" in r.stdout
+    return r.stdout
+
+
+def test_tensor_parallel_two_ranks_match_oracle():
+    _run(2, "toy", 29533)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_qwen3_4b_layer_shapes_match_oracle(world):
+    _run(world, "qwen3-4b-layers", 29540 + world)

@@ -1,7 +1,13 @@
-"""Worker for the 2-GPU tensor-parallel test (started once per rank by torch.distributed.run).
+"""Worker for the tensor-parallel tests (started once per rank by torch.distributed.run).
+
+    tp_worker.py [toy|qwen3-4b-layers]
 
 Every rank builds the tensor-parallel engine on its slice of the weights, runs prefill + greedy decode
-on the same batch, and rank 0 compares logits / tokens with the CPU oracle of the full model."""
+on the same batch, and rank 0 compares logits / tokens with the CPU oracle of the full model.
+`toy`: hidden 512, 8/4 heads, 3 layers.  `qwen3-4b-layers`: the layer shapes of the 4B configuration
+(hidden 2560, 32 query / 8 KV heads x 128, MLP 9728), 2 layers, a 4096-entry vocabulary.  A second
+engine whose weights every rank draws on the device (`RandomInit`) must give the same tokens on every
+rank count, which the caller checks by comparing the printed token hash across runs."""
 import os
 import sys
 
@@ -31,13 +37,18 @@ def main():
         return box[0]
 
     parallel.init_tensor_parallel(rank, world, bcast)
-    dims = dict(vocab=1024, hidden=512, inter=1024, layers=3, heads=8, kv_heads=4, head_dim=128)
-    full = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(std=0.03, **dims).items()}
-    mine = parallel.shard_qwen3_weights(full, heads=8, kv_heads=4, head_dim=128, rank=rank, world=world)
-    cfg = Qwen3Config(vocabSize=1024, hiddenSize=512, intermediateSize=1024, numHiddenLayers=3, numAttentionHeads=8,
-                      numKeyValueHeads=4, headDim=128, dtype="bfloat16")
-    eng = Qwen3Engine(cfg, mine, 2, 224, tp_size=world)
-    ids = synth.token_ids("tp.ids", (2, 150), 1024)
+    which = sys.argv[1] if len(sys.argv) > 1 else "toy"
+    if which == "toy":
+        dims, std, prompt = dict(vocab=1024, hidden=512, inter=1024, layers=3, heads=8, kv_heads=4, head_dim=128), 0.03, 150
+    else:
+        dims, std, prompt = dict(vocab=4096, hidden=2560, inter=9728, layers=2, heads=32, kv_heads=8, head_dim=128), 0.02, 200
+    V = dims["vocab"]
+    full = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(std=std, **dims).items()}
+    mine = parallel.shard_qwen3_weights(full, heads=dims["heads"], kv_heads=dims["kv_heads"], head_dim=128, rank=rank, world=world)
+    cfg = Qwen3Config(vocabSize=V, hiddenSize=dims["hidden"], intermediateSize=dims["inter"], numHiddenLayers=dims["layers"],
+                      numAttentionHeads=dims["heads"], numKeyValueHeads=dims["kv_heads"], headDim=128, dtype="bfloat16")
+    eng = Qwen3Engine(cfg, mine, 2, prompt + 74, tp_size=world)
+    ids = synth.token_ids("tp.ids", (2, prompt), V)
     tok, logits = eng.prefill(ids, all_logits=True)
     got = logits.dataAsync()
     toks = eng.generate(ids, 6, use_graph=True)
@@ -52,17 +63,27 @@ def main():
     msg = ""
     if rank == 0:
         from oracle import oracle as orc
-        ocfg = orc.Qwen3Config(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
-                               num_attention_heads=8, num_key_value_heads=4, head_dim=128)
+        ocfg = orc.Qwen3Config(vocab_size=V, hidden_size=dims["hidden"], intermediate_size=dims["inter"],
+                               num_hidden_layers=dims["layers"], num_attention_heads=dims["heads"],
+                               num_key_value_heads=dims["kv_heads"], head_dim=128)
         om = orc.Qwen3Oracle(ocfg, full)
         ref = om.logits(ids)
         err = np.abs(got - ref)
         ref_t = om.greedy_generate(ids, 6).astype(np.int64)
-        ok = (np.quantile(err, 0.999) <= 2e-2 and err.max() <= 3e-2 and same_across_ranks and np.array_equal(toks, toks_eager)
+        tol = max(1.0, float(np.abs(ref).max()) / 3.0)      # the bf16 bound is relative to the logits' range (|3| at the 0.6B widths)
+        ok = (np.quantile(err, 0.999) <= 2e-2 * tol and err.max() <= 3e-2 * tol and same_across_ranks and np.array_equal(toks, toks_eager)
               and (toks == ref_t).mean() >= 0.8)
         msg = (f"TP{world}: logits max err {err.max():.3e} p99.9 {np.quantile(err, 0.999):.3e}; tokens equal across ranks "
                f"{same_across_ranks}; graph==eager {np.array_equal(toks, toks_eager)}; token agreement with oracle {(toks == ref_t).mean():.2f}")
         print(msg, flush=True)
+    eng.dispose()
+    # weights drawn on the device: every rank draws its own slice of the same full model
+    import hashlib
+    from kandle_b200.engine import RandomInit
+    eng = Qwen3Engine(cfg, RandomInit(seed=99, std=std), 2, prompt + 74, tp_size=world, tp_rank=rank)
+    t_rand = eng.generate(ids, 4, use_graph=False)
+    if rank == 0:
+        print(f"TP{world} {which}: device-drawn model, first tokens {t_rand[:, 0].tolist()} sha {hashlib.sha256(t_rand[:, :1].tobytes()).hexdigest()[:12]}", flush=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.broadcast(flag, src=0)
     eng.dispose()
