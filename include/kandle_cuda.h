@@ -393,25 +393,27 @@ int kd_decode_layer_chain(const kd_tensor* attn, const kd_tensor* w_o, const kd_
                           const kd_tensor* resid_mid, const kd_tensor* resid_out, const kd_tensor* x_out,
                           const kd_tensor* act, const kd_tensor* qkv_partials);
 int kd_decode_layer_chain_splits(int64_t N, int64_t K, int* splits_out);
-/* The same stretch of a decode step in FOUR dependent phases, and further: up to and including the
- * next layer's q_norm / k_norm, rotary embedding and KV-cache write
+/* The same stretch of a decode step in FOUR dependent phases and without split-K, and further: up
+ * to and including the next layer's q_norm / k_norm, rotary embedding and KV-cache write
  * (packages/model-utils/src/attention/gqa.ts:274-322, rope.ts:546-644, kv-cache.ts:164-212), so that
  * a decode step is two launches per layer (this one and kd_attention_decode).
- *   h1 = resid_in + attn W_o^T                 split-K; the CTA that finishes a 128-row tile last sums
- *                                              the splits in split order and adds the residual
- *   act = silu(rs1 (x1 Wg^T)) * (rs1 (x1 Wu^T))  x1 = bf16(h1 * post_norm_w), rs1 = 1/sqrt(mean(h1^2)+eps):
+ *   h1 = resid_in + attn W_o^T
+ *   act = silu(rs1 (x1 Wg^T)) * (rs1 (x1 Wu^T))   x1 = bf16(h1 * post_norm_w), rs1 = 1/sqrt(mean(h1^2)+eps):
  *                                              RMSNorm's per-sequence scale is applied to the fp32
  *                                              accumulator instead of to the activations
- *   resid_out = h1 + act W_down^T              split-K as above; x2 = bf16(resid_out * next_norm_w)
- *   qkv = rs2 (x2 W_qkv_next^T)                split-K; the CTA that completes a head's 128 rows does that
- *                                              head's RMSNorm (q_norm_w / k_norm_w), the rotation by
- *                                              cos/sin [1,64] and stores q into q_out [Mb,1,Hq,128] or
- *                                              k / v into row *pos of the next layer's caches
+ *   resid_out = h1 + act W_down^T               x2 = bf16(resid_out * next_norm_w)
+ *   qkv = rs2 (x2 W_qkv_next^T)                 one head per unit of work, whose epilogue does that head's
+ *                                              RMSNorm (q_norm_w / k_norm_w), the rotation by cos/sin
+ *                                              [1,64] and stores q into q_out [Mb,1,Hq,128] or k / v into
+ *                                              row *pos of the next layer's caches
+ * The sequences are the rows of every accumulator and a unit of work is a narrow slice of weight
+ * rows over the whole of K, so no partial sums exist and an epilogue thread owns one sequence.
  * With w_qkv_next == NULL (after the last layer) the launch ends with
  * x_final = bf16(resid_out * rs2 * next_norm_w), the lm_head's input, and the arguments from
- * q_norm_w to q_out are ignored.  head_dim 128 only; 1 <= Mb <= 128; resid_out may be resid_in.
- * A cache row outside [0, maxS) is not written and reports KD_ERR_DEVICE code 102, a wait that runs
- * out codes 521-528.  Results are bit-identical from launch to launch. */
+ * q_norm_w to q_out are ignored.  head_dim 128 only; 1 <= Mb <= 128; hidden size a multiple of 16;
+ * resid_out may be resid_in.  A cache row outside [0, maxS) is not written and reports KD_ERR_DEVICE
+ * code 102, a wait that runs out codes 521-528.  Results are bit-identical from launch to launch
+ * and do not depend on how many sequences share the launch. */
 int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
                           const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
                           const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
@@ -435,6 +437,40 @@ int kd_comm_info(int* nranks, int* rank);
 int kd_allreduce_sum(const kd_tensor* t);
 int kd_comm_check(void);
 int kd_comm_destroy(void);
+
+/* One-shot all-reduce over NVLink peer memory for the small messages of a tensor-parallel decode
+ * step, fused with the residual add and RMSNorm that follow (no counterpart in the reference; the
+ * steps it replaces per rank are o_proj / down_proj partial sums -> residual add -> RMSNorm,
+ * packages/model-utils/src/qwen3/decoder_layer.ts:218-238).  Every rank owns one buffer (two 2 MiB
+ * data slots + flags) that its peers map through CUDA IPC; the kernel uses ordinary loads and
+ * stores on those addresses (no TMA, no multicast), publishes one flag per row into every peer's
+ * buffer and polls only local flags, each wait bounded (about five seconds, then KD_ERR_DEVICE code
+ * 601 at the next synchronisation and an undefined result for that call).
+ *   kd_p2p_prepare     allocates the buffer and returns its 64-byte IPC handle; the host program
+ *                      gathers the handles of all ranks (rank order)
+ *   kd_p2p_connect     maps the peers' buffers (at most 8 ranks, all on one node)
+ *   kd_p2p_emulate     instead of the two calls above: `nranks` ranks emulated on this one GPU, all in
+ *                      one cooperative launch (tests on a single GPU); tensors then carry a leading
+ *                      [nranks] dimension for x, sum_out and norm_out
+ *   kd_allreduce_add_rmsnorm
+ *                      x fp32 [splits,rows,n] split-K partial sums of this rank;
+ *                      sum_out = sum over ranks (rank order, so identical bits on every rank) of
+ *                      sum over splits of x, + residual (fp32 [rows,n], may be NULL);
+ *                      norm_out = bf16 RMSNorm(sum_out) * weight.  rows <= 128, rows*n*4 <= 2 MiB.
+ *                      Every rank must make the same sequence of calls; capture into a graph is
+ *                      possible (the call counter lives in device memory).
+ *   kd_p2p_selftest_dropped_flag
+ *                      emulated ranks only: rank `drop_rank` never publishes its flags, the others'
+ *                      waits run out after `wait_cycles` clock cycles; used to test the error path. */
+int kd_p2p_prepare(char* handle_out, size_t handle_bytes);
+int kd_p2p_connect(int nranks, int rank, const char* handles, size_t handle_bytes);
+int kd_p2p_emulate(int nranks);
+int kd_p2p_info(int* ready, int* nranks, int* rank);
+int kd_p2p_disconnect(void);
+int kd_allreduce_add_rmsnorm(const kd_tensor* x, const kd_tensor* residual, const kd_tensor* weight, float eps,
+                             const kd_tensor* sum_out, const kd_tensor* norm_out);
+int kd_p2p_selftest_dropped_flag(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* norm_out, int drop_rank,
+                                 uint32_t wait_cycles);
 
 #ifdef __cplusplus
 }

@@ -173,7 +173,7 @@ static void release_retired_workspaces() {
 
 }  // namespace kd
 
-namespace kd { int decode_chain_reset_counters(); int decode_layer_reset_counters(); }
+namespace kd { int decode_chain_reset_counters(); int decode_layer_reset_counters(); int p2p_shutdown(); }
 
 using namespace kd;
 
@@ -223,6 +223,7 @@ KD_API int kd_shutdown(void) {
   Context& c = ctx();
   if (!c.ready) return KD_OK;
   cudaStreamSynchronize(c.stream);
+  p2p_shutdown();
   {
     std::lock_guard<std::mutex> lk(g_alloc.mu);
     for (auto& kv : g_alloc.live) {

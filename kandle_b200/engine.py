@@ -29,7 +29,7 @@ import math
 
 import numpy as np
 
-from . import core, lib
+from . import core, lib, parallel
 from .core import Tensor
 from .model_utils.qwen3 import Qwen3Config
 
@@ -115,6 +115,9 @@ class Qwen3Engine:
         # ... and further, through the next layer's q/k-norm + RoPE + cache write, in four phases
         # (kd_decode_layer_fused): two launches per layer and decode step
         self.use_fused_layer = self.tp == 1 and self.D == 128 and self.H <= 8192
+        # tensor parallel decode: sum the partial outputs over ranks through mapped peer memory when
+        # the host program has connected the peer buffers (parallel.init_peer_buffers), else NCCL
+        self.use_p2p = True
         self.sampler = None   # None: greedy argmax; else dict(temperature, top_k, top_p, rng), see set_sampler
 
     def _random_weights(self, init: RandomInit, rank: int) -> None:
@@ -186,6 +189,19 @@ class Qwen3Engine:
 
     def _allreduce(self, t) -> None:
         lib.call("kd_allreduce_sum", _r(t))
+
+    def _reduce_add_norm(self, d: dict, partials, norm_w, resid, sum_out) -> None:
+        """sum_out = resid + (sum over ranks and splits of `partials`); d["x"] = RMSNorm(sum_out).
+        Tensor parallel with mapped peer buffers: one kernel does the sum over ranks through peer
+        memory (kd_allreduce_add_rmsnorm); otherwise the library all-reduce followed by the fused
+        add + norm kernel."""
+        if self.tp > 1 and d["p2p"]:
+            lib.call("kd_allreduce_add_rmsnorm", _r(partials), _r(resid), _r(norm_w), ctypes.c_float(self.cfg.rmsNormEps),
+                     _r(sum_out), _r(d["x"]))
+            return
+        if self.tp > 1:
+            self._allreduce(partials)
+        self._norm(partials, norm_w, d["x"], resid=resid, sum_out=sum_out)
 
     def kv_bytes_per_token(self) -> int:
         return 2 * self.L * self.Hkv * self.D * 2
@@ -309,6 +325,7 @@ class Qwen3Engine:
             return s.value
         d = {
             "B": B, "graph": None, "chain": self.use_chain, "fused": self.use_fused_layer,
+            "p2p": self.tp > 1 and self.use_p2p and parallel.peer_buffers_ready(),
             "scalars": core.zeros((2,), "int32"),           # [write position, context length]
             "ids": core.zeros((B,), "int64"), "emb": e(B, self.H), "h": f(B, self.H), "h1": f(B, self.H), "x": e(B, self.H),
             # a projection whose suggested split factor is 1 writes bf16 directly, otherwise fp32 partials
@@ -381,14 +398,10 @@ class Qwen3Engine:
                 vc.dispose()
                 continue
             lib.call("kd_linear_bf16_skinny", _r(attn2d), _r(lw["wo"]), 0, _r(d["o_p"]))
-            if self.tp > 1:
-                self._allreduce(d["o_p"])
-            self._norm(d["o_p"], lw["post_norm"], d["x"], resid=h, sum_out=h1)
+            self._reduce_add_norm(d, d["o_p"], lw["post_norm"], h, h1)
             lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wgu"]), 2, _r(d["act"]))   # SiLU*up in the epilogue
             lib.call("kd_linear_bf16_skinny", _r(d["act"]), _r(lw["wdown"]), 0, _r(d["down_p"]))
-            if self.tp > 1:
-                self._allreduce(d["down_p"])
-            self._norm(d["down_p"], nxt, d["x"], resid=h1, sum_out=h)
+            self._reduce_add_norm(d, d["down_p"], nxt, h1, h)
             kc.dispose()
             vc.dispose()
         lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(self.embed), 0, _r(d["logits"]))

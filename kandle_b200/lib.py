@@ -162,6 +162,13 @@ _SIGNATURES = {
     "kd_allreduce_sum": [_T],
     "kd_comm_check": [],
     "kd_comm_destroy": [],
+    "kd_p2p_prepare": [ctypes.c_char_p, ctypes.c_size_t],
+    "kd_p2p_connect": [ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t],
+    "kd_p2p_emulate": [ctypes.c_int],
+    "kd_p2p_info": [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+    "kd_p2p_disconnect": [],
+    "kd_allreduce_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
+    "kd_p2p_selftest_dropped_flag": [_T, _T, _T, ctypes.c_int, ctypes.c_uint32],
     "kd_attention_decode": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_noalloc": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_paged": [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],

@@ -83,3 +83,21 @@ def init_tensor_parallel(rank: int, world: int, broadcast) -> None:
 def allreduce(t) -> None:
     """In-place sum over ranks of a contiguous bf16/fp32 device tensor, on the library's stream."""
     lib.call("kd_allreduce_sum", ctypes.byref(t._handle.c()))
+
+
+def init_peer_buffers(rank: int, world: int, allgather) -> None:
+    """Maps every rank's peer buffer for the one-shot all-reduce (kd_allreduce_add_rmsnorm).
+    `allgather(bytes) -> list[bytes]` must return every rank's object in rank order (e.g. a
+    torch.distributed.all_gather_object wrapper).  All ranks must be on one node with peer access."""
+    buf = ctypes.create_string_buffer(64)
+    lib.call("kd_p2p_prepare", buf, 64)
+    handles = allgather(buf.raw)
+    if len(handles) != world:
+        raise ValueError(f"expected {world} handles, got {len(handles)}")
+    lib.call("kd_p2p_connect", world, rank, b"".join(handles), 64)
+
+
+def peer_buffers_ready() -> bool:
+    r = ctypes.c_int(0)
+    lib.call("kd_p2p_info", ctypes.byref(r), None, None)
+    return bool(r.value)

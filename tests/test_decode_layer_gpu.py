@@ -1,6 +1,6 @@
 """GPU parity of kd_decode_layer_fused (o_proj + residual, gate/up SiLU*up, down + residual, the
 next layer's QKV with q/k RMSNorm, rotary embedding and the KV-cache write: one persistent kernel,
-four dependent phases) against the oracle's unfused operator sequence, i.e. what
+four dependent phases, no split-K) against the oracle's unfused operator sequence, i.e. what
 packages/model-utils/src/qwen3/decoder_layer.ts:191-241 and attention/gqa.ts:246-322 compute for one
 new token per sequence."""
 import ctypes
@@ -106,7 +106,9 @@ def test_fused_layer_matches_the_unfused_oracle(backend, oracle, mb, H, Ko, I, h
     lib.call("kd_debug_fill_scratch", 0xFF)        # NaN patterns: a slot that is read before it is written shows
     t = _run(c, eps)
     backend.synchronize()
-    _close(t["h2"].dataAsync(), h2, 2e-3, "h2")
+    # h2 sums up to 9728 products of bf16 activations that were rounded at another point than the
+    # oracle's (bf16(h1 * w) scaled afterwards, against bf16(h1 * rs * w)): near-ties fall differently
+    _close(t["h2"].dataAsync(), h2, 4e-3, "h2")
     if not hq:
         _close(t["xf"].dataAsync(), x2, 4e-3, "x_final")
         return
