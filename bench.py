@@ -584,6 +584,12 @@ def extra_tp_4b(bn: Bench) -> dict:
             bn.dist.broadcast_object_list(box, src=0)
             return box[0]
         parallel.init_tensor_parallel(rank, world, bcast)
+
+        def allgather(obj):
+            out = [None] * world
+            bn.dist.all_gather_object(out, obj)
+            return out
+        parallel.init_peer_buffers(rank, world, allgather)     # one-shot all-reduce of the decode step
         bn.tp_ready = True
     B, S, T = 8, 4096, 128
     eng = bn.make_engine(dims, L, dims["vocab"], B, S + T + 16, tp_size=world)
@@ -617,7 +623,30 @@ def extra_tp_4b(bn: Bench) -> dict:
         ms_ar_o = bn.timed_ms(lambda: eng._allreduce(d["o_p"]), reps=50, warm=5)
         ms_ar_d = bn.timed_ms(lambda: eng._allreduce(d["down_p"]), reps=50, warm=5)
         bn.sync_all()
-        ms_ar_prefill, ms_ar_o, ms_ar_d = bn.max_over_ranks([ms_ar_prefill, ms_ar_o, ms_ar_d])
+        # the fused one-shot kernel (sum over ranks through peer memory + residual add + RMSNorm) against
+        # what it replaces (library all-reduce, then the add + RMSNorm kernel)
+        lw0 = eng.layers[0]
+        ms_fused = bn.timed_ms(lambda: eng._reduce_add_norm(d, d["o_p"], lw0["post_norm"], d["h"], d["h1"]), reps=50, warm=5)
+        def unfused():
+            eng._allreduce(d["o_p"])
+            eng._norm(d["o_p"], lw0["post_norm"], d["x"], resid=d["h"], sum_out=d["h1"])
+        ms_unfused = bn.timed_ms(unfused, reps=50, warm=5)
+        # the decode phase again with the library all-reduce (new graph)
+        eng.dispose()
+        eng.use_p2p = False
+        q0, q1 = CudaEvent(), CudaEvent()
+        tok = eng.prefill(ids)
+        eng.start_decode(tok, use_graph=True)
+        q0.record()
+        for _ in range(1, T):
+            eng.decode_step()
+        q1.record()
+        bn.be.synchronize()
+        ms_decode_nccl = q0.elapsed_ms(q1)
+        eng.use_p2p = True
+        bn.sync_all()
+        ms_ar_prefill, ms_ar_o, ms_ar_d, ms_fused, ms_unfused, ms_decode_nccl = bn.max_over_ranks(
+            [ms_ar_prefill, ms_ar_o, ms_ar_d, ms_fused, ms_unfused, ms_decode_nccl])
         nbytes = part.numel * 2
         rec["allreduce"] = {
             "library": "NCCL (ncclAllReduce on the library's stream)",
@@ -627,6 +656,9 @@ def extra_tp_4b(bn: Bench) -> dict:
             "decode_message_bytes": [int(d["o_p"].numel * 4), int(d["down_p"].numel * 4)],
             "decode_us_per_call": [ms_ar_o * 1e3, ms_ar_d * 1e3],
             "decode_ms_per_step": (ms_ar_o + ms_ar_d) * L,
+            "one_shot_peer_memory": {"kernel": "allreduce_add_rmsnorm_kernel (sum over ranks by peer loads + residual add + RMSNorm)",
+                                     "us_per_call": ms_fused * 1e3, "replaces_us_per_call": ms_unfused * 1e3,
+                                     "in_use": bool(d["p2p"]), "decode_ms_per_step_with_library_allreduce": ms_decode_nccl / (T - 1)},
         }
     ms, ms_prefill, ms_decode = bn.max_over_ranks([ms, ms_prefill, ms_decode])
     per_layer_params = dims["hidden"] * ((dims["heads"] + 2 * dims["kv_heads"]) * dims["head_dim"]) + \
@@ -736,6 +768,7 @@ def run_ours(a) -> None:
     if bn.rank == 0:
         print(json.dumps(line), flush=True)
     if bn.tp_ready:
+        lib.call("kd_p2p_disconnect")
         lib.call("kd_comm_destroy")
     if bn.dist is not None:
         bn.dist.barrier()

@@ -414,6 +414,11 @@ int kd_decode_layer_chain_splits(int64_t N, int64_t K, int* splits_out);
  * resid_out may be resid_in.  A cache row outside [0, maxS) is not written and reports KD_ERR_DEVICE
  * code 102, a wait that runs out codes 521-528.  Results are bit-identical from launch to launch
  * and do not depend on how many sequences share the launch. */
+/* Test / profiling support, no counterpart in the reference: device-side timestamps of the last
+ * kd_decode_layer_fused launch, [SMs][16] nanoseconds (0: start; per phase g: 1+3g dependency seen,
+ * 2+3g accumulator ready, 3+3g outputs published); only in a process started with
+ * KD_DECODE_LAYER_TRACE=1. */
+int kd_debug_decode_layer_trace(uint64_t* out, int max_entries);
 int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
                           const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
                           const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,

@@ -234,7 +234,9 @@ class Tensor:
         shape, strides, offset = [], [], self.offset
         for it, n, st in zip(items, self.shape, self.strides):
             if isinstance(it, int):
-                idx = it % n
+                idx = it + n if it < 0 else it
+                if idx < 0 or idx >= n:     # the reference throws (dispatch/handlers/shape.ts:511-518), it never wraps
+                    raise IndexError(f"select: index {it} out of range for dim {len(shape)} with size {n}")
                 offset += idx * st
             else:
                 a, b, step = it.indices(n)
@@ -246,8 +248,16 @@ class Tensor:
         return self._view(shape, strides, offset)
 
     def select(self, dim: int, index: int) -> "Tensor":
+        """packages/core/src/dispatch/handlers/shape.ts:500-540, with its two range errors."""
+        nd = dim + self.ndim if dim < 0 else dim
+        if nd < 0 or nd >= self.ndim:
+            raise IndexError(f"select: dim {dim} out of range for tensor with {self.ndim} dimensions")
+        n = self.shape[nd]
+        idx = index + n if index < 0 else index
+        if idx < 0 or idx >= n:
+            raise IndexError(f"select: index {index} out of range for dim {dim} with size {n}")
         items = [slice(None)] * self.ndim
-        items[dim % self.ndim] = int(index)
+        items[nd] = int(idx)
         return self.slice(items)
 
     def contiguous(self) -> "Tensor":
@@ -269,7 +279,12 @@ def _binary(key: str, a: Tensor, b, scalars=None) -> Tensor:
     if not isinstance(b, Tensor):
         if key == "mul":
             return _unary("mul_scalar", a, {"scalar": float(b)})
-        b = Tensor(np.asarray(b, dtype=np.float32).reshape(()), dtype="float32")
+        # a Python scalar takes the tensor's dtype when it can (an int next to an integer tensor stays
+        # integer); a float next to an integer tensor promotes to float32
+        if a.dtype not in _FLOAT_RANK and float(b) == int(b) and not isinstance(b, float):
+            b = Tensor(np.asarray(b).reshape(()), dtype=a.dtype)
+        else:
+            b = Tensor(np.asarray(b, dtype=np.float32).reshape(()), dtype="float32")
     shape = _broadcast_shape(a.shape, b.shape)
     out = _new(shape, _promote(a.dtype, b.dtype))
     _kernel(key)(TensorIterator([a._handle, b._handle], [out], scalars or {}))
@@ -277,7 +292,9 @@ def _binary(key: str, a: Tensor, b, scalars=None) -> Tensor:
 
 
 def _unary(key: str, a: Tensor, scalars=None) -> Tensor:
-    out = _new(a.shape, a.dtype if a.dtype in _FLOAT_RANK else "float32")
+    # neg / abs keep an integer dtype; the transcendental keys promote integers to float32
+    keep = a.dtype in _FLOAT_RANK or key in ("neg", "abs")
+    out = _new(a.shape, a.dtype if keep else "float32")
     _kernel(key)(TensorIterator([a._handle], [out], scalars or {}))
     return Tensor(_handle=out)
 

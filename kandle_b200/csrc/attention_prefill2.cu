@@ -340,10 +340,10 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
 template <int D>
 static int launch_fa2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const Fa2Params& p, dim3 grid) {
   constexpr int SMEM = 2 * FA2_BQ * D * 2 + FA2_NSLOT * FA2_BKV * D * 2 + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};   // per device: kd_shutdown + kd_init may move the library to another GPU
+  if (!configured[ctx().device & 63]) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(flash_attention_prefill2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    configured = true;
+    configured[ctx().device & 63] = true;
   }
   flash_attention_prefill2_kernel<D><<<grid, FA2_THREADS, SMEM, ctx().stream>>>(tq, tk, tv, p);
   return after_launch("flash_attention_prefill2_kernel");

@@ -666,11 +666,11 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 template <int D, bool DECODE>
 static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid) {
   constexpr int SMEM = (DECODE ? 16 : FA_BQ) * D * 2 + (DECODE ? 6 * FA_DEC_BKV : 2 * FA_STAGES * FA_BKV) * D * 2 + 1024 + 256 + 2048;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};   // per device: kd_shutdown + kd_init may move the library to another GPU
+  if (!configured[ctx().device & 63]) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(flash_attention_tcgen05_kernel<D, DECODE>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    configured = true;
+    configured[ctx().device & 63] = true;
   }
   if (DECODE) KD_CUDA_CHECK(launch_ex(flash_attention_tcgen05_kernel<D, DECODE>, grid, dim3(FA_THREADS), (size_t)SMEM, tq, tk, tv, p));
   else flash_attention_tcgen05_kernel<D, DECODE><<<grid, FA_THREADS_PREFILL, SMEM, ctx().stream>>>(tq, tk, tv, p);

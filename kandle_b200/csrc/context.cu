@@ -193,7 +193,9 @@ KD_API int kd_init(int device_ordinal, unsigned flags) {
   Context& c = ctx();
   if (c.ready) {
     if (c.device == device_ordinal) return KD_OK;
-    return fail(KD_ERR_INVALID, "already initialised on device %d", c.device);
+    // launch state (tensor maps, counters, scratch) is kept per process for ONE device: a second
+    // device needs kd_shutdown first, or a process of its own (one process drives one GPU)
+    return fail(KD_ERR_UNSUPPORTED, "already initialised on device %d: one process drives one GPU (kd_shutdown first)", c.device);
   }
   int n = 0;
   cudaError_t e = cudaGetDeviceCount(&n);

@@ -462,10 +462,10 @@ int decode_chain_launch(int Mb, int H, float eps, const ChainOperand* ops, int n
   p.n[0] = ChainNorm{part0, p.g[0].splits, 0, resid_in, resid_mid, w_post, x_out};
   p.n[1] = ChainNorm{part2, p.g[2].splits, 0, resid_mid, resid_out, w_next, x_out};
   const int smem = p.stages * stage_bytes + 1024 + 256 + 4096;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};   // per device: kd_shutdown + kd_init may move the library to another GPU
+  if (!configured[ctx().device & 63]) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(decode_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
-    configured = true;
+    configured[ctx().device & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(G);

@@ -37,6 +37,8 @@
 // epilogues and counters.  One CTA per SM, cooperative launch, every wait bounded (codes 521-528).
 // Results are bit-identical from launch to launch and do not depend on the number of sequences.
 // Roofline: HBM, the bytes of the four weight matrices; in practice latency.
+#include <algorithm>
+
 #include "chain_common.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
@@ -50,9 +52,15 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
                       uint32_t box_rows, uint32_t box_cols);
 int decode_layer_reset_counters();
 
-constexpr int DL_BK = 64;                       // K elements per stage (one 128-byte swizzle atom)
-constexpr int DL_W_BYTES = 128 * DL_BK * 2;     // weight area of a stage: up to 128 weight rows
-constexpr int DL_THREADS = 192;
+constexpr int DL_BK = 64;                       // K elements per k-block (one 128-byte swizzle atom)
+constexpr int DL_THREADS = 224;                 // warp 0 producer, warps 1 and 6 MMA issuers, warps 2-5 epilogues
+// A slot of the shared-memory ring holds a GROUP of consecutive k-blocks: the activation tiles of
+// the group (one bulk tensor copy, a 3-D box [k-blocks, rows, 64]) and the weight tiles of the group
+// (another).  What a unit that walks 16-48 k-blocks pays for is neither bandwidth nor the tensor
+// pipe but the instructions its two single-thread roles execute per k-block (wait, arm, issue,
+// commit); with groups the producer and the barriers work per group, and the MMA thread's inner
+// loop is four tcgen05.mma with descriptors advanced by additions.
+constexpr int DL_X_AREA = 16 * 1024, DL_W_AREA = 32 * 1024, DL_SLOT = DL_X_AREA + DL_W_AREA, DL_STAGES = 4;
 constexpr int DL_MAX_UNITS = 512;               // units of a phase that publish sums of squares
 constexpr int DL_COUNTERS = 8;
 
@@ -61,10 +69,12 @@ struct DlGemm {
   int n_unit;                 // weight rows per unit (multiple of 16, at most 128)
   int units;
   int rot;                    // unit u runs on CTA (u + rot) % gridDim.x
+  int kg;                     // k-blocks per slot (per activation copy and per weight copy)
+  int grouped;                // 1: tensor maps are [k-block, row, 64] (K a multiple of 64); 0: [1, row, K], one k-block per copy
 };
 
 struct DlParams {
-  int Mb, x_box, stages, H;
+  int Mb, x_box, H;
   int has_qkv;                // 1: phase 3 is the next layer's QKV; 0: phase 3 writes x_final
   float eps;
   DlGemm g[4];
@@ -92,12 +102,32 @@ struct DlParams {
   __nv_bfloat16* x_final;     // [Mb][H] (last layer)
   unsigned* counters;         // [8]: phases 0..2, [7] exit ticket
   int* err;
+  unsigned long long* trace;  // optional [gridDim][16] nanosecond timestamps (kd_debug_decode_layer_trace)
 };
 
 struct DlMaps {
   CUtensorMap w[4];
   CUtensorMap x[4];
 };
+
+__device__ __forceinline__ unsigned long long dl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define DL_TRACE(slot) do { if (p.trace) p.trace[(size_t)blockIdx.x * 16 + (slot)] = dl_now(); } while (0)
+
+// tcgen05.mma with both shared-memory descriptors given as (low word, shared high word).
+__device__ __forceinline__ void umma_ss_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 __device__ __forceinline__ void ld_f32x16(const float* p, float (&v)[16]) {
 #pragma unroll
@@ -126,6 +156,30 @@ __device__ __forceinline__ void st_bf16x16(__nv_bfloat16* p, const float (&v)[16
   }
 }
 
+// 16 / 32 accumulator columns of this thread's row: the sum of the two issuers' halves (128 columns
+// apart); a unit with a single k-block only has the first half.
+__device__ __forceinline__ void dl_acc16(uint32_t t_acc, bool two, float (&v)[16]) {
+  uint32_t a[16], b[16];
+  tmem_ld_32x16(t_acc, a);
+  if (two) tmem_ld_32x16(t_acc + 128u, b);
+  tmem_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(a[i]) + (two ? __uint_as_float(b[i]) : 0.f);
+}
+__device__ __forceinline__ void dl_acc32(uint32_t t_acc, bool two, float (&v)[32]) {
+  uint32_t a[32];
+  tmem_ld_32x32(t_acc, a);
+  tmem_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(a[i]);
+  if (two) {
+    tmem_ld_32x32(t_acc + 128u, a);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(a[i]);
+  }
+}
+
 // 1/rms of a sequence from the per-unit sums of squares its producer phase published.
 __device__ __forceinline__ float dl_rs(const float* ssq, int units, int Mb, int m, int H, float eps) {
   float tot = 0.f;
@@ -143,14 +197,13 @@ __device__ __forceinline__ float dl_rs(const float* ssq, int units, int Mb, int 
 
 __global__ void __launch_bounds__(DL_THREADS, 1)
 decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__ DlParams p) {
-  const int x_bytes = p.x_box * DL_BK * 2;
-  const int stage_bytes = x_bytes + DL_W_BYTES;      // [activation tile][weight tile]
+  const int x1 = p.x_box * DL_BK * 2;                 // bytes of one activation k-block tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
-  uint64_t* empty = full + p.stages;
-  uint64_t* acc_full = empty + p.stages;     // 2
-  uint64_t* acc_empty = acc_full + 2;        // 2
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + DL_STAGES * DL_SLOT);   // slot s: [activations DL_X_AREA][weights DL_W_AREA]
+  uint64_t* empty = full + DL_STAGES;
+  uint64_t* acc_full = empty + DL_STAGES;       // 2
+  uint64_t* acc_empty = acc_full + 2;           // 2
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -159,8 +212,9 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
   const int n_gemms = p.has_qkv ? 4 : 3;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    // both MMA issuers release a slot and complete an accumulator
+    for (int s = 0; s < DL_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 2); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 2); mbar_init(&acc_empty[s], 4); }
     *abort_flag = 0;
     fence_mbar_init();
     for (int i = 0; i < n_gemms; ++i) {
@@ -169,13 +223,14 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     }
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);              // two accumulators of up to 128 columns
+    tmem_alloc(tmem_slot, 512);              // two accumulator buffers x two halves (one per MMA issuer) of up to 128 columns
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) DL_TRACE(0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -186,19 +241,32 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
       for (int gi = 0; ok && gi < n_gemms; ++gi) {
         const DlGemm& g = p.g[gi];
         const int n_kb = (g.K + DL_BK - 1) / DL_BK;
-        const uint32_t tx = (uint32_t)(x_bytes + g.n_unit * DL_BK * 2);
+        const int n_grp = (n_kb + g.kg - 1) / g.kg;
+        const uint32_t tx = (uint32_t)(g.kg * (x1 + g.n_unit * DL_BK * 2));
+        const CUtensorMap* wm = &maps.w[gi];
+        const CUtensorMap* xm = &maps.x[gi];
+        // group `grp` of this unit: k-blocks [grp * kg, grp * kg + kg)
+        auto load_w = [&](int st, int grp, int row0) {
+          if (g.grouped) tma_load_3d(smem + st * DL_SLOT + DL_X_AREA, wm, &full[st], 0, row0, grp * g.kg);
+          else tma_load_3d(smem + st * DL_SLOT + DL_X_AREA, wm, &full[st], grp * DL_BK, row0, 0);
+        };
+        auto load_x = [&](int st, int grp) {
+          if (g.grouped) tma_load_3d(smem + st * DL_SLOT, xm, &full[st], 0, 0, grp * g.kg);
+          else tma_load_3d(smem + st * DL_SLOT, xm, &full[st], grp * DL_BK, 0, 0);
+        };
         bool dep_ready = (gi == 0);
         for (int u = (cta - g.rot % G + G) % G; ok && u < g.units; u += G) {
+          const int row0 = u * g.n_unit;
           int i = 0;
           if (!dep_ready) {
             // weights first, as far as the ring reaches; their activations follow once they exist
-            const int pre = min(n_kb, p.stages);
+            const int pre = min(n_grp, DL_STAGES);
             const int stage0 = stage;
             for (; i < pre; ++i) {
               if (!mbar_wait(&empty[stage], ring_phase ^ 1, abort_flag, p.err, 521)) { ok = false; break; }
               mbar_arrive_expect_tx(&full[stage], tx);
-              tma_load_2d(smem + stage * stage_bytes + x_bytes, &maps.w[gi], &full[stage], i * DL_BK, u * g.n_unit);
-              if (++stage == p.stages) { stage = 0; ring_phase ^= 1; }
+              load_w(stage, i, row0);
+              if (++stage == DL_STAGES) { stage = 0; ring_phase ^= 1; }
             }
             if (!ok) break;
             if (!counter_wait(p.counters + (gi - 1), (unsigned)p.g[gi - 1].units, abort_flag, p.err, 522)) { ok = false; break; }
@@ -206,51 +274,71 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             // through the async proxy
             asm volatile("fence.proxy.async;" ::: "memory");
             dep_ready = true;
+            DL_TRACE(1 + 3 * gi);
             for (int t = 0; t < pre; ++t) {
-              const int st = (stage0 + t) % p.stages;
-              tma_load_2d(smem + st * stage_bytes, &maps.x[gi], &full[st], t * DL_BK, 0);
+              int st = stage0 + t;
+              if (st >= DL_STAGES) st -= DL_STAGES;
+              load_x(st, t);
             }
           }
-          for (; i < n_kb; ++i) {
+          for (; i < n_grp; ++i) {
             if (!mbar_wait(&empty[stage], ring_phase ^ 1, abort_flag, p.err, 523)) { ok = false; break; }
             mbar_arrive_expect_tx(&full[stage], tx);
-            tma_load_2d(smem + stage * stage_bytes + x_bytes, &maps.w[gi], &full[stage], i * DL_BK, u * g.n_unit);
-            tma_load_2d(smem + stage * stage_bytes, &maps.x[gi], &full[stage], i * DL_BK, 0);
-            if (++stage == p.stages) { stage = 0; ring_phase ^= 1; }
+            load_w(stage, i, row0);
+            load_x(stage, i);
+            if (++stage == DL_STAGES) { stage = 0; ring_phase ^= 1; }
           }
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 6) {
+    // ------------------------------------------------------------------ MMA issuers
+    // One thread issues a tcgen05.mma of this size every ~55-95 cycles however narrow it is, while
+    // the tensor pipe takes one every ~40-50: two issuing warps share a unit's k-blocks (even ones to
+    // warp 1, odd ones to warp 6), each accumulating into its own half of the buffer; the epilogue
+    // adds the halves.
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
       int stage = 0;
       uint32_t ring_phase = 0;
       int acc_n = 0;
       bool ok = true;
+      // shared-memory descriptors (128-byte swizzle, K-major, 8-row groups 1024 bytes apart): the high
+      // word is constant, the low word is the address in 16-byte units plus the (unused) leading offset
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t smem_lo = ((smem_u32(smem) >> 4) & 0x3FFFu) | (1u << 16);
       for (int gi = 0; ok && gi < n_gemms; ++gi) {
         const DlGemm& g = p.g[gi];
         const int n_kb = (g.K + DL_BK - 1) / DL_BK;
+        const uint32_t x_step = (uint32_t)x1 >> 4, w_step = (uint32_t)(g.n_unit * DL_BK * 2) >> 4;
         // D[128 sequence rows, n_unit weight rows] += X[128, 16] * W[n_unit, 16]^T
         const uint32_t idesc = make_idesc_bf16(128, g.n_unit, 0, 0);
         for (int u = (cta - g.rot % G + G) % G; ok && u < g.units; u += G) {
           const int buf = acc_n & 1, use = acc_n >> 1;
           if (!mbar_wait(&acc_empty[buf], (uint32_t)((use & 1) ^ 1), abort_flag, p.err, 524)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)buf * 128u;
-          for (int i = 0; i < n_kb; ++i) {
+          const uint32_t d_tmem = tmem_base + (uint32_t)buf * 256u + (uint32_t)me * 128u;
+          uint32_t acc = 0u;
+          for (int kb = 0; kb < n_kb; kb += g.kg) {
             if (!mbar_wait(&full[stage], ring_phase, abort_flag, p.err, 525)) { ok = false; break; }
             tc_fence_after();
-            // the activation tile holds x_box rows; rows beyond them are read from the weight tile
-            // that follows it in the same stage (always inside this stage: x_bytes + 16 KB >= 16 KB)
-            const uint32_t x_addr = smem_u32(smem + stage * stage_bytes);
-            const uint32_t w_addr = x_addr + (uint32_t)x_bytes;
-#pragma unroll
-            for (int k = 0; k < DL_BK / 16; ++k)
-              umma_ss(d_tmem, make_smem_desc_sw128(x_addr + k * 32, 16, 1024), make_smem_desc_sw128(w_addr + k * 32, 16, 1024),
-                      idesc, (i | k) != 0 ? 1u : 0u);
+            // an activation tile holds x_box rows; the MMA's other rows are read from whatever follows
+            // it in the slot (later tiles, the weight area) and give accumulator rows of no sequence
+            const int nk = min(g.kg, n_kb - kb);
+            const int j0 = (kb + me) & 1 ? 1 : 0;          // this issuer's first k-block of the group: global index parity == me
+            uint32_t xl = smem_lo + (uint32_t)(stage * (DL_SLOT >> 4)) + (uint32_t)j0 * x_step;
+            uint32_t wl = smem_lo + (uint32_t)(stage * (DL_SLOT >> 4)) + (uint32_t)(DL_X_AREA >> 4) + (uint32_t)j0 * w_step;
+            for (int j = j0; j < nk; j += 2) {
+              umma_ss_lohi(d_tmem, xl, wl, DESC_HI, idesc, acc);
+              umma_ss_lohi(d_tmem, xl + 2, wl + 2, DESC_HI, idesc, 1u);
+              umma_ss_lohi(d_tmem, xl + 4, wl + 4, DESC_HI, idesc, 1u);
+              umma_ss_lohi(d_tmem, xl + 6, wl + 6, DESC_HI, idesc, 1u);
+              acc = 1u;
+              xl += 2 * x_step;
+              wl += 2 * w_step;
+            }
             umma_commit(&empty[stage]);
-            if (++stage == p.stages) { stage = 0; ring_phase ^= 1; }
+            if (++stage == DL_STAGES) { stage = 0; ring_phase ^= 1; }
           }
           if (!ok) break;
           umma_commit(&acc_full[buf]);
@@ -280,12 +368,20 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
       }
       for (int u = (cta - g.rot % G + G) % G; u < g.units; u += G) {
         const int buf = acc_n & 1, use = acc_n >> 1;
+        const int n0 = u * g.n_unit;
+        // the residual and the norm weights do not depend on the GEMM: fetch the first columns' worth
+        // while the MMAs run (the first 16 columns; the later ones are loaded in the loop below, where
+        // their latency hides behind the work on the columns before them)
+        float pre_r[16];
+        if ((gi == 0 || gi == 2) && valid && n0 < g.N)
+          ld_f32x16((gi == 0 ? p.resid_in : p.resid_mid) + (int64_t)m * p.H + n0, pre_r);
         if (ok) ok = mbar_wait(&acc_full[buf], (uint32_t)(use & 1), abort_flag, p.err, 527);
         if (epi_bar_any(!ok || *abort_flag != 0)) ok = false;   // one answer for all 128 threads
         if (!ok) continue;
         tc_fence_after();
-        const uint32_t t_acc = t_row + (uint32_t)buf * 128u;
-        const int n0 = u * g.n_unit;
+        if ((threadIdx.x & 127) == 0) DL_TRACE(2 + 3 * gi);
+        const uint32_t t_acc = t_row + (uint32_t)buf * 256u;
+        const bool two = g.K > DL_BK;           // the second issuer had at least one k-block
         if (gi == 0 || gi == 2) {
           // ---- residual add; hand on h, bf16(h * w) and this unit's share of sum(h^2)
           const float* resid = gi == 0 ? p.resid_in : p.resid_mid;
@@ -293,17 +389,16 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           __nv_bfloat16* x_out = gi == 0 ? p.x1 : p.x2;
           const __nv_bfloat16* wn = gi == 0 ? p.w_post : p.w_next;
           float ss = 0.f;
-          for (int c0 = 0; c0 < g.n_unit; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld_32x16(t_acc + c0, r);
-            tmem_wait_ld();
+          // one 16-column chunk: add the accumulator to the residual, store h and bf16(h * w)
+          auto chunk = [&](int c0, float (&a)[16]) {
+            float r[16];
+            dl_acc16(t_acc + c0, two, r);
             if (valid && n0 + c0 < g.N) {
-              float a[16], w[16];
-              ld_f32x16(resid + (int64_t)m * p.H + n0 + c0, a);
+              float w[16];
               ld_bf16x16(wn + n0 + c0, w);
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                a[i] += __uint_as_float(r[i]);
+                a[i] += r[i];
                 ss += a[i] * a[i];
               }
               float4* ho = reinterpret_cast<float4*>(h_out + (int64_t)m * p.H + n0 + c0);
@@ -313,18 +408,23 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
               for (int i = 0; i < 16; ++i) a[i] *= w[i];
               st_bf16x16(x_out + (int64_t)m * p.H + n0 + c0, a);
             }
+          };
+          chunk(0, pre_r);
+          for (int c0 = 16; c0 < g.n_unit; c0 += 16) {
+            float a[16];
+            if (valid && n0 + c0 < g.N) ld_f32x16(resid + (int64_t)m * p.H + n0 + c0, a);
+            chunk(c0, a);
           }
           if (valid) (gi == 0 ? p.ssq1 : p.ssq2)[u * p.Mb + m] = ss;
         } else if (gi == 1) {
           // ---- gate/up: columns come in groups of 16 gate rows followed by the 16 matching up rows
           for (int c0 = 0; c0 < g.n_unit; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32(t_acc + c0, r);
-            tmem_wait_ld();
+            float r[32];
+            dl_acc32(t_acc + c0, two, r);
             if (valid && n0 + c0 < g.N) {
               float o[16];
 #pragma unroll
-              for (int i = 0; i < 16; ++i) o[i] = chain_silu(__uint_as_float(r[i]) * rs) * (__uint_as_float(r[16 + i]) * rs);
+              for (int i = 0; i < 16; ++i) o[i] = chain_silu(r[i] * rs) * (r[16 + i] * rs);
               st_bf16x16(p.act + (int64_t)m * (g.N / 2) + (n0 + c0) / 2, o);
             }
           }
@@ -336,12 +436,11 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           if (is_q || is_k) {
             float ss = 0.f;
             for (int c0 = 0; c0 < 128; c0 += 32) {
-              uint32_t r[32];
-              tmem_ld_32x32(t_acc + c0, r);
-              tmem_wait_ld();
+              float r[32];
+              dl_acc32(t_acc + c0, two, r);
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const float v = __uint_as_float(r[i]) * rs;
+                const float v = r[i] * rs;
                 ss += v * v;
               }
             }
@@ -361,16 +460,14 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           const __nv_bfloat16* hw = is_q ? p.qw : p.kw;
           for (int c0 = 0; c0 < 64; c0 += 16) {
             // elements d = c0..c0+15 and their rotation partners d + 64
-            uint32_t r1[16], r2[16];
-            tmem_ld_32x16(t_acc + c0, r1);
-            tmem_ld_32x16(t_acc + 64 + c0, r2);
-            tmem_wait_ld();
+            float y1[16], y2[16];
+            dl_acc16(t_acc + c0, two, y1);
+            dl_acc16(t_acc + 64 + c0, two, y2);
             if (dst) {
-              float y1[16], y2[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                y1[i] = __uint_as_float(r1[i]) * rs;
-                y2[i] = __uint_as_float(r2[i]) * rs;
+                y1[i] *= rs;
+                y2[i] *= rs;
               }
               if (is_q || is_k) {
                 float w1[16], w2[16], cs[16], sn[16];
@@ -400,9 +497,11 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           // (the barrier orders the other 127 threads' writes before thread 0's release, which is cumulative)
           epi_bar_sync();
           if ((threadIdx.x & 127) == 0 && *abort_flag == 0) {
-            __threadfence();
-            red_release_add(p.counters + gi, 1u);
+            red_release_add(p.counters + gi, 1u);     // release at gpu scope: no separate fence needed
+            DL_TRACE(3 + 3 * gi);
           }
+        } else if ((threadIdx.x & 127) == 0) {
+          DL_TRACE(3 + 3 * gi);
         }
       }
     }
@@ -425,7 +524,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && *abort_flag == 0) {
     // the last CTA out re-arms the counters for the next launch
@@ -439,12 +538,41 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
 
 // ----------------------------------------------------------------------------- host side
 static unsigned* g_dl_counters[64] = {nullptr};
+static unsigned long long* g_dl_trace = nullptr;     // [sm_count][16], only with KD_DECODE_LAYER_TRACE=1
 
 // Called when a kernel reported an error: a launch that gave up leaves its counters dirty.
 int decode_layer_reset_counters() {
   const int dev = ctx().device;
   if (dev >= 0 && dev < 64 && g_dl_counters[dev])
     KD_CUDA_CHECK(cudaMemsetAsync(g_dl_counters[dev], 0, DL_COUNTERS * sizeof(unsigned), ctx().stream));
+  return KD_OK;
+}
+
+typedef CUresult (*DlEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+// bf16 tensor map with dims (innermost first) {d0, d1, d2}, byte strides {s1, s2} of d1 and d2, box {64, b1, b2},
+// 128-byte swizzle, zero fill outside.
+static int dl_tmap3(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2, uint32_t b1,
+                    uint32_t b2) {
+  static DlEncodeFn fn = nullptr;
+  if (!fn) {
+    void* q = nullptr;
+    cudaDriverEntryPointQueryResult r;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &q, cudaEnableDefault, &r) == cudaSuccess && r == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<DlEncodeFn>(q);
+  }
+  if (!fn) return fail(KD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  KD_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0 && s1 % 16 == 0 && s2 % 16 == 0, "TMA base and strides must be multiples of 16 bytes");
+  KD_REQUIRE(b1 >= 1 && b1 <= 256 && b2 >= 1 && b2 <= 256, "TMA box [%u,%u] out of range", b1, b2);
+  cuuint64_t gdim[3] = {d0, d1, d2};
+  cuuint64_t gstr[2] = {s1, s2};
+  cuuint32_t box[3] = {(cuuint32_t)DL_BK, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(KD_ERR_CUDA, "cuTensorMapEncodeTiled (decode layer) failed with code %d", (int)r);
   return KD_OK;
 }
 
@@ -468,6 +596,19 @@ static bool dl_bf16_2d(const kd_tensor* t, int64_t rows, int64_t cols) {
 }
 static bool dl_f32_rows(const kd_tensor* t, int64_t rows, int64_t cols) {
   return t && t->dtype == KD_F32 && is_contiguous(t) && numel(t) == rows * cols;
+}
+
+// Timestamps of the last kd_decode_layer_fused launch (nanoseconds, [sm_count][16]: 0 start; per phase
+// g: 1+3g dependency seen by the producer, 2+3g accumulator seen by the epilogue, 3+3g outputs
+// published).  Filled only when the process runs with KD_DECODE_LAYER_TRACE=1.
+KD_API int kd_debug_decode_layer_trace(uint64_t* out, int max_entries) {
+  KD_TRY(require_init());
+  KD_REQUIRE(out && max_entries > 0, "bad argument");
+  KD_REQUIRE(g_dl_trace != nullptr, "no trace: start the process with KD_DECODE_LAYER_TRACE=1");
+  const int n = ctx().sm_count * 16 < max_entries ? ctx().sm_count * 16 : max_entries;
+  KD_CUDA_CHECK(cudaStreamSynchronize(ctx().stream));
+  KD_CUDA_CHECK(cudaMemcpy(out, g_dl_trace, (size_t)n * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+  return KD_OK;
 }
 
 KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
@@ -552,9 +693,6 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
   p.Mb = (int)Mb; p.H = (int)H; p.eps = eps;
   p.x_box = Mb <= 8 ? 8 : (Mb <= 16 ? 16 : (Mb <= 32 ? 32 : (Mb <= 64 ? 64 : 128)));
   p.has_qkv = has_qkv ? 1 : 0;
-  const int stage_bytes = p.x_box * DL_BK * 2 + DL_W_BYTES;
-  p.stages = (226 * 1024 - 1024 - 1024) / stage_bytes;
-  if (p.stages > 12) p.stages = 12;
   const int dev = c.device;
   KD_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
   if (!g_dl_counters[dev]) {
@@ -563,6 +701,10 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
   }
   p.counters = g_dl_counters[dev];
   p.err = c.error_flag;
+  static const bool want_trace = [] { const char* e = getenv("KD_DECODE_LAYER_TRACE"); return e && e[0] == '1'; }();
+  if (want_trace && !g_dl_trace) KD_CUDA_CHECK(cudaMalloc(&g_dl_trace, (size_t)G * 16 * sizeof(unsigned long long)));
+  if (g_dl_trace) KD_CUDA_CHECK(cudaMemsetAsync(g_dl_trace, 0, (size_t)G * 16 * sizeof(unsigned long long), c.stream));
+  p.trace = g_dl_trace;
 
   struct Op { const void* w; int N, K, step; } ops[4] = {
       {p_wo, (int)H, (int)Ko, 16}, {p_wgu, (int)I2, (int)H, 32}, {p_wd, (int)H, (int)I, 16}, {p_wq, (int)Nq, (int)H, 128}};
@@ -571,6 +713,11 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
     DlGemm& g = p.g[i];
     g.N = ops[i].N; g.K = ops[i].K;
     g.n_unit = i == 3 ? 128 : dl_unit_rows(g.N, g.K, G, ops[i].step);
+    {   // experiment hook: KD_DL_N0 / KD_DL_N1 / KD_DL_N2 override the unit width of a phase
+      const char* names[3] = {"KD_DL_N0", "KD_DL_N1", "KD_DL_N2"};
+      const char* e = i < 3 ? getenv(names[i]) : nullptr;
+      if (e && atoi(e) >= ops[i].step && atoi(e) <= 128 && atoi(e) % ops[i].step == 0) g.n_unit = atoi(e);
+    }
     g.units = (g.N + g.n_unit - 1) / g.n_unit;
     KD_REQUIRE(g.units <= DL_MAX_UNITS, "%d units in phase %d (at most %d)", g.units, i, DL_MAX_UNITS);
   }
@@ -612,12 +759,26 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
   static DlMaps maps;   // large: keep it off the stack
   const void* xs[4] = {p_attn, p.x1, p.act, p.x2};
   const int64_t ldx[4] = {attn->strides[0], H, I, H};
+  const int x1 = p.x_box * DL_BK * 2;
+  static const bool no_groups = [] { const char* e = getenv("KD_DL_NO_GROUPS"); return e && e[0] == '1'; }();
   for (int i = 0; i < n_gemms; ++i) {
-    KD_TRY(make_tmap_bf16_2d(&maps.w[i], ops[i].w, (uint64_t)ops[i].N, (uint64_t)ops[i].K, (uint64_t)ops[i].K, (uint32_t)p.g[i].n_unit, DL_BK));
-    KD_TRY(make_tmap_bf16_2d(&maps.x[i], xs[i], (uint64_t)Mb, (uint64_t)ops[i].K, (uint64_t)ldx[i], (uint32_t)p.x_box, DL_BK));
+    DlGemm& g = p.g[i];
+    const int n_kb = (g.K + DL_BK - 1) / DL_BK;
+    g.grouped = (g.K % DL_BK == 0 && !no_groups) ? 1 : 0;
+    g.kg = g.grouped ? std::max(1, std::min(std::min(DL_X_AREA / x1, DL_W_AREA / (g.n_unit * DL_BK * 2)), std::min(n_kb, 16))) : 1;
+    if (g.grouped) {
+      // [k-block, row, 64]: the k-blocks of a row are 128 bytes apart, rows a whole row apart
+      int rc = dl_tmap3(&maps.w[i], ops[i].w, DL_BK, (uint64_t)g.N, (uint64_t)n_kb, (uint64_t)g.K * 2, 128, (uint32_t)g.n_unit, (uint32_t)g.kg);
+      if (rc == KD_OK) rc = dl_tmap3(&maps.x[i], xs[i], DL_BK, (uint64_t)Mb, (uint64_t)n_kb, (uint64_t)ldx[i] * 2, 128, (uint32_t)p.x_box, (uint32_t)g.kg);
+      if (rc != KD_OK) { g.grouped = 0; g.kg = 1; }   // the driver refused the view: one k-block per copy
+    }
+    if (!g.grouped) {
+      KD_TRY(dl_tmap3(&maps.w[i], ops[i].w, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * (uint64_t)g.N, (uint32_t)g.n_unit, 1));
+      KD_TRY(dl_tmap3(&maps.x[i], xs[i], (uint64_t)g.K, (uint64_t)Mb, 1, (uint64_t)ldx[i] * 2, (uint64_t)ldx[i] * 2 * (uint64_t)Mb, (uint32_t)p.x_box, 1));
+    }
   }
   if (n_gemms < 4) { maps.w[3] = maps.w[0]; maps.x[3] = maps.x[0]; }
-  const int smem = p.stages * stage_bytes + 1024 + 1024;
+  const int smem = DL_STAGES * DL_SLOT + 1024 + 1024;
   static bool configured[64] = {false};
   if (!configured[dev]) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(decode_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));

@@ -514,11 +514,11 @@ template <int BLOCK_N, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p) {
   constexpr int STAGE_BYTES = GEMM_BM * GEMM_BK * 2 + BLOCK_N * GEMM_BK * 2;
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};   // per device: kd_shutdown + kd_init may move the library to another GPU
+  if (!configured[ctx().device & 63]) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BLOCK_N, STAGES>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    configured = true;
+    configured[ctx().device & 63] = true;
   }
   p.num_m_tiles = (p.M + GEMM_BM - 1) / GEMM_BM;
   p.num_n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
@@ -795,10 +795,10 @@ int gemm_bf16_skinny(const void* x, int64_t ldx, const void* W, int64_t ldw, int
   KD_TRY(make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, GEMM_BK));
   KD_TRY(make_tmap_bf16_2d(&tx, x, (uint64_t)Mb, (uint64_t)K, (uint64_t)ldx, (uint32_t)p.x_box, GEMM_BK));
   const int smem = stages * stage_bytes + 1024 + 256;
-  static int configured = 0;
-  if (configured < smem) {
+  static bool skinny_configured[64] = {false};   // per device
+  if (!skinny_configured[ctx().device & 63]) {
     KD_CUDA_CHECK(cudaFuncSetAttribute(gemm_skinny_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
-    configured = 210 * 1024;
+    skinny_configured[ctx().device & 63] = true;
   }
   dim3 grid((N + 127) / 128, splits);
   KD_CUDA_CHECK(launch_ex(gemm_skinny_tcgen05_kernel, grid, dim3(GEMM_THREADS), (size_t)smem, tw, tx, p));

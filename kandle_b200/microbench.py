@@ -160,6 +160,22 @@ def bench_layer(a) -> dict:
                  r(w["wq"]), r(qw), r(kw), r(cos), r(sin), r(pos), r(w["kc"]), r(w["vc"]), r(q), r(h2), None)
     ms = _time(run, a.iters, a.warmup)
     nbytes = 2.0 * (H * Ko + 2 * I * H + H * I + Nq * H)
+    import os
+    if os.environ.get("KD_DECODE_LAYER_TRACE") == "1":
+        # phase timeline of the last launch: for each phase, when the first / last CTA saw its
+        # dependency, had its accumulator, had published (microseconds after the earliest CTA start)
+        buf = (ctypes.c_uint64 * (148 * 16))()
+        lib.call("kd_debug_decode_layer_trace", buf, 148 * 16)
+        t = np.array(buf, dtype=np.float64).reshape(-1, 16)
+        t0 = t[:, 0][t[:, 0] > 0].min()
+        rows = []
+        for g in range(4):
+            row = {}
+            for name, col in (("dep_seen", 1 + 3 * g), ("acc_ready", 2 + 3 * g), ("published", 3 + 3 * g)):
+                v = t[:, col][t[:, col] > 0]
+                row[name] = [round(float(v.min() - t0) / 1e3, 2), round(float(v.max() - t0) / 1e3, 2), int(v.size)] if v.size else None
+            rows.append(row)
+        print(json.dumps({"trace_us_first_last_count": rows, "start_spread_us": round(float(t[:, 0].max() - t0) / 1e3, 2)}))
     return {"kernel": "decode_layer_kernel", "m": m, "hidden": H, "attn": Ko, "inter": I, "qkv": Nq, "weight_sets": a.sets,
             "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
 

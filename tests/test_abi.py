@@ -80,3 +80,35 @@ def test_slice_parser_and_broadcast():
         core._broadcast_shape((4, 3), (5,))
     assert core._promote("int32", "float32") == "float32"
     assert core._promote("bfloat16", "float32") == "float32"
+
+
+class _FakeStorage:
+    """Stands in for a device storage so that view arithmetic can be checked without a GPU."""
+    handle, id, nbytes = 1, 1, 1 << 20
+
+    def incRef(self):
+        pass
+
+    def decRef(self):
+        pass
+
+    isDisposed = False
+
+
+def test_select_and_integer_index_raise_like_the_reference():
+    """packages/core/src/dispatch/handlers/shape.ts:500-518: a dim or an index outside its range is an
+    error, never a wrap-around to another element."""
+    from kandle_b200 import core
+    from kandle_b200.backend import CudaTensorHandle
+    t = core.Tensor(_handle=CudaTensorHandle(_FakeStorage(), (4, 5, 6), "float32"))
+    assert t.select(1, -1).shape == (4, 6) and t.select(1, -1).offset == 4 * 6
+    assert t.select(-1, 2).shape == (4, 5) and t.select(-1, 2).offset == 2
+    with pytest.raises(IndexError, match="index 5 out of range for dim 1 with size 5"):
+        t.select(1, 5)
+    with pytest.raises(IndexError, match="index -6 out of range"):
+        t.select(1, -6)
+    with pytest.raises(IndexError, match="dim 3 out of range for tensor with 3 dimensions"):
+        t.select(3, 0)
+    with pytest.raises(IndexError):
+        t.slice(":, 7, :")
+    assert t.slice(":, -5, 1:3").shape == (4, 2)
