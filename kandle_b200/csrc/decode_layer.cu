@@ -365,6 +365,10 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
         if ((threadIdx.x & 127) == 0) counter_wait(p.counters + (gi - 1), (unsigned)p.g[gi - 1].units, abort_flag, p.err, 526);
         epi_bar_sync();
         if (valid) rs = dl_rs(gi == 1 ? p.ssq1 : p.ssq2, p.g[gi - 1].units, p.Mb, m, p.H, p.eps);
+      } else if (has_unit && gi == 2) {
+        // h1 (the residual of this phase) is complete once phase 0 is: only then may it be fetched early
+        if ((threadIdx.x & 127) == 0) counter_wait(p.counters + 0, (unsigned)p.g[0].units, abort_flag, p.err, 526);
+        epi_bar_sync();
       }
       for (int u = (cta - g.rot % G + G) % G; u < g.units; u += G) {
         const int buf = acc_n & 1, use = acc_n >> 1;
