@@ -82,7 +82,8 @@ def main():
         err = np.abs(got - ref)
         ref_t = om.greedy_generate(ids, 6).astype(np.int64)
         tol = max(1.0, float(np.abs(ref).max()) / 3.0)      # the bf16 bound is relative to the logits' range (|3| at the 0.6B widths)
-        ok = (np.quantile(err, 0.999) <= 2e-2 * tol and err.max() <= 3e-2 * tol and same_across_ranks and np.array_equal(toks, toks_eager)
+        # (the prefill partial sums of o_proj / down_proj are rounded to bf16 before the all-reduce: one more rounding than on one GPU)
+        ok = (np.quantile(err, 0.999) <= 2e-2 * tol and err.max() <= 3.5e-2 * tol and same_across_ranks and np.array_equal(toks, toks_eager)
               and (toks == ref_t).mean() >= 0.8 and (toks_nccl == ref_t).mean() >= 0.8)
         msg = (f"TP{world}: logits max err {err.max():.3e} p99.9 {np.quantile(err, 0.999):.3e}; tokens equal across ranks "
                f"{same_across_ranks}; graph==eager {np.array_equal(toks, toks_eager)}; token agreement with oracle {(toks == ref_t).mean():.2f}; "
