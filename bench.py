@@ -505,7 +505,7 @@ def kernel_rooflines(bn: Bench, eng, B: int, S: int, T: int, dims: dict):
                     lw_, nl = eng.layers[li], eng.layers[li + 1]
                     lib.call("kd_decode_layer_fused", r_(attn2d), r_(lw_["wo"]), r_(d["h"]), r_(lw_["post_norm"]), r_(lw_["wgu"]),
                              r_(lw_["wdown"]), r_(nl["in_norm"]), eps, r_(nl["wqkv"]), r_(nl["q_norm"]), r_(nl["k_norm"]), r_(d["cos"]),
-                             r_(d["sin"]), r_(d["pos"]), r_(caches[li + 1][0]), r_(caches[li + 1][1]), r_(d["q"]), r_(d["h"]), None)
+                             r_(d["sin"]), r_(d["pos"]), r_(caches[li + 1][0]), r_(caches[li + 1][1]), None, r_(d["q"]), r_(d["h"]), None)
             us_c = bn.timed_ms(layer_all, reps=5) * 1e3 / (n_l - 1)
             other["decode_layer_fused"] = roof("hbm", wbytes / (us_c * 1e-6) / 1e9, bn.peaks, us_per_launch=us_c, sequences=B,
                                                note="o_proj .. next layer's QKV + q/k-norm + RoPE + cache write in one launch; latency-bound "

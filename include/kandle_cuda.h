@@ -304,6 +304,19 @@ int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_norm_we
                                 const kd_tensor* k_norm_weight, float eps, const kd_tensor* cos,
                                 const kd_tensor* sin, const kd_tensor* k_cache, const kd_tensor* v_cache,
                                 const kd_tensor* pos, int start_pos, const kd_tensor* q_out);
+/* The same into a PAGED cache (no counterpart in the reference, whose only cache is the contiguous
+ * StaticKVCache; the update semantics of packages/model-utils/src/kv-cache.ts:164-212 are kept:
+ * positions [pos, pos+S) of every sequence are overwritten, nothing else moves): k_pool / v_pool
+ * [pages,Hkv,128,D], block_table int32 [B,max_pages] names the page of each run of 128 positions. */
+int kd_qkv_norm_rope_cachewrite_paged(const kd_tensor* qkv, const kd_tensor* q_norm_weight,
+                                      const kd_tensor* k_norm_weight, float eps, const kd_tensor* cos,
+                                      const kd_tensor* sin, const kd_tensor* k_pool, const kd_tensor* v_pool,
+                                      const kd_tensor* block_table, const kd_tensor* pos, int start_pos,
+                                      const kd_tensor* q_out);
+/* Scatters rows [0,S) of contiguous K / V [B,Hkv,S,D] (what a prefill produced) into positions
+ * [start_pos, start_pos+S) of a paged cache.  Same cache-update semantics as above. */
+int kd_kv_pages_write(const kd_tensor* k_src, const kd_tensor* v_src, const kd_tensor* k_pool, const kd_tensor* v_pool,
+                      const kd_tensor* block_table, int start_pos);
 /* The QKV projection and kd_qkv_norm_rope_cachewrite in one tensor-core GEMM whose epilogue does the
  * q/k-norm, RoPE and KV-cache write (head_dim 128, prefill): x bf16 [B*S,K], wqkv bf16 [(Hq+2Hkv)*128,K]
  * (q rows, k rows, v rows). */
@@ -405,7 +418,9 @@ int kd_decode_layer_chain_splits(int64_t N, int64_t K, int* splits_out);
  *   qkv = rs2 (x2 W_qkv_next^T)                 one head per unit of work, whose epilogue does that head's
  *                                              RMSNorm (q_norm_w / k_norm_w), the rotation by cos/sin
  *                                              [1,64] and stores q into q_out [Mb,1,Hq,128] or k / v into
- *                                              row *pos of the next layer's caches
+ *                                              row *pos of the next layer's caches (contiguous
+ *                                              [B,Hkv,maxS,128], or pools [pages,Hkv,128,128] addressed
+ *                                              through block_table int32 [B,max_pages] when it is given)
  * The sequences are the rows of every accumulator and a unit of work is a narrow slice of weight
  * rows over the whole of K, so no partial sums exist and an epilogue thread owns one sequence.
  * With w_qkv_next == NULL (after the last layer) the launch ends with
@@ -424,8 +439,8 @@ int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_
                           const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
                           const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
                           const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
-                          const kd_tensor* v_cache_next, const kd_tensor* q_out, const kd_tensor* resid_out,
-                          const kd_tensor* x_final);
+                          const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
+                          const kd_tensor* resid_out, const kd_tensor* x_final);
 
 /* ---------------------------------------------------------------------------------------------
  * Tensor-parallel collectives (no counterpart in the reference, which is single-device).  One

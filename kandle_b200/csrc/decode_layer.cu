@@ -99,6 +99,8 @@ struct DlParams {
   __nv_bfloat16* k_cache;     // [Mb][Hkv][max_s][128] with strides kc_*
   __nv_bfloat16* v_cache;
   int64_t kc_b, kc_h, kc_s;
+  const int* table;           // paged cache: page of position pos of sequence m = table[m * max_pages + pos / 128] (NULL: contiguous)
+  int max_pages;
   __nv_bfloat16* x_final;     // [Mb][H] (last layer)
   unsigned* counters;         // [8]: phases 0..2, [7] exit ticket
   int* err;
@@ -231,6 +233,12 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) DL_TRACE(0);
+  // Programmatic dependent launch, both ways.  The next kernel (the attention of the next layer) may
+  // start filling SMs as this kernel's CTAs leave them: it waits for this whole grid before it reads
+  // anything.  And this kernel may have been started while the attention before it was still
+  // running: nothing that depends on earlier kernels is touched before pdl_wait() below (the weight
+  // tiles of phase 0 are fetched ahead of it, they depend on nothing).
+  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -254,7 +262,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           if (g.grouped) tma_load_3d(smem + st * DL_SLOT, xm, &full[st], 0, 0, grp * g.kg);
           else tma_load_3d(smem + st * DL_SLOT, xm, &full[st], grp * DL_BK, 0, 0);
         };
-        bool dep_ready = (gi == 0);
+        bool dep_ready = false;
         for (int u = (cta - g.rot % G + G) % G; ok && u < g.units; u += G) {
           const int row0 = u * g.n_unit;
           int i = 0;
@@ -269,7 +277,8 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
               if (++stage == DL_STAGES) { stage = 0; ring_phase ^= 1; }
             }
             if (!ok) break;
-            if (!counter_wait(p.counters + (gi - 1), (unsigned)p.g[gi - 1].units, abort_flag, p.err, 522)) { ok = false; break; }
+            if (gi == 0) pdl_wait();          // the attention output: complete when the preceding kernels are
+            else if (!counter_wait(p.counters + (gi - 1), (unsigned)p.g[gi - 1].units, abort_flag, p.err, 522)) { ok = false; break; }
             // the activations were written through the generic proxy by other SMs; TMA reads them
             // through the async proxy
             asm volatile("fence.proxy.async;" ::: "memory");
@@ -354,6 +363,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
     int acc_n = 0;
     bool ok = true;
+    pdl_wait();      // residual, position, tables: produced by earlier kernels
     // Control flow between the 128-thread barriers below never depends on per-thread state: `ok`
     // is made uniform (a barrier that ORs the threads' flags) before it decides anything.
     for (int gi = 0; gi < n_gemms; ++gi) {
@@ -458,7 +468,12 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             if (is_q) dst = p.q_out + ((int64_t)m * p.Hq + head) * 128;
             else if (pos_ok) {
               const int hk = is_k ? head - p.Hq : head - p.Hq - p.Hkv;
-              dst = (is_k ? p.k_cache : p.v_cache) + (int64_t)m * p.kc_b + (int64_t)hk * p.kc_h + (int64_t)pos * p.kc_s;
+              int64_t outer = m, row = pos;
+              if (p.table) {
+                outer = p.table[(int64_t)m * p.max_pages + pos / 128];
+                row = pos % 128;
+              }
+              dst = (is_k ? p.k_cache : p.v_cache) + outer * p.kc_b + (int64_t)hk * p.kc_h + row * p.kc_s;
             }
           }
           const __nv_bfloat16* hw = is_q ? p.qw : p.kw;
@@ -620,8 +635,8 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
                                  const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
                                  const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
                                  const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
-                                 const kd_tensor* v_cache_next, const kd_tensor* q_out, const kd_tensor* resid_out,
-                                 const kd_tensor* x_final) {
+                                 const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
+                                 const kd_tensor* resid_out, const kd_tensor* x_final) {
   KD_TRY(require_init());
   KD_REQUIRE(attn && w_o && resid_in && post_norm_w && w_gate_up && w_down && next_norm_w && resid_out, "null tensor");
   KD_REQUIRE(attn->ndim == 2 && w_o->ndim == 2 && w_gate_up->ndim == 2 && w_down->ndim == 2, "operands must be 2-D");
@@ -653,8 +668,12 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
                "q_out must be contiguous bf16 [Mb,1,Hq,128]");
     Hq = (int)q_out->shape[2];
     KD_REQUIRE(k_cache_next->ndim == 4 && k_cache_next->dtype == KD_BF16 && v_cache_next->dtype == KD_BF16 &&
-                   k_cache_next->shape[0] >= Mb && k_cache_next->shape[3] == 128 && k_cache_next->strides[3] == 1,
-               "caches must be bf16 [B>=Mb,Hkv,maxS,128] with unit head_dim stride");
+                   (block_table || k_cache_next->shape[0] >= Mb) && k_cache_next->shape[3] == 128 && k_cache_next->strides[3] == 1,
+               "caches must be bf16 [B>=Mb,Hkv,maxS,128] (or pools [pages,Hkv,128,128] with a block table) with unit head_dim stride");
+    if (block_table)
+      KD_REQUIRE(block_table->dtype == KD_I32 && block_table->ndim == 2 && is_contiguous(block_table) && block_table->shape[0] >= Mb &&
+                     k_cache_next->shape[2] == 128,
+                 "block_table must be a contiguous int32 [B>=Mb, max_pages] tensor and the pools must have pages of 128 rows");
     Hkv = (int)k_cache_next->shape[1];
     for (int i = 0; i < 4; ++i)
       KD_REQUIRE(v_cache_next->shape[i] == k_cache_next->shape[i] && v_cache_next->strides[i] == k_cache_next->strides[i],
@@ -674,11 +693,12 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
   KD_TRY(tensor_ptr(post_norm_w, &p_pn)); KD_TRY(tensor_ptr(w_gate_up, &p_wgu)); KD_TRY(tensor_ptr(w_down, &p_wd));
   KD_TRY(tensor_ptr(next_norm_w, &p_nn)); KD_TRY(tensor_ptr(resid_out, &p_ro));
   void *p_wq = nullptr, *p_qw = nullptr, *p_kw = nullptr, *p_cos = nullptr, *p_sin = nullptr, *p_pos = nullptr, *p_kc = nullptr,
-       *p_vc = nullptr, *p_q = nullptr, *p_xf = nullptr;
+       *p_vc = nullptr, *p_q = nullptr, *p_xf = nullptr, *p_bt = nullptr;
   if (has_qkv) {
     KD_TRY(tensor_ptr(w_qkv_next, &p_wq)); KD_TRY(tensor_ptr(q_norm_w, &p_qw)); KD_TRY(tensor_ptr(k_norm_w, &p_kw));
     KD_TRY(tensor_ptr(cos, &p_cos)); KD_TRY(tensor_ptr(sin, &p_sin)); KD_TRY(tensor_ptr(pos, &p_pos));
     KD_TRY(tensor_ptr(k_cache_next, &p_kc)); KD_TRY(tensor_ptr(v_cache_next, &p_vc)); KD_TRY(tensor_ptr(q_out, &p_q));
+    if (block_table) KD_TRY(tensor_ptr(block_table, &p_bt));
   } else {
     KD_TRY(tensor_ptr(x_final, &p_xf));
   }
@@ -750,7 +770,9 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
   p.w_next = static_cast<const __nv_bfloat16*>(p_nn);
   p.Hq = Hq; p.Hkv = Hkv;
   if (has_qkv) {
-    p.max_s = (int)k_cache_next->shape[2];
+    p.table = static_cast<const int*>(p_bt);
+    p.max_pages = block_table ? (int)block_table->shape[1] : 0;
+    p.max_s = block_table ? p.max_pages * 128 : (int)k_cache_next->shape[2];
     p.qw = static_cast<const __nv_bfloat16*>(p_qw); p.kw = static_cast<const __nv_bfloat16*>(p_kw);
     p.cos_t = static_cast<const float*>(p_cos); p.sin_t = static_cast<const float*>(p_sin);
     p.pos = static_cast<const int*>(p_pos);
@@ -793,11 +815,16 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
   cfg.blockDim = dim3(DL_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = c.stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident, or the launch fails
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (c.pdl) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   KD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, decode_layer_kernel, maps, p));
   return after_launch("decode_layer_kernel");
 }

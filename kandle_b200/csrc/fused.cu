@@ -5,6 +5,8 @@
 //
 // Several take their input either as a bf16 matrix or as fp32 split-K partial sums
 // [splits][rows][cols] written by the skinny decode GEMM, which they add up on the fly.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -39,6 +41,10 @@ struct QkvRopeParams {
   int64_t kc_b, kc_h, kc_s;   // cache strides (elements)
   int max_s;
   int pos_host;
+  // paged cache: the "cache" tensors are pools [pages,Hkv,128,D] and the page of position `pos` of
+  // sequence b is table[b * max_pages + pos / 128] (NULL: contiguous [B,Hkv,maxS,D])
+  const int* table;
+  int max_pages;
 };
 
 template <int V>
@@ -156,7 +162,12 @@ __global__ void qkv_norm_rope_kernel(const void* __restrict__ src, const void* _
       return;
     }
     const int hk = is_k ? head - p.Hq : head - p.Hq - p.Hkv;
-    dst = (is_k ? k_cache : v_cache) + (int64_t)b * p.kc_b + (int64_t)hk * p.kc_h + (int64_t)pos * p.kc_s;
+    int64_t outer = b, row = pos;
+    if (p.table) {
+      outer = p.table[(int64_t)b * p.max_pages + pos / 128];
+      row = pos % 128;
+    }
+    dst = (is_k ? k_cache : v_cache) + outer * p.kc_b + (int64_t)hk * p.kc_h + row * p.kc_s;
   }
   store_bf16<V>(dst + e0, x1.v);
   store_bf16<V>(dst + HALF + e0, x2.v);
@@ -405,10 +416,10 @@ KD_API int kd_rope_table(const kd_tensor* inv_freq, const kd_tensor* pos, int st
   return after_launch("rope_table_kernel");
 }
 
-KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_norm_weight, const kd_tensor* k_norm_weight,
-                                       float eps, const kd_tensor* cos, const kd_tensor* sin, const kd_tensor* k_cache,
-                                       const kd_tensor* v_cache, const kd_tensor* pos, int start_pos,
-                                       const kd_tensor* q_out) {
+static int qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_norm_weight, const kd_tensor* k_norm_weight,
+                                    float eps, const kd_tensor* cos, const kd_tensor* sin, const kd_tensor* k_cache,
+                                    const kd_tensor* v_cache, const kd_tensor* block_table, const kd_tensor* pos, int start_pos,
+                                    const kd_tensor* q_out) {
   KD_TRY(require_init());
   KD_REQUIRE(qkv && q_norm_weight && k_norm_weight && cos && sin && k_cache && v_cache && q_out, "null tensor");
   KD_REQUIRE(q_out->ndim == 4 && q_out->dtype == KD_BF16 && is_contiguous(q_out), "q_out must be contiguous bf16 [B,S,Hq,D]");
@@ -417,7 +428,19 @@ KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_
   const int B = (int)q_out->shape[0], S = (int)q_out->shape[1], Hq = (int)q_out->shape[2], D = (int)q_out->shape[3];
   const int Hkv = (int)k_cache->shape[1];
   KD_REQUIRE(D == 64 || D == 128, "head_dim must be 64 or 128");
-  KD_REQUIRE(k_cache->shape[0] == B && k_cache->shape[3] == D && k_cache->strides[3] == 1, "k_cache shape/stride mismatch");
+  const int* table = nullptr;
+  int max_pages = 0;
+  if (block_table) {
+    KD_REQUIRE(block_table->dtype == KD_I32 && block_table->ndim == 2 && is_contiguous(block_table) && block_table->shape[0] == B,
+               "block_table must be a contiguous int32 [B, max_pages] tensor");
+    KD_REQUIRE(k_cache->shape[2] == 128, "a paged cache needs pages of 128 rows");
+    void* pt = nullptr;
+    KD_TRY(tensor_ptr(block_table, &pt));
+    table = static_cast<const int*>(pt);
+    max_pages = (int)block_table->shape[1];
+  }
+  const int64_t cache_rows = table ? (int64_t)max_pages * 128 : k_cache->shape[2];
+  KD_REQUIRE((table || k_cache->shape[0] == B) && k_cache->shape[3] == D && k_cache->strides[3] == 1, "k_cache shape/stride mismatch");
   for (int i = 0; i < 4; ++i)
     KD_REQUIRE(v_cache->shape[i] == k_cache->shape[i] && v_cache->strides[i] == k_cache->strides[i],
                "v_cache must have k_cache's shape and strides");
@@ -442,8 +465,8 @@ KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_
     KD_TRY(tensor_ptr(pos, &pp));
     pos_dev = static_cast<const int*>(pp);
   } else {
-    KD_REQUIRE(start_pos >= 0 && start_pos + S <= k_cache->shape[2], "Cache overflow: trying to write to position %d-%d, but maxSeqLen is %lld",
-               start_pos, start_pos + S, (long long)k_cache->shape[2]);
+    KD_REQUIRE(start_pos >= 0 && start_pos + S <= cache_rows, "Cache overflow: trying to write to position %d-%d, but maxSeqLen is %lld",
+               start_pos, start_pos + S, (long long)cache_rows);
   }
   if (tokens == 0) return KD_OK;
   void *psrc, *pqw, *pkw, *pcos, *psin, *pkc, *pvc, *pqo;
@@ -458,8 +481,10 @@ KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_
   QkvRopeParams p{};
   p.tokens = (int)tokens; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.splits = splits; p.eps = eps;
   p.kc_b = k_cache->strides[0]; p.kc_h = k_cache->strides[1]; p.kc_s = k_cache->strides[2];
-  p.max_s = (int)k_cache->shape[2];
+  p.max_s = (int)cache_rows;
   p.pos_host = start_pos;
+  p.table = table;
+  p.max_pages = max_pages;
   const int threads = 256;                          // 16 heads of one token per CTA
   const dim3 blocks((unsigned)tokens, (unsigned)((Hq + 2 * Hkv + 15) / 16));
   KD_REQUIRE((q_norm_weight->dtype == KD_BF16 || q_norm_weight->dtype == KD_F32) &&
@@ -485,6 +510,86 @@ KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_
                             (int)k_norm_weight->dtype, (const float*)pcos, (const float*)psin, (__nv_bfloat16*)pqo,
                             (__nv_bfloat16*)pkc, (__nv_bfloat16*)pvc, pos_dev, p, ctx().error_flag));
   return after_launch("qkv_norm_rope_kernel");
+}
+
+KD_API int kd_qkv_norm_rope_cachewrite(const kd_tensor* qkv, const kd_tensor* q_norm_weight, const kd_tensor* k_norm_weight,
+                                       float eps, const kd_tensor* cos, const kd_tensor* sin, const kd_tensor* k_cache,
+                                       const kd_tensor* v_cache, const kd_tensor* pos, int start_pos,
+                                       const kd_tensor* q_out) {
+  return qkv_norm_rope_cachewrite(qkv, q_norm_weight, k_norm_weight, eps, cos, sin, k_cache, v_cache, nullptr, pos, start_pos, q_out);
+}
+
+KD_API int kd_qkv_norm_rope_cachewrite_paged(const kd_tensor* qkv, const kd_tensor* q_norm_weight, const kd_tensor* k_norm_weight,
+                                             float eps, const kd_tensor* cos, const kd_tensor* sin, const kd_tensor* k_pool,
+                                             const kd_tensor* v_pool, const kd_tensor* block_table, const kd_tensor* pos,
+                                             int start_pos, const kd_tensor* q_out) {
+  KD_REQUIRE(block_table != nullptr, "kd_qkv_norm_rope_cachewrite_paged needs a block table");
+  return qkv_norm_rope_cachewrite(qkv, q_norm_weight, k_norm_weight, eps, cos, sin, k_pool, v_pool, block_table, pos, start_pos, q_out);
+}
+
+// ----------------------------------------------------------------------------- contiguous K/V rows -> pages
+// Rows [0,S) of k_src / v_src [B,Hkv,S,D] go to positions [start_pos, start_pos+S) of a paged cache.
+// One thread per 16 bytes.
+__global__ void kv_pages_write_kernel(const __nv_bfloat16* __restrict__ ks, const __nv_bfloat16* __restrict__ vs,
+                                      __nv_bfloat16* __restrict__ kp, __nv_bfloat16* __restrict__ vp, const int* __restrict__ table,
+                                      int max_pages, int B, int Hkv, int S, int D, int start_pos, int64_t ss_b, int64_t ss_h,
+                                      int64_t ss_s, int64_t ps_p, int64_t ps_h, int64_t ps_s, int* __restrict__ err) {
+  pdl_wait();
+  pdl_trigger();
+  const int vec = D / 8;
+  const int64_t n = (int64_t)B * Hkv * S * vec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % vec);
+    int64_t r = i / vec;
+    const int s = (int)(r % S); r /= S;
+    const int h = (int)(r % Hkv);
+    const int b = (int)(r / Hkv);
+    const int pos = start_pos + s;
+    if (pos < 0 || pos >= max_pages * 128) {
+      if (atomicCAS(err, 0, 102) == 0) { err[1] = pos; err[2] = max_pages * 128; }
+      continue;
+    }
+    const int page = table[(int64_t)b * max_pages + pos / 128];
+    const int64_t src = (int64_t)b * ss_b + (int64_t)h * ss_h + (int64_t)s * ss_s + c * 8;
+    const int64_t dst = (int64_t)page * ps_p + (int64_t)h * ps_h + (int64_t)(pos % 128) * ps_s + c * 8;
+    *reinterpret_cast<uint4*>(kp + dst) = *reinterpret_cast<const uint4*>(ks + src);
+    *reinterpret_cast<uint4*>(vp + dst) = *reinterpret_cast<const uint4*>(vs + src);
+  }
+}
+
+KD_API int kd_kv_pages_write(const kd_tensor* k_src, const kd_tensor* v_src, const kd_tensor* k_pool, const kd_tensor* v_pool,
+                             const kd_tensor* block_table, int start_pos) {
+  KD_TRY(require_init());
+  KD_REQUIRE(k_src && v_src && k_pool && v_pool && block_table, "null tensor");
+  KD_REQUIRE(k_src->ndim == 4 && k_pool->ndim == 4 && k_src->dtype == KD_BF16 && v_src->dtype == KD_BF16 && k_pool->dtype == KD_BF16 &&
+                 v_pool->dtype == KD_BF16,
+             "sources [B,Hkv,S,D] and pools [pages,Hkv,128,D] must be bf16");
+  const int B = (int)k_src->shape[0], Hkv = (int)k_src->shape[1], S = (int)k_src->shape[2], D = (int)k_src->shape[3];
+  KD_REQUIRE(k_pool->shape[1] == Hkv && k_pool->shape[2] == 128 && k_pool->shape[3] == D && D % 8 == 0, "pool shape does not match the source");
+  for (int i = 0; i < 4; ++i) {
+    KD_REQUIRE(v_src->shape[i] == k_src->shape[i] && v_src->strides[i] == k_src->strides[i], "v_src must have k_src's shape and strides");
+    KD_REQUIRE(v_pool->shape[i] == k_pool->shape[i] && v_pool->strides[i] == k_pool->strides[i], "v_pool must have k_pool's shape and strides");
+  }
+  KD_REQUIRE(k_src->strides[3] == 1 && k_pool->strides[3] == 1, "unit stride along head_dim required");
+  for (int i = 0; i < 3; ++i) KD_REQUIRE(k_src->strides[i] % 8 == 0 && k_pool->strides[i] % 8 == 0, "strides must be multiples of 8 elements");
+  KD_REQUIRE(block_table->dtype == KD_I32 && block_table->ndim == 2 && is_contiguous(block_table) && block_table->shape[0] == B,
+             "block_table must be a contiguous int32 [B, max_pages] tensor");
+  const int max_pages = (int)block_table->shape[1];
+  KD_REQUIRE(start_pos >= 0 && start_pos + S <= max_pages * 128, "Cache overflow: trying to write to position %d-%d, but the block table covers %d",
+             start_pos, start_pos + S, max_pages * 128);
+  if ((int64_t)B * Hkv * S == 0) return KD_OK;
+  void *pks, *pvs, *pkp, *pvp, *pt;
+  KD_TRY(tensor_ptr(k_src, &pks)); KD_TRY(tensor_ptr(v_src, &pvs)); KD_TRY(tensor_ptr(k_pool, &pkp)); KD_TRY(tensor_ptr(v_pool, &pvp));
+  KD_TRY(tensor_ptr(block_table, &pt));
+  KD_REQUIRE(((reinterpret_cast<uintptr_t>(pks) | reinterpret_cast<uintptr_t>(pvs) | reinterpret_cast<uintptr_t>(pkp) |
+               reinterpret_cast<uintptr_t>(pvp)) & 15) == 0, "operands must be 16-byte aligned");
+  const int64_t n = (int64_t)B * Hkv * S * (D / 8);
+  const int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)ctx().sm_count * 16);
+  KD_CUDA_CHECK(launch_ex(kv_pages_write_kernel, dim3(blocks), dim3(256), 0, (const __nv_bfloat16*)pks, (const __nv_bfloat16*)pvs,
+                          (__nv_bfloat16*)pkp, (__nv_bfloat16*)pvp, (const int*)pt, max_pages, B, Hkv, S, D, start_pos, (int64_t)k_src->strides[0],
+                          (int64_t)k_src->strides[1], (int64_t)k_src->strides[2], (int64_t)k_pool->strides[0], (int64_t)k_pool->strides[1],
+                          (int64_t)k_pool->strides[2], ctx().error_flag));
+  return after_launch("kv_pages_write_kernel");
 }
 
 KD_API int kd_swiglu(const kd_tensor* gate_up, const kd_tensor* out) {

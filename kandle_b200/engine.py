@@ -59,12 +59,17 @@ class RandomInit:
 
 
 class Qwen3Engine:
-    def __init__(self, cfg: Qwen3Config, weights, max_batch: int, max_seq_len: int, tp_size: int = 1, tp_rank: int = 0):
+    def __init__(self, cfg: Qwen3Config, weights, max_batch: int, max_seq_len: int, tp_size: int = 1, tp_rank: int = 0,
+                 paged: bool = False, page_table: np.ndarray | None = None):
         """weights: HuggingFace-style names -> float32 arrays (rounded to bf16 on upload), or a
         RandomInit.  With tp_size > 1 a weight dictionary is this rank's tensor-parallel slice
         (parallel.shard_qwen3_weights; a RandomInit draws rank `tp_rank`'s slice itself), cfg
         describes the FULL model, and the library's communicator must have been initialised: the
-        partial outputs of o_proj and down_proj are all-reduced before the residual add."""
+        partial outputs of o_proj and down_proj are all-reduced before the residual add.
+        paged=True keeps the KV cache in pools of 128-position pages [pages,Hkv,128,D] per layer,
+        addressed through a block table int32 [max_batch, ceil(max_seq_len / 128)] (`page_table`, by
+        default a fixed shuffle of all pages): same cache semantics as the contiguous StaticKVCache
+        (packages/model-utils/src/kv-cache.ts:164-212), same tokens."""
         self.cfg = cfg
         self.tp = int(tp_size)
         self.B, self.max_seq_len = max_batch, max_seq_len
@@ -101,9 +106,25 @@ class Qwen3Engine:
         half = self.D // 2
         inv = np.array([1.0 / math.pow(c.ropeTheta, i / half) for i in range(half)], dtype=np.float32)  # rope.ts:159-171
         self.inv_freq = Tensor(inv, dtype="float32")
-        # KV cache [B,Hkv,maxS,D] per layer, zero-initialised (kv-cache.ts:123-130)
-        self.k_cache = [core.zeros((self.B, self.Hkv, max_seq_len, self.D), "bfloat16") for _ in range(self.L)]
-        self.v_cache = [core.zeros((self.B, self.Hkv, max_seq_len, self.D), "bfloat16") for _ in range(self.L)]
+        self.paged = bool(paged)
+        if self.paged:
+            per_seq = (max_seq_len + 127) // 128
+            n_pages = self.B * per_seq
+            if page_table is None:
+                page_table = np.random.Generator(np.random.PCG64(7)).permutation(n_pages).reshape(self.B, per_seq)
+            page_table = np.ascontiguousarray(page_table, dtype=np.int32)
+            if page_table.shape != (self.B, per_seq) or page_table.min() < 0 or len(np.unique(page_table)) != n_pages:
+                raise ValueError(f"page_table must hold {n_pages} distinct page indices in a [{self.B},{per_seq}] array")
+            n_pool = int(page_table.max()) + 1
+            self.block_table = Tensor(page_table)
+            # pools [pages,Hkv,128,D] per layer, zero-initialised like the contiguous cache
+            self.k_cache = [core.zeros((n_pool, self.Hkv, 128, self.D), "bfloat16") for _ in range(self.L)]
+            self.v_cache = [core.zeros((n_pool, self.Hkv, 128, self.D), "bfloat16") for _ in range(self.L)]
+        else:
+            self.block_table = None
+            # KV cache [B,Hkv,maxS,D] per layer, zero-initialised (kv-cache.ts:123-130)
+            self.k_cache = [core.zeros((self.B, self.Hkv, max_seq_len, self.D), "bfloat16") for _ in range(self.L)]
+            self.v_cache = [core.zeros((self.B, self.Hkv, max_seq_len, self.D), "bfloat16") for _ in range(self.L)]
         self.scale = 1.0 / math.sqrt(self.D)
         self._prefill_bufs = {}
         self._decode = None
@@ -221,6 +242,8 @@ class Qwen3Engine:
                 "sin": core.empty((S, self.D // 2), "float32"), "last": core.empty((B, self.H), "float32"), "xl": e(B, self.H),
                 "logits": core.empty((1, B, self.V), "float32"), "tok": core.empty((B,), "int64"),
                 "uniforms": core.zeros((B,), "float32"),
+                # paged cache: the prompt's K/V of one layer, contiguous, before they are scattered into pages
+                "kt": e(B, self.Hkv, S, self.D) if self.paged else None, "vt": e(B, self.Hkv, S, self.D) if self.paged else None,
             }}
         return self._prefill_bufs[key]
 
@@ -251,9 +274,14 @@ class Qwen3Engine:
         o_bhsd = w["attn"].permute([0, 2, 1, 3])
         attn2d = w["attn"].view(T, self.Hq * self.D)
         h, h1 = w["h"], w["h1"]
+        table = self.block_table.slice([slice(0, B), slice(None)]) if self.paged else None
         for li, lw in enumerate(self.layers):
-            kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
-            vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
+            if self.paged:
+                # the prompt's K/V go to a contiguous buffer that the attention reads, then into the pages
+                kc, vc = w["kt"].slice(":, :, :, :"), w["vt"].slice(":, :, :, :")
+            else:
+                kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
+                vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
             if self.tp == 1 or li == 0:
                 self._norm(h, lw["in_norm"], w["x"])     # (tensor parallel: later layers get x from the fused add+norm)
             if self.D == 128:
@@ -266,6 +294,8 @@ class Qwen3Engine:
                          ctypes.c_float(c.rmsNormEps), _r(w["cos"]), _r(w["sin"]), _r(kc), _r(vc), None, 0, _r(w["q"]))
             kp, vp = kc.slice(f":, :, :{S}, :"), vc.slice(f":, :, :{S}, :")
             lib.call("kd_flash_attention", _r(q_bhsd), _r(kp), _r(vp), _r(o_bhsd), ctypes.c_float(self.scale), 1)
+            if self.paged:
+                lib.call("kd_kv_pages_write", _r(kp), _r(vp), _r(self.k_cache[li]), _r(self.v_cache[li]), _r(table), 0)
             if self.tp == 1:
                 self._linear(attn2d, lw["wo"], h1, resid=h, epi=1)
                 self._norm(h1, lw["post_norm"], w["x"])
@@ -304,6 +334,8 @@ class Qwen3Engine:
             xa.dispose()
         for t in (q_bhsd, o_bhsd, attn2d, h3, last):
             t.dispose()
+        if table is not None:
+            table.dispose()
         self.pos = S
         self.cur_B = B
         return (w["tok"], full) if all_logits else w["tok"]
@@ -363,29 +395,43 @@ class Qwen3Engine:
         attn2d = d["attn"].view(B, self.Hq * self.D)
         h, h1 = d["h"], d["h1"]
         self._norm(h, self.layers[0]["in_norm"], d["x"])
+        table = self.block_table.slice([slice(0, B), slice(None)]) if self.paged else None
+
+        def cache_of(layer):
+            if self.paged:      # whole pools; the block table selects the pages of the B sequences
+                return self.k_cache[layer].slice(":, :, :, :"), self.v_cache[layer].slice(":, :, :, :")
+            return (self.k_cache[layer].slice([slice(0, B), slice(None), slice(None), slice(None)]),
+                    self.v_cache[layer].slice([slice(0, B), slice(None), slice(None), slice(None)]))
+
         for li, lw in enumerate(self.layers):
-            kc = self.k_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
-            vc = self.v_cache[li].slice([slice(0, B), slice(None), slice(None), slice(None)])
+            kc, vc = cache_of(li)
             if li == 0 or not (d["chain"] or d["fused"]):
                 lib.call("kd_linear_bf16_skinny", _r(d["x"]), _r(lw["wqkv"]), 0, _r(d["qkv_p"]))
             if li == 0 or not d["fused"]:
-                lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
-                         _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
-            lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
+                if self.paged:
+                    lib.call("kd_qkv_norm_rope_cachewrite_paged", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
+                             _r(d["sin"]), _r(kc), _r(vc), _r(table), _r(d["pos"]), 0, _r(d["q"]))
+                else:
+                    lib.call("kd_qkv_norm_rope_cachewrite", _r(d["qkv_p"]), _r(lw["q_norm"]), _r(lw["k_norm"]), eps, _r(d["cos"]),
+                             _r(d["sin"]), _r(kc), _r(vc), _r(d["pos"]), 0, _r(d["q"]))
+            if self.paged:
+                lib.call("kd_attention_decode_paged", _r(q_bh1d), _r(kc), _r(vc), _r(table), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0,
+                         _r(o_bh1d))
+            else:
+                lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
             nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
             if d["fused"]:
                 if li + 1 < self.L:
                     nl = self.layers[li + 1]
-                    kn = self.k_cache[li + 1].slice([slice(0, B), slice(None), slice(None), slice(None)])
-                    vn = self.v_cache[li + 1].slice([slice(0, B), slice(None), slice(None), slice(None)])
+                    kn, vn = cache_of(li + 1)
                     lib.call("kd_decode_layer_fused", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
                              _r(lw["wdown"]), _r(nxt), eps, _r(nl["wqkv"]), _r(nl["q_norm"]), _r(nl["k_norm"]), _r(d["cos"]),
-                             _r(d["sin"]), _r(d["pos"]), _r(kn), _r(vn), _r(d["q"]), _r(h), None)
+                             _r(d["sin"]), _r(d["pos"]), _r(kn), _r(vn), _r(table), _r(d["q"]), _r(h), None)
                     kn.dispose()
                     vn.dispose()
                 else:
                     lib.call("kd_decode_layer_fused", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
-                             _r(lw["wdown"]), _r(nxt), eps, None, None, None, None, None, None, None, None, None, _r(h), _r(d["x"]))
+                             _r(lw["wdown"]), _r(nxt), eps, None, None, None, None, None, None, None, None, None, None, _r(h), _r(d["x"]))
                 kc.dispose()
                 vc.dispose()
                 continue
@@ -412,6 +458,8 @@ class Qwen3Engine:
         lib.call("kd_increment_i32", _r(d["ctx"]), 1)
         for t in (q_bh1d, o_bh1d, attn2d):
             t.dispose()
+        if table is not None:
+            table.dispose()
 
     def start_decode(self, first_tokens: Tensor, use_graph: bool = True) -> dict:
         """Prepares the decode state after a prefill: next input ids = first_tokens (device int64 [B]),

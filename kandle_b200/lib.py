@@ -140,6 +140,8 @@ _SIGNATURES = {
     "kd_linear_bf16_skinny_splits": [ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)],
     "kd_rope_table": [_T, _T, ctypes.c_int, ctypes.c_int, _T, _T],
     "kd_qkv_norm_rope_cachewrite": [_T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, ctypes.c_int, _T],
+    "kd_qkv_norm_rope_cachewrite_paged": [_T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T, ctypes.c_int, _T],
+    "kd_kv_pages_write": [_T, _T, _T, _T, _T, ctypes.c_int],
     "kd_qkv_linear_norm_rope_cachewrite": [_T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, ctypes.c_int, _T],
     "kd_swiglu": [_T, _T],
     "kd_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
@@ -149,7 +151,7 @@ _SIGNATURES = {
     "kd_whisper_log_mel_norm": [_T, _T],
     "kd_sample": [_T, ctypes.c_double, ctypes.c_int, ctypes.c_double, ctypes.c_int, _T, _T, _T],
     "kd_decode_layer_chain": [_T, _T, _T, _T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T],
-    "kd_decode_layer_fused": [_T, _T, _T, _T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T],
+    "kd_decode_layer_fused": [_T, _T, _T, _T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T],
     "kd_debug_decode_layer_trace": [ctypes.POINTER(ctypes.c_uint64), ctypes.c_int],
     "kd_decode_layer_chain_splits": [ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)],
     "kd_set_pdl": [ctypes.c_int],

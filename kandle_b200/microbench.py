@@ -157,7 +157,7 @@ def bench_layer(a) -> dict:
         w = sets[state["i"] % a.sets]
         state["i"] += 1
         lib.call("kd_decode_layer_fused", r(attn), r(w["wo"]), r(h), r(post), r(w["wgu"]), r(w["wd"]), r(nxt), ctypes.c_float(1e-6),
-                 r(w["wq"]), r(qw), r(kw), r(cos), r(sin), r(pos), r(w["kc"]), r(w["vc"]), r(q), r(h2), None)
+                 r(w["wq"]), r(qw), r(kw), r(cos), r(sin), r(pos), r(w["kc"]), r(w["vc"]), None, r(q), r(h2), None)
     ms = _time(run, a.iters, a.warmup)
     nbytes = 2.0 * (H * Ko + 2 * I * H + H * I + Nq * H)
     import os

@@ -63,7 +63,7 @@ def _run(c, eps, alias=False):
     t = {"attn": bf(c["attn"]), "wo": bf(c["wo"]), "h": Tensor(c["h"]), "post": bf(c["post"]),
          "wgu": bf(interleave_gate_up(c["wg"], c["wu"])), "wd": bf(c["wd"]), "next": bf(c["next"])}
     t["h2"] = t["h"] if alias else core.empty((mb, H), "float32")
-    args = [None] * 9
+    args = [None] * 10
     xf = None
     if c["hq"]:
         hq, hkv = c["hq"], c["hkv"]
@@ -75,7 +75,7 @@ def _run(c, eps, alias=False):
         t["vc"] = Tensor(np.full((mb + 1, hkv, c["max_s"], D), 7.0, np.float32), dtype="bfloat16")
         t["q"] = core.empty((mb, 1, hq, D), "bfloat16")
         t["wq"], t["qw"], t["kw"] = bf(c["wq"]), bf(c["qw"]), bf(c["kw"])
-        args = [t["wq"], t["qw"], t["kw"], t["cos"], t["sin"], t["pos"], t["kc"], t["vc"], t["q"]]
+        args = [t["wq"], t["qw"], t["kw"], t["cos"], t["sin"], t["pos"], t["kc"], t["vc"], None, t["q"]]
     else:
         xf = t["xf"] = core.empty((mb, H), "bfloat16")
     t["call"] = lambda: lib.call("kd_decode_layer_fused", _r(t["attn"]), _r(t["wo"]), _r(t["h"]), _r(t["post"]), _r(t["wgu"]),
@@ -162,7 +162,7 @@ def test_fused_layer_reports_a_cache_row_outside_the_cache_and_checks_arguments(
     assert not (t["kc"].dataAsync()[:2, :, 7] == 7.0).all()
     with pytest.raises(lib.KandleCudaError):                          # QKV weights without caches
         lib.call("kd_decode_layer_fused", _r(t["attn"]), _r(t["wo"]), _r(t["h"]), _r(t["post"]), _r(t["wgu"]), _r(t["wd"]),
-                 _r(t["next"]), ctypes.c_float(eps), _r(t["wq"]), None, None, None, None, None, None, None, None, _r(t["h2"]), None)
+                 _r(t["next"]), ctypes.c_float(eps), _r(t["wq"]), None, None, None, None, None, None, None, None, None, _r(t["h2"]), None)
     with pytest.raises(lib.KandleCudaError):                          # last-layer form without x_final
         lib.call("kd_decode_layer_fused", _r(t["attn"]), _r(t["wo"]), _r(t["h"]), _r(t["post"]), _r(t["wgu"]), _r(t["wd"]),
-                 _r(t["next"]), ctypes.c_float(eps), None, None, None, None, None, None, None, None, None, _r(t["h2"]), None)
+                 _r(t["next"]), ctypes.c_float(eps), None, None, None, None, None, None, None, None, None, None, _r(t["h2"]), None)

@@ -137,3 +137,42 @@ def test_sampled_generation_replays_and_degenerates_to_greedy(backend, oracle):
     assert a.min() >= 0 and a.max() < 216
     eng.set_sampler(None)
     assert np.array_equal(eng.generate(ids, 10), greedy)
+
+
+def test_paged_engine_generates_the_tokens_of_the_contiguous_engine(backend, oracle):
+    """The KV cache in shuffled 128-position pages (pools + block table) end to end: prefill scatters
+    the prompt's K/V into pages, every decode step writes its row through the block table (layer 0
+    in kd_qkv_norm_rope_cachewrite_paged, the other layers in the fused layer kernel) and the paged
+    decode attention reads it back.  Cache semantics are those of the contiguous StaticKVCache
+    (packages/model-utils/src/kv-cache.ts:164-212), so the tokens must be the same, bit for bit: the
+    cache capacity is a multiple of the page size here, which keeps the split-KV factor identical."""
+    dims = dict(vocab=1024, hidden=256, inter=512, layers=3, heads=4, kv_heads=2, head_dim=128)
+    w = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(std=0.05, **dims).items()}
+    cfg = Qwen3Config(vocabSize=1024, hiddenSize=256, intermediateSize=512, numHiddenLayers=3, numAttentionHeads=4,
+                      numKeyValueHeads=2, headDim=128, dtype="bfloat16")
+    ids = synth.token_ids("paged.ids", (3, 150), 1024)
+    flat = Qwen3Engine(cfg, w, 3, 256)
+    want = flat.generate(ids, 12)
+    want_eager = flat.generate(ids, 12, use_graph=False)
+    flat.dispose()
+    paged = Qwen3Engine(cfg, w, 3, 256, paged=True)
+    assert paged.block_table.shape == (3, 2) and len(set(paged.block_table.dataAsync().ravel().tolist())) == 6
+    got = paged.generate(ids, 12)
+    got_eager = paged.generate(ids, 12, use_graph=False)
+    assert np.array_equal(want, want_eager) and np.array_equal(got, got_eager)
+    assert np.array_equal(got, want), (got, want)
+    # a smaller batch than the engine's capacity uses the first rows of the block table
+    assert np.array_equal(paged.generate(ids[:2], 5), want[:2, :5])
+    # an explicit table: pages in reverse order, with a hole in the pool
+    table = np.array([[7, 5], [4, 2], [1, 0]], np.int32)
+    with pytest.raises(ValueError):
+        Qwen3Engine(cfg, w, 3, 256, paged=True, page_table=np.zeros((3, 2), np.int32))     # pages must be distinct
+    paged2 = Qwen3Engine(cfg, w, 3, 256, paged=True, page_table=table)
+    assert np.array_equal(paged2.generate(ids, 12), want)
+    paged.dispose()
+    paged2.dispose()
+    # the oracle agrees with all of them on most tokens (bf16 against fp32)
+    ocfg = oracle.Qwen3Config(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=3,
+                              num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    ref = oracle.Qwen3Oracle(ocfg, w).greedy_generate(ids, 12, max_seq_len=256).astype(np.int64)
+    assert (want == ref).mean() >= 0.8
