@@ -174,7 +174,12 @@ class WhisperDecoderEngine:
         rows = y.shape[0] * y.shape[1]
         y2d = core.contiguous(y).view(rows, E) if not y.isContiguous() else y.view(rows, E)
         logits = core.empty((rows, self.V), "float32")
-        lib.call("kd_linear_bf16", _r(y2d), _r(dec.embed_tokens.weight), None, 0, _r(logits))
+        # the `matmul` key with transposeB (what `linear` issues): any vocabulary size (51865 is odd),
+        # fp32 result from bf16 operands
+        cfg = lib.kd_matmul_cfg()
+        cfg.M, cfg.N, cfg.K = rows, self.V, E
+        cfg.transpose_a, cfg.transpose_b, cfg.alpha, cfg.beta, cfg.has_c = 0, 1, 1.0, 0.0, 0
+        lib.call("kd_matmul", ctypes.byref(cfg), _r(y2d), _r(dec.embed_tokens.weight), None, _r(logits))
         out = logits.view(B, y.shape[1], self.V)
         for t in (y2d, y, x) + (() if xs is x else (xs,)):
             t.dispose()
