@@ -615,6 +615,9 @@ def extra_tp_4b(bn: Bench) -> dict:
     bn.be.synchronize()
     ms_prefill, ms_decode = p0.elapsed_ms(p1), p1.elapsed_ms(p2)
     rec = {}
+    decode_kernels = ("separate kernels with all-reduces after o_proj and down_proj" if not eng._decode["fused"] else
+                      "attention + one fused layer kernel per layer" if world == 1 else
+                      "attention + one fused layer kernel per layer; the partial sums of o_proj and down_proj cross NVLink inside that kernel")
     if world > 1:
         # the collectives alone, on the buffers the engine reduces: 2 per layer, 72 per forward
         part = eng._bufs(B, S)["part"]
@@ -631,22 +634,30 @@ def extra_tp_4b(bn: Bench) -> dict:
             eng._allreduce(d["o_p"])
             eng._norm(d["o_p"], lw0["post_norm"], d["x"], resid=d["h"], sum_out=d["h1"])
         ms_unfused = bn.timed_ms(unfused, reps=50, warm=5)
-        # the decode phase again with the library all-reduce (new graph)
-        eng.dispose()
+        # the decode phase again (new graphs): separate kernels with the one-shot all-reduce, then with
+        # the library all-reduce
+        def decode_again():
+            eng.dispose()
+            q0, q1 = CudaEvent(), CudaEvent()
+            tok = eng.prefill(ids)
+            eng.start_decode(tok, use_graph=True)
+            q0.record()
+            for _ in range(1, T):
+                eng.decode_step()
+            q1.record()
+            bn.be.synchronize()
+            bn.sync_all()
+            return q0.elapsed_ms(q1)
+        layer_kernel_in_use = bool(d["fused"])
+        eng.use_fused_layer = False
+        ms_decode_oneshot = decode_again()
         eng.use_p2p = False
-        q0, q1 = CudaEvent(), CudaEvent()
-        tok = eng.prefill(ids)
-        eng.start_decode(tok, use_graph=True)
-        q0.record()
-        for _ in range(1, T):
-            eng.decode_step()
-        q1.record()
-        bn.be.synchronize()
-        ms_decode_nccl = q0.elapsed_ms(q1)
+        ms_decode_nccl = decode_again()
         eng.use_p2p = True
+        eng.use_fused_layer = True
         bn.sync_all()
-        ms_ar_prefill, ms_ar_o, ms_ar_d, ms_fused, ms_unfused, ms_decode_nccl = bn.max_over_ranks(
-            [ms_ar_prefill, ms_ar_o, ms_ar_d, ms_fused, ms_unfused, ms_decode_nccl])
+        ms_ar_prefill, ms_ar_o, ms_ar_d, ms_fused, ms_unfused, ms_decode_nccl, ms_decode_oneshot = bn.max_over_ranks(
+            [ms_ar_prefill, ms_ar_o, ms_ar_d, ms_fused, ms_unfused, ms_decode_nccl, ms_decode_oneshot])
         nbytes = part.numel * 2
         rec["allreduce"] = {
             "library": "NCCL (ncclAllReduce on the library's stream)",
@@ -658,9 +669,16 @@ def extra_tp_4b(bn: Bench) -> dict:
             "decode_ms_per_step": (ms_ar_o + ms_ar_d) * L,
             "one_shot_peer_memory": {"kernel": "allreduce_add_rmsnorm_kernel (sum over ranks by peer loads + residual add + RMSNorm)",
                                      "us_per_call": ms_fused * 1e3, "replaces_us_per_call": ms_unfused * 1e3,
-                                     "in_use": bool(d["p2p"]), "decode_ms_per_step_with_library_allreduce": ms_decode_nccl / (T - 1)},
+                                     "in_use": bool(d["p2p"]) and not layer_kernel_in_use},
+            "decode_ms_per_step_by_variant": {
+                "layer_kernel_with_in_kernel_exchange": layer_kernel_in_use,      # replaced by the time below
+                "separate_kernels_one_shot_peer_memory": ms_decode_oneshot / (T - 1),
+                "separate_kernels_library_allreduce": ms_decode_nccl / (T - 1)},
         }
     ms, ms_prefill, ms_decode = bn.max_over_ranks([ms, ms_prefill, ms_decode])
+    if world > 1:
+        v = rec["allreduce"]["decode_ms_per_step_by_variant"]
+        v["layer_kernel_with_in_kernel_exchange"] = ms_decode / (T - 1) if v["layer_kernel_with_in_kernel_exchange"] else None
     per_layer_params = dims["hidden"] * ((dims["heads"] + 2 * dims["kv_heads"]) * dims["head_dim"]) + \
         dims["hidden"] * dims["heads"] * dims["head_dim"] + 3 * dims["hidden"] * dims["inter"]
     flops_prefill = B * S * (2.0 * per_layer_params * L) + 4.0 * B * dims["heads"] * dims["head_dim"] * (S * (S + 1) / 2) * L
@@ -672,8 +690,7 @@ def extra_tp_4b(bn: Bench) -> dict:
         "prefill_ms": ms_prefill, "decode_ms_per_step": ms_decode / (T - 1),
         "prefill_tflops_per_gpu": flops_prefill / world / (ms_prefill * 1e-3) / 1e12,
         "prefill_frac_of_tensor_peak": flops_prefill / world / (ms_prefill * 1e-3) / 1e12 / tc_peak,
-        "decode_kernels": ("attention + one fused layer kernel per layer" if eng.use_fused_layer else "fused per-layer chain kernel" if eng.use_chain
-                           else "separate kernels with all-reduces after o_proj and down_proj"),
+        "decode_kernels": decode_kernels,
     })
     eng.dispose()
     ids.dispose()

@@ -441,6 +441,20 @@ int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_
                           const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
                           const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
                           const kd_tensor* resid_out, const kd_tensor* x_final);
+/* The tensor-parallel form (no counterpart in the reference): every rank passes ITS slices (W_o and
+ * W_down: input columns; W_gate_up and W_qkv_next: rows; attn, caches and q_out: its heads) and the
+ * same residual; the partial sums of o_proj and down_proj are exchanged INSIDE the kernel, unit by
+ * unit, through the peer-mapped buffers of kd_p2p_connect (plain stores and loads, one flag per unit
+ * written into every peer's buffer, local polling, every wait bounded at about five seconds: error
+ * code 531) and summed in rank order, so every rank holds the same residual bit for bit.  All ranks
+ * must issue the same sequence of calls.  After an error 531 reconnect the peer buffers. */
+int kd_decode_layer_fused_tp(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
+                             const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
+                             const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
+                             const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
+                             const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
+                             const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
+                             const kd_tensor* resid_out, const kd_tensor* x_final);
 
 /* ---------------------------------------------------------------------------------------------
  * Tensor-parallel collectives (no counterpart in the reference, which is single-device).  One

@@ -42,6 +42,7 @@
 #include "chain_common.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
+#include "p2p_layout.cuh"
 #include "sm100.cuh"
 
 namespace kd {
@@ -105,6 +106,13 @@ struct DlParams {
   unsigned* counters;         // [8]: phases 0..2, [7] exit ticket
   int* err;
   unsigned long long* trace;  // optional [gridDim][16] nanosecond timestamps (kd_debug_decode_layer_trace)
+  // Tensor parallel (tp > 1): W_o and W_down hold this rank's input columns, so phases 0 and 2 give
+  // PARTIAL sums; each unit's epilogue exchanges them with the same unit on the other ranks through
+  // the peer-mapped buffers (plain stores / loads) before the residual add.
+  int tp, tp_rank;
+  char* peer[P2P_MAX_RANKS];
+  unsigned* tp_seq;           // [0] call counter (tags), advanced by the last CTA of each launch
+  long long tp_wait;
 };
 
 struct DlMaps {
@@ -364,6 +372,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     int acc_n = 0;
     bool ok = true;
     pdl_wait();      // residual, position, tables: produced by earlier kernels
+    const unsigned tp_tag = p.tp > 1 ? p.tp_seq[0] + 1u : 0u;     // this launch's tag on the exchange flags
     // Control flow between the 128-thread barriers below never depends on per-thread state: `ok`
     // is made uniform (a barrier that ORs the threads' flags) before it decides anything.
     for (int gi = 0; gi < n_gemms; ++gi) {
@@ -403,10 +412,72 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           __nv_bfloat16* x_out = gi == 0 ? p.x1 : p.x2;
           const __nv_bfloat16* wn = gi == 0 ? p.w_post : p.w_next;
           float ss = 0.f;
+          const float* xch[P2P_MAX_RANKS];      // tensor parallel: every rank's partial sums of this phase
+          if (p.tp > 1) {
+            // ---- exchange with the same unit on the other ranks.  Pass A: this rank's partial sums into
+            // its own slot of the exchange buffer, then one flag per (phase, unit) into EVERY rank's
+            // buffer; wait on the LOCAL flags (bounded); pass B below sums the ranks in rank order.
+            const size_t slot_off = P2P_LAYER_SLOT_OFFSET + (gi == 0 ? 0 : P2P_SLOT_BYTES);
+#pragma unroll
+            for (int r = 0; r < P2P_MAX_RANKS; ++r) xch[r] = reinterpret_cast<const float*>(p.peer[r < p.tp ? r : 0] + slot_off);
+            float* mine = reinterpret_cast<float*>(p.peer[p.tp_rank] + slot_off);
+            for (int c0 = 0; c0 < g.n_unit; c0 += 16) {
+              float r[16];
+              dl_acc16(t_acc + c0, two, r);
+              if (valid && n0 + c0 < g.N) {
+                float4* o = reinterpret_cast<float4*>(mine + (int64_t)m * p.H + n0 + c0);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+              }
+            }
+            epi_bar_sync();
+            const int t = (int)(threadIdx.x & 127);
+            bool failed = false;
+            if (t < p.tp) {
+              const size_t fidx = ((size_t)(gi == 0 ? 0 : 1) * P2P_MAX_ROWS + u) * P2P_MAX_RANKS;
+              __threadfence_system();
+              st_release_sys(reinterpret_cast<unsigned*>(p.peer[t] + P2P_LAYER_FLAG_OFFSET) + fidx + p.tp_rank, tp_tag);
+              const unsigned* f = reinterpret_cast<const unsigned*>(p.peer[p.tp_rank] + P2P_LAYER_FLAG_OFFSET) + fidx + t;
+              const long long t0 = clock64();
+              int spins = 0;
+              while (ld_acquire_sys(f) != tp_tag) {
+                if (((++spins) & 7) == 0 && (*abort_flag || clock64() - t0 > p.tp_wait)) {
+                  failed = true;
+                  *abort_flag = 1;
+                  if (atomicCAS(p.err, 0, 531) == 0) { p.err[1] = u; p.err[2] = t; p.err[3] = gi; }
+                  break;
+                }
+              }
+            }
+            if (epi_bar_any(failed)) {
+              // a peer's partial sums never came: give the accumulator back and stop working on units
+              ok = false;
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[buf]);
+              ++acc_n;
+              continue;
+            }
+          }
           // one 16-column chunk: add the accumulator to the residual, store h and bf16(h * w)
           auto chunk = [&](int c0, float (&a)[16]) {
             float r[16];
-            dl_acc16(t_acc + c0, two, r);
+            if (p.tp > 1) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) r[i] = 0.f;
+              if (valid && n0 + c0 < g.N) {
+                for (int rk = 0; rk < p.tp; ++rk) {      // rank order: the same bits on every rank
+                  const float4* src = reinterpret_cast<const float4*>(xch[rk] + (int64_t)m * p.H + n0 + c0);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float4 v4 = ld_peer_f4(src + i);
+                    r[4 * i] += v4.x; r[4 * i + 1] += v4.y; r[4 * i + 2] += v4.z; r[4 * i + 3] += v4.w;
+                  }
+                }
+              }
+            } else {
+              dl_acc16(t_acc + c0, two, r);
+            }
             if (valid && n0 + c0 < g.N) {
               float w[16];
               ld_bf16x16(wn + n0 + c0, w);
@@ -550,6 +621,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     const unsigned ticket = atomicAdd(p.counters + 7, 1u);
     if (ticket == (unsigned)G - 1) {
       for (int i = 0; i < DL_COUNTERS; ++i) p.counters[i] = 0u;
+      if (p.tp > 1) p.tp_seq[0] += 1u;       // every CTA has read this launch's tag long ago
       __threadfence();
     }
   }
@@ -630,13 +702,13 @@ KD_API int kd_debug_decode_layer_trace(uint64_t* out, int max_entries) {
   return KD_OK;
 }
 
-KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
-                                 const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
-                                 const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
-                                 const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
-                                 const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
-                                 const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
-                                 const kd_tensor* resid_out, const kd_tensor* x_final) {
+static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
+                              const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
+                              const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
+                              const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
+                              const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
+                              const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
+                              const kd_tensor* resid_out, const kd_tensor* x_final) {
   KD_TRY(require_init());
   KD_REQUIRE(attn && w_o && resid_in && post_norm_w && w_gate_up && w_down && next_norm_w && resid_out, "null tensor");
   KD_REQUIRE(attn->ndim == 2 && w_o->ndim == 2 && w_gate_up->ndim == 2 && w_down->ndim == 2, "operands must be 2-D");
@@ -743,7 +815,26 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
       if (e && atoi(e) >= ops[i].step && atoi(e) <= 128 && atoi(e) % ops[i].step == 0) g.n_unit = atoi(e);
     }
     g.units = (g.N + g.n_unit - 1) / g.n_unit;
+    if (tensor_parallel && (i == 0 || i == 2)) {
+      // one exchange flag per unit: at most P2P_MAX_ROWS units in the phases that exchange partial sums
+      while (g.n_unit < 128 && (g.N + g.n_unit - 1) / g.n_unit > P2P_MAX_ROWS) g.n_unit += ops[i].step;
+      g.units = (g.N + g.n_unit - 1) / g.n_unit;
+      KD_REQUIRE(g.units <= P2P_MAX_ROWS, "hidden size %d needs %d exchange units (at most %d)", g.N, g.units, P2P_MAX_ROWS);
+    }
     KD_REQUIRE(g.units <= DL_MAX_UNITS, "%d units in phase %d (at most %d)", g.units, i, DL_MAX_UNITS);
+  }
+  if (tensor_parallel) {
+    P2pPeers peers;
+    KD_TRY(p2p_peers(&peers));
+    KD_REQUIRE((size_t)Mb * H * sizeof(float) <= P2P_SLOT_BYTES, "%lld x %lld fp32 partial sums do not fit the %zu-byte exchange slot",
+               (long long)Mb, (long long)H, P2P_SLOT_BYTES);
+    p.tp = peers.nranks;
+    p.tp_rank = peers.rank;
+    for (int r = 0; r < P2P_MAX_RANKS; ++r) p.peer[r] = peers.buf[r];
+    p.tp_seq = peers.layer_seq;
+    p.tp_wait = P2P_WAIT_CYCLES;
+  } else {
+    p.tp = 1;
   }
   // scratch: h1, x1, x2, act, per-unit sums of squares
   size_t bytes = ((size_t)Mb * H + (size_t)(p.g[0].units + p.g[2].units) * Mb) * sizeof(float) +
@@ -827,4 +918,26 @@ KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, co
   }
   KD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, decode_layer_kernel, maps, p));
   return after_launch("decode_layer_kernel");
+}
+
+KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
+                                 const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
+                                 const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
+                                 const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
+                                 const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
+                                 const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
+                                 const kd_tensor* resid_out, const kd_tensor* x_final) {
+  return decode_layer_fused(false, attn, w_o, resid_in, post_norm_w, w_gate_up, w_down, next_norm_w, eps, w_qkv_next, q_norm_w, k_norm_w,
+                            cos, sin, pos, k_cache_next, v_cache_next, block_table, q_out, resid_out, x_final);
+}
+
+KD_API int kd_decode_layer_fused_tp(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
+                                    const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
+                                    const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,
+                                    const kd_tensor* q_norm_w, const kd_tensor* k_norm_w, const kd_tensor* cos,
+                                    const kd_tensor* sin, const kd_tensor* pos, const kd_tensor* k_cache_next,
+                                    const kd_tensor* v_cache_next, const kd_tensor* block_table, const kd_tensor* q_out,
+                                    const kd_tensor* resid_out, const kd_tensor* x_final) {
+  return decode_layer_fused(true, attn, w_o, resid_in, post_norm_w, w_gate_up, w_down, next_norm_w, eps, w_qkv_next, q_norm_w, k_norm_w,
+                            cos, sin, pos, k_cache_next, v_cache_next, block_table, q_out, resid_out, x_final);
 }

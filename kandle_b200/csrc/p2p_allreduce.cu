@@ -29,15 +29,10 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "p2p_layout.cuh"
 
 namespace kd {
 
-constexpr int P2P_MAX_RANKS = 8;
-constexpr int P2P_MAX_ROWS = 128;
-constexpr size_t P2P_SLOT_BYTES = 2u << 20;                 // per data slot: rows * hidden * 4 bytes must fit
-constexpr size_t P2P_FLAG_OFFSET = 2 * P2P_SLOT_BYTES;
-constexpr size_t P2P_BUF_BYTES = P2P_FLAG_OFFSET + 2 * P2P_MAX_ROWS * P2P_MAX_RANKS * sizeof(unsigned);
-constexpr long long P2P_WAIT_CYCLES = 10000000000LL;        // about five seconds: ranks are separate processes
 constexpr int P2P_THREADS = 128;
 constexpr int P2P_MAXV = 8;                                 // 8-element vectors per thread: rows up to 8192 wide
 
@@ -48,9 +43,19 @@ struct P2pState {
   void* local[P2P_MAX_RANKS] = {nullptr}; // buffers this process allocated (1, or `emulate`)
   void* peer[P2P_MAX_RANKS] = {nullptr};  // address of every rank's buffer as seen from here
   bool opened[P2P_MAX_RANKS] = {false};
-  unsigned* seq = nullptr;                // [P2P_MAX_RANKS] call counters (one per emulated rank), [8] completion tickets
+  unsigned* seq = nullptr;                // [P2P_MAX_RANKS] call counters (one per emulated rank), [8] completion tickets,
+                                          // [16] call counter of the layer kernel, [17] its completion ticket
 };
 static P2pState g_p2p;
+
+int p2p_peers(P2pPeers* out) {
+  if (!g_p2p.ready || g_p2p.emulate) return fail(KD_ERR_INVALID, "peer buffers are not connected (kd_p2p_prepare + kd_p2p_connect)");
+  for (int r = 0; r < P2P_MAX_RANKS; ++r) out->buf[r] = static_cast<char*>(g_p2p.peer[r]);
+  out->nranks = g_p2p.nranks;
+  out->rank = g_p2p.rank;
+  out->layer_seq = g_p2p.seq + 2 * P2P_MAX_RANKS;
+  return KD_OK;
+}
 
 struct P2pArgs {
   char* buf[P2P_MAX_RANKS];
@@ -69,20 +74,6 @@ struct P2pArgs {
   int64_t out_rank_stride;
   int* err;
 };
-
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 ld_peer_f4(const float4* p) {
-  float4 v;
-  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-  return v;
-}
 
 __global__ void __launch_bounds__(P2P_THREADS) allreduce_add_rmsnorm_kernel(const P2pArgs a) {
   __shared__ float red[P2P_THREADS / 32];
@@ -201,8 +192,8 @@ static int p2p_alloc_local(int count) {
     KD_CUDA_CHECK(cudaMemsetAsync(g_p2p.local[i], 0, P2P_BUF_BYTES, ctx().stream));
   }
   if (!g_p2p.seq) {
-    KD_CUDA_CHECK(cudaMalloc(&g_p2p.seq, 2 * P2P_MAX_RANKS * sizeof(unsigned)));
-    KD_CUDA_CHECK(cudaMemsetAsync(g_p2p.seq, 0, 2 * P2P_MAX_RANKS * sizeof(unsigned), ctx().stream));
+    KD_CUDA_CHECK(cudaMalloc(&g_p2p.seq, (2 * P2P_MAX_RANKS + 2) * sizeof(unsigned)));
+    KD_CUDA_CHECK(cudaMemsetAsync(g_p2p.seq, 0, (2 * P2P_MAX_RANKS + 2) * sizeof(unsigned), ctx().stream));
   }
   KD_CUDA_CHECK(cudaStreamSynchronize(ctx().stream));
   return KD_OK;

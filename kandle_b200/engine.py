@@ -135,7 +135,9 @@ class Qwen3Engine:
         self.use_chain = self.tp == 1 and self.H <= 4096
         # ... and further, through the next layer's q/k-norm + RoPE + cache write, in four phases
         # (kd_decode_layer_fused): two launches per layer and decode step
-        self.use_fused_layer = self.tp == 1 and self.D == 128 and self.H <= 8192
+        # (tensor parallel: the form of that kernel that exchanges the partial sums of o_proj and down_proj
+        # with its peers inside the kernel, when the peer buffers are connected)
+        self.use_fused_layer = self.D == 128 and self.H <= 8192
         # tensor parallel decode: sum the partial outputs over ranks through mapped peer memory when
         # the host program has connected the peer buffers (parallel.init_peer_buffers), else NCCL
         self.use_p2p = True
@@ -355,9 +357,12 @@ class Qwen3Engine:
             s = ctypes.c_int(0)
             lib.call("kd_decode_layer_chain_splits", ctypes.c_int64(n), ctypes.c_int64(k), ctypes.byref(s))
             return s.value
+        p2p = self.tp > 1 and self.use_p2p and parallel.peer_buffers_ready()
         d = {
-            "B": B, "graph": None, "chain": self.use_chain, "fused": self.use_fused_layer,
-            "p2p": self.tp > 1 and self.use_p2p and parallel.peer_buffers_ready(),
+            "B": B, "graph": None, "chain": self.use_chain,
+            # (tensor parallel: fp32 partial sums of all sequences must fit one 2 MiB exchange slot)
+            "fused": self.use_fused_layer and (self.tp == 1 or (p2p and B * self.H * 4 <= (2 << 20))),
+            "p2p": p2p,
             "scalars": core.zeros((2,), "int32"),           # [write position, context length]
             "ids": core.zeros((B,), "int64"), "emb": e(B, self.H), "h": f(B, self.H), "h1": f(B, self.H), "x": e(B, self.H),
             # a projection whose suggested split factor is 1 writes bf16 directly, otherwise fp32 partials
@@ -421,16 +426,17 @@ class Qwen3Engine:
                 lib.call("kd_attention_decode", _r(q_bh1d), _r(kc), _r(vc), _r(d["ctx"]), 0, ctypes.c_float(self.scale), 0, _r(o_bh1d))
             nxt = self.layers[li + 1]["in_norm"] if li + 1 < self.L else self.final_norm
             if d["fused"]:
+                layer_fn = "kd_decode_layer_fused_tp" if self.tp > 1 else "kd_decode_layer_fused"
                 if li + 1 < self.L:
                     nl = self.layers[li + 1]
                     kn, vn = cache_of(li + 1)
-                    lib.call("kd_decode_layer_fused", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
+                    lib.call(layer_fn, _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
                              _r(lw["wdown"]), _r(nxt), eps, _r(nl["wqkv"]), _r(nl["q_norm"]), _r(nl["k_norm"]), _r(d["cos"]),
                              _r(d["sin"]), _r(d["pos"]), _r(kn), _r(vn), _r(table), _r(d["q"]), _r(h), None)
                     kn.dispose()
                     vn.dispose()
                 else:
-                    lib.call("kd_decode_layer_fused", _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
+                    lib.call(layer_fn, _r(attn2d), _r(lw["wo"]), _r(h), _r(lw["post_norm"]), _r(lw["wgu"]),
                              _r(lw["wdown"]), _r(nxt), eps, None, None, None, None, None, None, None, None, None, None, _r(h), _r(d["x"]))
                 kc.dispose()
                 vc.dispose()

@@ -59,11 +59,15 @@ def main():
     ids = synth.token_ids("tp.ids", (2, prompt), V)
     tok, logits = eng.prefill(ids, all_logits=True)
     got = logits.dataAsync()
-    toks = eng.generate(ids, 6, use_graph=True)                 # decode sums over ranks through peer memory
+    toks = eng.generate(ids, 6, use_graph=True)                 # layer kernel that exchanges partial sums with its peers
+    layer_kernel_ran = bool(eng._decode["fused"])
     toks_eager = eng.generate(ids, 6, use_graph=False)
+    eng.use_fused_layer = False
+    toks_oneshot = eng.generate(ids, 6, use_graph=True)         # separate kernels, one-shot all-reduce through peer memory
     eng.use_p2p = False
     toks_nccl = eng.generate(ids, 6, use_graph=True)            # the same steps with the library all-reduce
     eng.use_p2p = True
+    eng.use_fused_layer = True
     lib.call("kd_comm_check")
     # every rank must hold the same result
     t = torch.tensor(toks, device="cuda")
@@ -83,11 +87,15 @@ def main():
         ref_t = om.greedy_generate(ids, 6).astype(np.int64)
         tol = max(1.0, float(np.abs(ref).max()) / 3.0)      # the bf16 bound is relative to the logits' range (|3| at the 0.6B widths)
         # (the prefill partial sums of o_proj / down_proj are rounded to bf16 before the all-reduce: one more rounding than on one GPU)
+        # each doubling of the ranks adds one more bf16 rounding level to those sums: the bound widens by an eighth per doubling
+        tol *= 1.0 + 0.125 * np.log2(world)
         ok = (np.quantile(err, 0.999) <= 2e-2 * tol and err.max() <= 3.5e-2 * tol and same_across_ranks and np.array_equal(toks, toks_eager)
-              and (toks == ref_t).mean() >= 0.8 and (toks_nccl == ref_t).mean() >= 0.8)
-        msg = (f"TP{world}: logits max err {err.max():.3e} p99.9 {np.quantile(err, 0.999):.3e}; tokens equal across ranks "
+              and (toks == ref_t).mean() >= 0.8 and (toks_nccl == ref_t).mean() >= 0.8 and (toks_oneshot == ref_t).mean() >= 0.8
+              and layer_kernel_ran)
+        msg = (f"TP{world}: logits max err {err.max():.3e} p99.9 {np.quantile(err, 0.999):.3e} (bounds {3.5e-2 * tol:.3e} / {2e-2 * tol:.3e}); tokens equal across ranks "
                f"{same_across_ranks}; graph==eager {np.array_equal(toks, toks_eager)}; token agreement with oracle {(toks == ref_t).mean():.2f}; "
-               f"peer-memory vs NCCL decode tokens equal {(toks == toks_nccl).mean():.2f}")
+               f"layer kernel ran {layer_kernel_ran}; decode tokens equal to the library all-reduce's: layer kernel "
+               f"{(toks == toks_nccl).mean():.2f}, one-shot {(toks_oneshot == toks_nccl).mean():.2f}")
         print(msg, flush=True)
     eng.dispose()
     # weights drawn on the device: every rank draws its own slice of the same full model
