@@ -495,7 +495,16 @@ int kd_comm_destroy(void);
  *                      possible (the call counter lives in device memory).
  *   kd_p2p_selftest_dropped_flag
  *                      emulated ranks only: rank `drop_rank` never publishes its flags, the others'
- *                      waits run out after `wait_cycles` clock cycles; used to test the error path. */
+ *                      waits run out after `wait_cycles` clock cycles; used to test the error path.
+ *   kd_p2p_selftest_silent_peers
+ *                      connects this process as rank 0 of `nranks` whose other ranks are buffers on
+ *                      this GPU that nobody writes: kd_decode_layer_fused_tp then publishes its
+ *                      partial sums, waits `wait_cycles` clock cycles for peers that never answer
+ *                      and reports error 531; used to test that error path without a second GPU
+ *                      and without a hang.  With answered_tag = t the stand-ins' flags already
+ *                      carry the tag of launch number t (launches count from 1) and their partial
+ *                      sums are zero: that launch completes and must give the result of
+ *                      kd_decode_layer_fused.  kd_p2p_disconnect ends it. */
 int kd_p2p_prepare(char* handle_out, size_t handle_bytes);
 int kd_p2p_connect(int nranks, int rank, const char* handles, size_t handle_bytes);
 int kd_p2p_emulate(int nranks);
@@ -503,6 +512,7 @@ int kd_p2p_info(int* ready, int* nranks, int* rank);
 int kd_p2p_disconnect(void);
 int kd_allreduce_add_rmsnorm(const kd_tensor* x, const kd_tensor* residual, const kd_tensor* weight, float eps,
                              const kd_tensor* sum_out, const kd_tensor* norm_out);
+int kd_p2p_selftest_silent_peers(int nranks, uint32_t wait_cycles, uint32_t answered_tag);
 int kd_p2p_selftest_dropped_flag(const kd_tensor* x, const kd_tensor* weight, const kd_tensor* norm_out, int drop_rank,
                                  uint32_t wait_cycles);
 

@@ -396,7 +396,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
         // while the MMAs run (the first 16 columns; the later ones are loaded in the loop below, where
         // their latency hides behind the work on the columns before them)
         float pre_r[16];
-        if ((gi == 0 || gi == 2) && valid && n0 < g.N)
+        if ((gi == 0 || gi == 2) && valid && n0 < g.N && p.tp == 1)
           ld_f32x16((gi == 0 ? p.resid_in : p.resid_mid) + (int64_t)m * p.H + n0, pre_r);
         if (ok) ok = mbar_wait(&acc_full[buf], (uint32_t)(use & 1), abort_flag, p.err, 527);
         if (epi_bar_any(!ok || *abort_flag != 0)) ok = false;   // one answer for all 128 threads
@@ -412,14 +412,11 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           __nv_bfloat16* x_out = gi == 0 ? p.x1 : p.x2;
           const __nv_bfloat16* wn = gi == 0 ? p.w_post : p.w_next;
           float ss = 0.f;
-          const float* xch[P2P_MAX_RANKS];      // tensor parallel: every rank's partial sums of this phase
           if (p.tp > 1) {
             // ---- exchange with the same unit on the other ranks.  Pass A: this rank's partial sums into
             // its own slot of the exchange buffer, then one flag per (phase, unit) into EVERY rank's
-            // buffer; wait on the LOCAL flags (bounded); pass B below sums the ranks in rank order.
+            // buffer; wait on the LOCAL flags (bounded).
             const size_t slot_off = P2P_LAYER_SLOT_OFFSET + (gi == 0 ? 0 : P2P_SLOT_BYTES);
-#pragma unroll
-            for (int r = 0; r < P2P_MAX_RANKS; ++r) xch[r] = reinterpret_cast<const float*>(p.peer[r < p.tp ? r : 0] + slot_off);
             float* mine = reinterpret_cast<float*>(p.peer[p.tp_rank] + slot_off);
             for (int c0 = 0; c0 < g.n_unit; c0 += 16) {
               float r[16];
@@ -430,6 +427,11 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
                 for (int i = 0; i < 4; ++i) o[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
               }
             }
+            // the accumulator is read: the MMA warps may start this CTA's next unit during the exchange
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            ++acc_n;
             epi_bar_sync();
             const int t = (int)(threadIdx.x & 127);
             bool failed = false;
@@ -449,35 +451,60 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
                 }
               }
             }
-            if (epi_bar_any(failed)) {
-              // a peer's partial sums never came: give the accumulator back and stop working on units
+            if (epi_bar_any(failed)) {      // a peer's partial sums never came: stop working on units
               ok = false;
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&acc_empty[buf]);
-              ++acc_n;
               continue;
             }
+            // Pass B, flat over the unit's [sequences x n_unit] block so that every thread has work and all
+            // peer loads of a thread are in flight together (a peer load is a round trip over NVLink):
+            // item i = four columns of one sequence; sum over ranks in rank order (the same bits on every
+            // rank), residual add, h and bf16(h * w) stores; the row's share of sum(h^2) is reduced over
+            // the adjacent lanes that hold the row (n_unit is a power of two here).
+            const int vpr = g.n_unit >> 2;              // items per sequence: 4, 8, 16 or 32
+            const int items = p.Mb * vpr;
+            for (int i0 = 0; i0 < items; i0 += 128) {
+              const int i = i0 + t;
+              const int row = i / vpr, col = n0 + (i % vpr) * 4;
+              const bool inb = i < items && col < g.N;
+              float part = 0.f;
+              if (inb) {
+                const int64_t off = (int64_t)row * p.H + col;
+                float4 v[P2P_MAX_RANKS];
+#pragma unroll
+                for (int rk = 0; rk < P2P_MAX_RANKS; ++rk)
+                  if (rk < p.tp) v[rk] = ld_peer_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.peer[rk] + slot_off) + off));
+                float4 a = __ldcg(reinterpret_cast<const float4*>(resid + off));
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int rk = 0; rk < P2P_MAX_RANKS; ++rk)
+                  if (rk < p.tp) { sum.x += v[rk].x; sum.y += v[rk].y; sum.z += v[rk].z; sum.w += v[rk].w; }
+                a.x += sum.x; a.y += sum.y; a.z += sum.z; a.w += sum.w;
+                part = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                *reinterpret_cast<float4*>(h_out + off) = a;
+                const uint2 wraw = *reinterpret_cast<const uint2*>(wn + col);
+                const __nv_bfloat16* wh = reinterpret_cast<const __nv_bfloat16*>(&wraw);
+                uint2 xo;
+                __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(&xo);
+                xh[0] = __float2bfloat16_rn(a.x * __bfloat162float(wh[0]));
+                xh[1] = __float2bfloat16_rn(a.y * __bfloat162float(wh[1]));
+                xh[2] = __float2bfloat16_rn(a.z * __bfloat162float(wh[2]));
+                xh[3] = __float2bfloat16_rn(a.w * __bfloat162float(wh[3]));
+                *reinterpret_cast<uint2*>(x_out + off) = xo;
+              }
+              for (int o = vpr >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+              if (inb && (i % vpr) == 0) (gi == 0 ? p.ssq1 : p.ssq2)[u * p.Mb + row] = part;
+            }
+            epi_bar_sync();
+            if (t == 0 && *abort_flag == 0) {
+              red_release_add(p.counters + gi, 1u);
+              DL_TRACE(3 + 3 * gi);
+            }
+            continue;
           }
           // one 16-column chunk: add the accumulator to the residual, store h and bf16(h * w)
           auto chunk = [&](int c0, float (&a)[16]) {
             float r[16];
-            if (p.tp > 1) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) r[i] = 0.f;
-              if (valid && n0 + c0 < g.N) {
-                for (int rk = 0; rk < p.tp; ++rk) {      // rank order: the same bits on every rank
-                  const float4* src = reinterpret_cast<const float4*>(xch[rk] + (int64_t)m * p.H + n0 + c0);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    const float4 v4 = ld_peer_f4(src + i);
-                    r[4 * i] += v4.x; r[4 * i + 1] += v4.y; r[4 * i + 2] += v4.z; r[4 * i + 3] += v4.w;
-                  }
-                }
-              }
-            } else {
-              dl_acc16(t_acc + c0, two, r);
-            }
+            dl_acc16(t_acc + c0, two, r);
             if (valid && n0 + c0 < g.N) {
               float w[16];
               ld_bf16x16(wn + n0 + c0, w);
@@ -817,7 +844,11 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
     g.units = (g.N + g.n_unit - 1) / g.n_unit;
     if (tensor_parallel && (i == 0 || i == 2)) {
       // one exchange flag per unit: at most P2P_MAX_ROWS units in the phases that exchange partial sums
-      while (g.n_unit < 128 && (g.N + g.n_unit - 1) / g.n_unit > P2P_MAX_ROWS) g.n_unit += ops[i].step;
+      // (widths are powers of two there: the epilogue reduces a row's sum of squares over adjacent lanes)
+      int w2 = 16;
+      while (w2 < g.n_unit) w2 *= 2;
+      g.n_unit = w2 > 128 ? 128 : w2;
+      while (g.n_unit < 128 && (g.N + g.n_unit - 1) / g.n_unit > P2P_MAX_ROWS) g.n_unit *= 2;
       g.units = (g.N + g.n_unit - 1) / g.n_unit;
       KD_REQUIRE(g.units <= P2P_MAX_ROWS, "hidden size %d needs %d exchange units (at most %d)", g.N, g.units, P2P_MAX_ROWS);
     }
@@ -832,7 +863,7 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
     p.tp_rank = peers.rank;
     for (int r = 0; r < P2P_MAX_RANKS; ++r) p.peer[r] = peers.buf[r];
     p.tp_seq = peers.layer_seq;
-    p.tp_wait = P2P_WAIT_CYCLES;
+    p.tp_wait = peers.wait_cycles;
   } else {
     p.tp = 1;
   }

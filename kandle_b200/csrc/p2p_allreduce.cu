@@ -40,6 +40,7 @@ struct P2pState {
   bool ready = false;
   int nranks = 1, rank = 0;
   int emulate = 0;                        // > 0: that many ranks emulated on this GPU
+  long long silent_wait = 0;              // > 0: the peers are local stand-ins that never answer (self-test); the wait bound to use
   void* local[P2P_MAX_RANKS] = {nullptr}; // buffers this process allocated (1, or `emulate`)
   void* peer[P2P_MAX_RANKS] = {nullptr};  // address of every rank's buffer as seen from here
   bool opened[P2P_MAX_RANKS] = {false};
@@ -54,6 +55,7 @@ int p2p_peers(P2pPeers* out) {
   out->nranks = g_p2p.nranks;
   out->rank = g_p2p.rank;
   out->layer_seq = g_p2p.seq + 2 * P2P_MAX_RANKS;
+  out->wait_cycles = g_p2p.silent_wait > 0 ? g_p2p.silent_wait : P2P_WAIT_CYCLES;
   return KD_OK;
 }
 
@@ -258,6 +260,31 @@ KD_API int kd_p2p_emulate(int nranks) {
   g_p2p.nranks = nranks;
   g_p2p.rank = 0;
   g_p2p.emulate = nranks;
+  g_p2p.ready = true;
+  return KD_OK;
+}
+
+KD_API int kd_p2p_selftest_silent_peers(int nranks, uint32_t wait_cycles, uint32_t answered_tag) {
+  KD_TRY(require_init());
+  KD_REQUIRE(nranks >= 2 && nranks <= P2P_MAX_RANKS, "2..%d ranks", P2P_MAX_RANKS);
+  KD_REQUIRE(wait_cycles > 0, "wait_cycles must be positive");
+  KD_REQUIRE(!g_p2p.ready, "peer buffers are already connected");
+  KD_TRY(p2p_alloc_local(nranks));
+  for (int r = 0; r < nranks; ++r) g_p2p.peer[r] = g_p2p.local[r];
+  g_p2p.nranks = nranks;
+  g_p2p.rank = 0;
+  g_p2p.emulate = 0;
+  g_p2p.silent_wait = (long long)wait_cycles;
+  if (answered_tag) {
+    // the stand-ins "answered" the launch with this tag: their flags in this rank's buffer carry it,
+    // their partial sums are the zeros the buffers were cleared to
+    std::vector<unsigned> flags(2 * P2P_MAX_ROWS * P2P_MAX_RANKS, 0u);
+    for (size_t i = 0; i < flags.size(); ++i)
+      if ((int)(i % P2P_MAX_RANKS) >= 1 && (int)(i % P2P_MAX_RANKS) < nranks) flags[i] = answered_tag;
+    KD_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(g_p2p.local[0]) + P2P_LAYER_FLAG_OFFSET, flags.data(), flags.size() * sizeof(unsigned),
+                                  cudaMemcpyHostToDevice, ctx().stream));
+    KD_CUDA_CHECK(cudaStreamSynchronize(ctx().stream));
+  }
   g_p2p.ready = true;
   return KD_OK;
 }

@@ -36,8 +36,10 @@ struct P2pPeers {
   char* buf[P2P_MAX_RANKS];
   int nranks, rank;
   unsigned* layer_seq;      // device call counter of the layer kernel (+1: its completion ticket)
+  long long wait_cycles;    // bound of every wait on a peer's flag
 };
-// KD_OK and *out filled when peer buffers are connected across processes (not in emulation mode).
+// KD_OK and *out filled when peer buffers are connected across processes, or to silent stand-ins
+// (kd_p2p_selftest_silent_peers); not in emulation mode.
 int p2p_peers(P2pPeers* out);
 
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {

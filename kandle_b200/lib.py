@@ -173,6 +173,7 @@ _SIGNATURES = {
     "kd_p2p_disconnect": [],
     "kd_allreduce_add_rmsnorm": [_T, _T, _T, ctypes.c_float, _T, _T],
     "kd_p2p_selftest_dropped_flag": [_T, _T, _T, ctypes.c_int, ctypes.c_uint32],
+    "kd_p2p_selftest_silent_peers": [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32],
     "kd_attention_decode": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_noalloc": [_T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],
     "kd_attention_decode_paged": [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_float, ctypes.c_int, _T],

@@ -56,7 +56,7 @@ def _oracle(oracle, c, eps):
     return h1, act, h2, x2, (rope(q), rope(k), qkv[:, hq + hkv:])
 
 
-def _run(c, eps, alias=False):
+def _run(c, eps, alias=False, entry="kd_decode_layer_fused"):
     mb, Ko = c["attn"].shape
     H, I = c["wo"].shape[0], c["wg"].shape[0]
     bf = lambda a: Tensor(a, dtype="bfloat16")  # noqa: E731
@@ -78,7 +78,7 @@ def _run(c, eps, alias=False):
         args = [t["wq"], t["qw"], t["kw"], t["cos"], t["sin"], t["pos"], t["kc"], t["vc"], None, t["q"]]
     else:
         xf = t["xf"] = core.empty((mb, H), "bfloat16")
-    t["call"] = lambda: lib.call("kd_decode_layer_fused", _r(t["attn"]), _r(t["wo"]), _r(t["h"]), _r(t["post"]), _r(t["wgu"]),
+    t["call"] = lambda: lib.call(entry, _r(t["attn"]), _r(t["wo"]), _r(t["h"]), _r(t["post"]), _r(t["wgu"]),
                                  _r(t["wd"]), _r(t["next"]), ctypes.c_float(eps), *[_r(a) for a in args], _r(t["h2"]), _r(xf))
     t["call"]()
     return t
@@ -166,3 +166,33 @@ def test_fused_layer_reports_a_cache_row_outside_the_cache_and_checks_arguments(
     with pytest.raises(lib.KandleCudaError):                          # last-layer form without x_final
         lib.call("kd_decode_layer_fused", _r(t["attn"]), _r(t["wo"]), _r(t["h"]), _r(t["post"]), _r(t["wgu"]), _r(t["wd"]),
                  _r(t["next"]), ctypes.c_float(eps), None, None, None, None, None, None, None, None, None, None, _r(t["h2"]), None)
+
+
+def test_tensor_parallel_form_with_stand_in_peers_matches_the_plain_kernel_then_times_out(backend, oracle):
+    """One GPU: this process is rank 0 of 4 whose peers are local buffers.  Launch 1 finds their
+    flags set and their partial sums zero, so it must give what the plain kernel gives (up to the
+    order in which a sequence's sum of squares is added up: that epilogue is organised differently); launch 2
+    waits for peers that never answer, gives up after its bound (error 531) and leaves the
+    context usable."""
+    eps, mb, H, Ko, I, hq, hkv = 1e-6, 8, 2560, 2048, 2432, 8, 2        # one rank's share of the Qwen3-4B layer on 4 GPUs
+    c = _case(mb, H, Ko, I, hq, hkv, "tp")
+    plain = _run(c, eps)
+    backend.synchronize()
+    want = {k: plain[k].dataAsync().copy() for k in ("h2", "q", "kc", "vc")}
+    lib.call("kd_p2p_selftest_silent_peers", 4, ctypes.c_uint32(20_000_000), ctypes.c_uint32(1))
+    try:
+        t = _run(c, eps, entry="kd_decode_layer_fused_tp")
+        backend.synchronize()
+        for k, v in want.items():
+            _close(t[k].dataAsync(), v, 1e-3, f"{k} (tensor-parallel form against the plain kernel)")
+        t["call"]()                                                    # tag 2: nobody answers
+        with pytest.raises(lib.KandleCudaError) as e:
+            backend.synchronize()
+        assert e.value.status == 6 and "531" in str(e.value)
+    finally:
+        lib.call("kd_p2p_disconnect")
+    again = _run(c, eps)                                               # the context and the kernel still work
+    backend.synchronize()
+    assert np.array_equal(again["h2"].dataAsync(), want["h2"])
+    with pytest.raises(lib.KandleCudaError):                           # no peers connected
+        _run(c, eps, entry="kd_decode_layer_fused_tp")
