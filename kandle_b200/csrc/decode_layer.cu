@@ -64,13 +64,19 @@ constexpr int DL_THREADS = 224;                 // warp 0 producer, warps 1 and 
 constexpr int DL_X_AREA = 16 * 1024, DL_W_AREA = 32 * 1024, DL_SLOT = DL_X_AREA + DL_W_AREA, DL_STAGES = 4;
 constexpr int DL_MAX_UNITS = 512;               // units of a phase that publish sums of squares
 constexpr int DL_COUNTERS = 8;
+// K split inside a thread-block cluster: the CTAs of a group (2 or 4 neighbours of one cluster) take
+// consecutive ranges of k-blocks of the same weight slice; the others ship their partial sums into
+// this much shared memory of the group's first CTA ([split - 1][n_unit / 4][sequences] float4).
+constexpr int DL_RED_BYTES = 24 * 1024;
 
 struct DlGemm {
   int N, K;                   // weight matrix [N, K]
   int n_unit;                 // weight rows per unit (multiple of 16, at most 128)
   int units;
-  int rot;                    // unit u runs on CTA (u + rot) % gridDim.x
+  int rot;                    // unit u runs on CTA group (u + rot) % (gridDim.x / split)
   int kg;                     // k-blocks per slot (per activation copy and per weight copy)
+  int split;                  // 1, or CTAs of a cluster that share a slice's K (phases 0 and 2 only)
+  int kb_per;                 // k-blocks per CTA of the group (an even multiple of kg; all of them when split == 1)
   int grouped;                // 1: tensor maps are [k-block, row, 64] (K a multiple of 64); 0: [1, row, K], one k-block per copy
 };
 
@@ -205,6 +211,108 @@ __device__ __forceinline__ float dl_rs(const float* ssq, int units, int Mb, int 
   return 1.0f / sqrtf(tot / (float)H + eps);
 }
 
+// ---- thread-block cluster helpers (distributed shared memory)
+__device__ __forceinline__ uint32_t dl_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t dl_cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void dl_cluster_sync() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dl_mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void dl_st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void dl_arrive_remote(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+// Wait (bounded) for a phase of an mbarrier whose arrivals come from other CTAs of the cluster.
+__device__ __forceinline__ bool dl_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  const long long t0 = clock64();
+  int spins = 0;
+  for (;;) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if (((++spins) & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_CYCLE_LIMIT) {
+        *abort_flag = 1;
+        if (atomicCAS(err, 0, code) == 0) { err[1] = (int)blockIdx.x; err[2] = (int)threadIdx.x; err[3] = (int)parity; }
+        return false;
+      }
+    }
+  }
+}
+
+// Tensor-parallel exchange, pass B (see the call site): flat over the unit's [sequences x n_unit] block.
+// Kept out of line: its eight vector loads in flight would otherwise raise the register count of
+// the whole kernel.
+__device__ __noinline__ void dl_tp_sum_ranks(const DlParams& p, int n_unit, int N, int gi, int u, int n0, int t, size_t slot_off,
+                                   const float* resid, float* h_out, __nv_bfloat16* x_out, const __nv_bfloat16* wn) {
+  const int vpr = n_unit >> 2;              // items per sequence: 4, 8, 16 or 32
+  const int items = p.Mb * vpr;
+  for (int i0 = 0; i0 < items; i0 += 128) {
+    const int i = i0 + t;
+    const int row = i / vpr, col = n0 + (i % vpr) * 4;
+    const bool inb = i < items && col < N;
+    float part = 0.f;
+    if (inb) {
+      const int64_t off = (int64_t)row * p.H + col;
+      float4 v[P2P_MAX_RANKS];
+#pragma unroll
+      for (int rk = 0; rk < P2P_MAX_RANKS; ++rk)
+        if (rk < p.tp) v[rk] = ld_peer_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.peer[rk] + slot_off) + off));
+      float4 a = __ldcg(reinterpret_cast<const float4*>(resid + off));
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int rk = 0; rk < P2P_MAX_RANKS; ++rk)
+        if (rk < p.tp) { sum.x += v[rk].x; sum.y += v[rk].y; sum.z += v[rk].z; sum.w += v[rk].w; }
+      a.x += sum.x; a.y += sum.y; a.z += sum.z; a.w += sum.w;
+      part = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      *reinterpret_cast<float4*>(h_out + off) = a;
+      const uint2 wraw = *reinterpret_cast<const uint2*>(wn + col);
+      const __nv_bfloat16* wh = reinterpret_cast<const __nv_bfloat16*>(&wraw);
+      uint2 xo;
+      __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(&xo);
+      xh[0] = __float2bfloat16_rn(a.x * __bfloat162float(wh[0]));
+      xh[1] = __float2bfloat16_rn(a.y * __bfloat162float(wh[1]));
+      xh[2] = __float2bfloat16_rn(a.z * __bfloat162float(wh[2]));
+      xh[3] = __float2bfloat16_rn(a.w * __bfloat162float(wh[3]));
+      *reinterpret_cast<uint2*>(x_out + off) = xo;
+    }
+    for (int o = vpr >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (inb && (i % vpr) == 0) (gi == 0 ? p.ssq1 : p.ssq2)[u * p.Mb + row] = part;
+  }
+}
+
+// The units of a phase that a CTA works on, and its range of k-blocks.
+struct DlWork { int first, step, sub, kb0, kb1; };
+__device__ __forceinline__ DlWork dl_work(const DlGemm& g, int cta, int G) {
+  DlWork w;
+  const int S = g.split, GS = G / S;
+  w.sub = cta % S;
+  w.first = (cta / S - g.rot % GS + GS) % GS;
+  w.step = GS;
+  const int n_kb = (g.K + DL_BK - 1) / DL_BK;
+  w.kb0 = w.sub * g.kb_per;
+  w.kb1 = min(n_kb, w.kb0 + g.kb_per);
+  return w;
+}
+
 __global__ void __launch_bounds__(DL_THREADS, 1)
 decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__ DlParams p) {
   const int x1 = p.x_box * DL_BK * 2;                 // bytes of one activation k-block tile
@@ -214,8 +322,10 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
   uint64_t* empty = full + DL_STAGES;
   uint64_t* acc_full = empty + DL_STAGES;       // 2
   uint64_t* acc_empty = acc_full + 2;           // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* red_bar = acc_empty + 2;            // 2: partial sums of the group's other CTAs have landed (phase 0, phase 2)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+#define DL_RED (reinterpret_cast<float4*>(smem + DL_STAGES * DL_SLOT + 1024))
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
@@ -225,6 +335,8 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     // both MMA issuers release a slot and complete an accumulator
     for (int s = 0; s < DL_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 2); }
     for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 2); mbar_init(&acc_empty[s], 4); }
+    // every epilogue thread of every other CTA of the group arrives once
+    for (int s = 0; s < 2; ++s) mbar_init(&red_bar[s], (uint32_t)(max(p.g[2 * s].split, 2) - 1) * 128u);
     *abort_flag = 0;
     fence_mbar_init();
     for (int i = 0; i < n_gemms; ++i) {
@@ -240,6 +352,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (dl_cluster_size() > 1) dl_cluster_sync();      // the neighbours' barriers exist before anybody arrives on them
   if (threadIdx.x == 0) DL_TRACE(0);
   // Programmatic dependent launch, both ways.  The next kernel (the attention of the next layer) may
   // start filling SMs as this kernel's CTAs leave them: it waits for this whole grid before it reads
@@ -256,8 +369,9 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
       bool ok = true;
       for (int gi = 0; ok && gi < n_gemms; ++gi) {
         const DlGemm& g = p.g[gi];
-        const int n_kb = (g.K + DL_BK - 1) / DL_BK;
-        const int n_grp = (n_kb + g.kg - 1) / g.kg;
+        const DlWork wk = dl_work(g, cta, G);
+        const int grp0 = wk.kb0 / g.kg;                                  // kb_per is a multiple of kg
+        const int n_grp = (wk.kb1 - wk.kb0 + g.kg - 1) / g.kg;           // groups of THIS CTA's k range
         const uint32_t tx = (uint32_t)(g.kg * (x1 + g.n_unit * DL_BK * 2));
         const CUtensorMap* wm = &maps.w[gi];
         const CUtensorMap* xm = &maps.x[gi];
@@ -271,7 +385,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           else tma_load_3d(smem + st * DL_SLOT, xm, &full[st], grp * DL_BK, 0, 0);
         };
         bool dep_ready = false;
-        for (int u = (cta - g.rot % G + G) % G; ok && u < g.units; u += G) {
+        for (int u = wk.first; ok && u < g.units && n_grp > 0; u += wk.step) {
           const int row0 = u * g.n_unit;
           int i = 0;
           if (!dep_ready) {
@@ -281,7 +395,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             for (; i < pre; ++i) {
               if (!mbar_wait(&empty[stage], ring_phase ^ 1, abort_flag, p.err, 521)) { ok = false; break; }
               mbar_arrive_expect_tx(&full[stage], tx);
-              load_w(stage, i, row0);
+              load_w(stage, grp0 + i, row0);
               if (++stage == DL_STAGES) { stage = 0; ring_phase ^= 1; }
             }
             if (!ok) break;
@@ -295,14 +409,14 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             for (int t = 0; t < pre; ++t) {
               int st = stage0 + t;
               if (st >= DL_STAGES) st -= DL_STAGES;
-              load_x(st, t);
+              load_x(st, grp0 + t);
             }
           }
           for (; i < n_grp; ++i) {
             if (!mbar_wait(&empty[stage], ring_phase ^ 1, abort_flag, p.err, 523)) { ok = false; break; }
             mbar_arrive_expect_tx(&full[stage], tx);
-            load_w(stage, i, row0);
-            load_x(stage, i);
+            load_w(stage, grp0 + i, row0);
+            load_x(stage, grp0 + i);
             if (++stage == DL_STAGES) { stage = 0; ring_phase ^= 1; }
           }
         }
@@ -326,22 +440,22 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
       const uint32_t smem_lo = ((smem_u32(smem) >> 4) & 0x3FFFu) | (1u << 16);
       for (int gi = 0; ok && gi < n_gemms; ++gi) {
         const DlGemm& g = p.g[gi];
-        const int n_kb = (g.K + DL_BK - 1) / DL_BK;
+        const DlWork wk = dl_work(g, cta, G);
         const uint32_t x_step = (uint32_t)x1 >> 4, w_step = (uint32_t)(g.n_unit * DL_BK * 2) >> 4;
         // D[128 sequence rows, n_unit weight rows] += X[128, 16] * W[n_unit, 16]^T
         const uint32_t idesc = make_idesc_bf16(128, g.n_unit, 0, 0);
-        for (int u = (cta - g.rot % G + G) % G; ok && u < g.units; u += G) {
+        for (int u = wk.first; ok && u < g.units && wk.kb0 < wk.kb1; u += wk.step) {
           const int buf = acc_n & 1, use = acc_n >> 1;
           if (!mbar_wait(&acc_empty[buf], (uint32_t)((use & 1) ^ 1), abort_flag, p.err, 524)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)buf * 256u + (uint32_t)me * 128u;
           uint32_t acc = 0u;
-          for (int kb = 0; kb < n_kb; kb += g.kg) {
+          for (int kb = wk.kb0; kb < wk.kb1; kb += g.kg) {
             if (!mbar_wait(&full[stage], ring_phase, abort_flag, p.err, 525)) { ok = false; break; }
             tc_fence_after();
             // an activation tile holds x_box rows; the MMA's other rows are read from whatever follows
             // it in the slot (later tiles, the weight area) and give accumulator rows of no sequence
-            const int nk = min(g.kg, n_kb - kb);
+            const int nk = min(g.kg, wk.kb1 - kb);
             const int j0 = (kb + me) & 1 ? 1 : 0;          // this issuer's first k-block of the group: global index parity == me
             uint32_t xl = smem_lo + (uint32_t)(stage * (DL_SLOT >> 4)) + (uint32_t)j0 * x_step;
             uint32_t wl = smem_lo + (uint32_t)(stage * (DL_SLOT >> 4)) + (uint32_t)(DL_X_AREA >> 4) + (uint32_t)j0 * w_step;
@@ -377,34 +491,64 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     // is made uniform (a barrier that ORs the threads' flags) before it decides anything.
     for (int gi = 0; gi < n_gemms; ++gi) {
       const DlGemm& g = p.g[gi];
-      const bool has_unit = ((cta - g.rot % G + G) % G) < g.units;
+      const DlWork wk = dl_work(g, cta, G);
+      const bool has_unit = wk.first < g.units && wk.kb0 < wk.kb1;
+      const bool leader = wk.sub == 0;          // of the group that shares a slice's K (always, when the phase is not split)
       float rs = 1.f;
       if (has_unit && (gi == 1 || gi == 3)) {
         // 1/rms of this thread's sequence, from the sums of squares of the phase that produced x
         if ((threadIdx.x & 127) == 0) counter_wait(p.counters + (gi - 1), (unsigned)p.g[gi - 1].units, abort_flag, p.err, 526);
         epi_bar_sync();
         if (valid) rs = dl_rs(gi == 1 ? p.ssq1 : p.ssq2, p.g[gi - 1].units, p.Mb, m, p.H, p.eps);
-      } else if (has_unit && gi == 2) {
+      } else if (has_unit && gi == 2 && leader) {
         // h1 (the residual of this phase) is complete once phase 0 is: only then may it be fetched early
         if ((threadIdx.x & 127) == 0) counter_wait(p.counters + 0, (unsigned)p.g[0].units, abort_flag, p.err, 526);
         epi_bar_sync();
       }
-      for (int u = (cta - g.rot % G + G) % G; u < g.units; u += G) {
+      for (int u = wk.first; has_unit && u < g.units; u += wk.step) {
         const int buf = acc_n & 1, use = acc_n >> 1;
         const int n0 = u * g.n_unit;
         // the residual and the norm weights do not depend on the GEMM: fetch the first columns' worth
         // while the MMAs run (the first 16 columns; the later ones are loaded in the loop below, where
         // their latency hides behind the work on the columns before them)
         float pre_r[16];
-        if ((gi == 0 || gi == 2) && valid && n0 < g.N && p.tp == 1)
+        if ((gi == 0 || gi == 2) && valid && n0 < g.N && p.tp == 1 && leader)
           ld_f32x16((gi == 0 ? p.resid_in : p.resid_mid) + (int64_t)m * p.H + n0, pre_r);
         if (ok) ok = mbar_wait(&acc_full[buf], (uint32_t)(use & 1), abort_flag, p.err, 527);
+        // the group's other CTAs have shipped their partial sums (a split phase is one unit per CTA, so
+        // each of the two barriers completes once per launch)
+        if (ok && g.split > 1 && leader) ok = dl_wait_cluster(&red_bar[gi >> 1], 0u, abort_flag, p.err, 529);
         if (epi_bar_any(!ok || *abort_flag != 0)) ok = false;   // one answer for all 128 threads
         if (!ok) continue;
         tc_fence_after();
         if ((threadIdx.x & 127) == 0) DL_TRACE(2 + 3 * gi);
         const uint32_t t_acc = t_row + (uint32_t)buf * 256u;
-        const bool two = g.K > DL_BK;           // the second issuer had at least one k-block
+        const bool two = wk.kb1 - wk.kb0 > 1;   // the second issuer had at least one k-block (kb0 is even)
+        if (!leader) {
+          // ---- partial sums of this CTA's k range: into the leader's shared memory, row m of column
+          // group c4 at [(sub - 1)][c4][m]; every thread arrives on the leader's barrier (release at
+          // cluster scope), valid row or not
+          const uint32_t lead_rank = dl_cluster_rank() - (uint32_t)wk.sub;
+          const uint32_t red_remote = dl_mapa(smem_u32(DL_RED), lead_rank);
+          const int vpr = g.n_unit >> 2;
+          for (int c0 = 0; c0 < g.n_unit; c0 += 16) {
+            float r[16];
+            dl_acc16(t_acc + c0, two, r);
+            if (valid) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                dl_st_cluster_f4(red_remote + (uint32_t)((((wk.sub - 1) * vpr + (c0 >> 2) + i) * p.Mb + m) << 4), r[4 * i], r[4 * i + 1],
+                                 r[4 * i + 2], r[4 * i + 3]);
+            }
+          }
+          dl_arrive_remote(dl_mapa(smem_u32(&red_bar[gi >> 1]), lead_rank));
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          ++acc_n;
+          if ((threadIdx.x & 127) == 0) DL_TRACE(3 + 3 * gi);
+          continue;
+        }
         if (gi == 0 || gi == 2) {
           // ---- residual add; hand on h, bf16(h * w) and this unit's share of sum(h^2)
           const float* resid = gi == 0 ? p.resid_in : p.resid_mid;
@@ -460,40 +604,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             // item i = four columns of one sequence; sum over ranks in rank order (the same bits on every
             // rank), residual add, h and bf16(h * w) stores; the row's share of sum(h^2) is reduced over
             // the adjacent lanes that hold the row (n_unit is a power of two here).
-            const int vpr = g.n_unit >> 2;              // items per sequence: 4, 8, 16 or 32
-            const int items = p.Mb * vpr;
-            for (int i0 = 0; i0 < items; i0 += 128) {
-              const int i = i0 + t;
-              const int row = i / vpr, col = n0 + (i % vpr) * 4;
-              const bool inb = i < items && col < g.N;
-              float part = 0.f;
-              if (inb) {
-                const int64_t off = (int64_t)row * p.H + col;
-                float4 v[P2P_MAX_RANKS];
-#pragma unroll
-                for (int rk = 0; rk < P2P_MAX_RANKS; ++rk)
-                  if (rk < p.tp) v[rk] = ld_peer_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.peer[rk] + slot_off) + off));
-                float4 a = __ldcg(reinterpret_cast<const float4*>(resid + off));
-                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int rk = 0; rk < P2P_MAX_RANKS; ++rk)
-                  if (rk < p.tp) { sum.x += v[rk].x; sum.y += v[rk].y; sum.z += v[rk].z; sum.w += v[rk].w; }
-                a.x += sum.x; a.y += sum.y; a.z += sum.z; a.w += sum.w;
-                part = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-                *reinterpret_cast<float4*>(h_out + off) = a;
-                const uint2 wraw = *reinterpret_cast<const uint2*>(wn + col);
-                const __nv_bfloat16* wh = reinterpret_cast<const __nv_bfloat16*>(&wraw);
-                uint2 xo;
-                __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(&xo);
-                xh[0] = __float2bfloat16_rn(a.x * __bfloat162float(wh[0]));
-                xh[1] = __float2bfloat16_rn(a.y * __bfloat162float(wh[1]));
-                xh[2] = __float2bfloat16_rn(a.z * __bfloat162float(wh[2]));
-                xh[3] = __float2bfloat16_rn(a.w * __bfloat162float(wh[3]));
-                *reinterpret_cast<uint2*>(x_out + off) = xo;
-              }
-              for (int o = vpr >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-              if (inb && (i % vpr) == 0) (gi == 0 ? p.ssq1 : p.ssq2)[u * p.Mb + row] = part;
-            }
+            dl_tp_sum_ranks(p, g.n_unit, g.N, gi, u, n0, t, slot_off, resid, h_out, x_out, wn);
             epi_bar_sync();
             if (t == 0 && *abort_flag == 0) {
               red_release_add(p.counters + gi, 1u);
@@ -505,6 +616,17 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
           auto chunk = [&](int c0, float (&a)[16]) {
             float r[16];
             dl_acc16(t_acc + c0, two, r);
+            if (g.split > 1 && valid) {
+              // + the other CTAs' k ranges, in the order of the ranges
+              const int vpr = g.n_unit >> 2;
+              for (int sgrp = 0; sgrp < g.split - 1; ++sgrp) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float4 v = DL_RED[((sgrp * vpr + (c0 >> 2) + i) * p.Mb + m)];
+                  r[4 * i] += v.x; r[4 * i + 1] += v.y; r[4 * i + 2] += v.z; r[4 * i + 3] += v.w;
+                }
+              }
+            }
             if (valid && n0 + c0 < g.N) {
               float w[16];
               ld_bf16x16(wn + n0 + c0, w);
@@ -643,6 +765,8 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+  // no CTA leaves while a neighbour may still write into its shared memory or arrive on its barriers
+  if (dl_cluster_size() > 1) dl_cluster_sync();
   if (threadIdx.x == 0 && *abort_flag == 0) {
     // the last CTA out re-arms the counters for the next launch
     const unsigned ticket = atomicAdd(p.counters + 7, 1u);
@@ -694,14 +818,47 @@ static int dl_tmap3(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1
   return KD_OK;
 }
 
-// Weight rows per unit: about 128 KB of weights per unit, not more units than SMs where that is
-// possible, a multiple of `step` rows (16, or 32 for the interleaved gate/up rows).
-static int dl_unit_rows(int N, int K, int G, int step) {
-  int n = (int)((128 * 1024) / ((int64_t)K * 2)) / step * step;
-  if (n < step) n = step;
-  if (n > 128) n = 128;
-  while (n < 128 && (N + n - 1) / n > G) n += step;
-  return n;
+// CTAs of a cooperative launch with clusters of `cs` CTAs (one CTA of `smem` bytes per SM): the
+// largest whole number of clusters that are resident together (132 of 148 SMs for clusters of 4 on
+// B200: clusters do not straddle GPCs).  0: such a launch is not possible.
+__global__ void decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__ DlParams p);
+static int dl_cluster_grid(int cs, int smem) {
+  static int cached[64][5] = {};
+  const int dev = ctx().device & 63;
+  if (cs == 1) return ctx().sm_count;
+  if (cached[dev][cs] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cs);
+    cfg.blockDim = dim3(DL_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cs; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, decode_layer_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    cached[dev][cs] = n > 0 ? n * cs : -1;
+  }
+  return cached[dev][cs] > 0 ? cached[dev][cs] : 0;
+}
+
+// Cost model behind the choice of the cluster size and of each phase's unit width and K split, in
+// microseconds, fitted to device-side timelines of the kernel (Qwen3-0.6B and 4B widths):
+//   - a CTA issues the MMAs of one k-block in about 0.127 us whatever the width of the slice (up to
+//     64 rows; wider: 0.17) and streams its weights at 80 GB/s at best; a phase as a whole cannot
+//     stream faster than about 5.5 TB/s;
+//   - an epilogue costs about 1 us plus 0.02 us per column of the slice (one thread owns a sequence
+//     and walks the columns), half as much again per partial sum it adds in;
+//   - a hand-over of partial sums inside a cluster about 0.6 us.
+static float dl_phase_cost(int N, int K, int n_unit, int split, int kb_per, int G) {
+  const int slices = (N + n_unit - 1) / n_unit;
+  const int waves = split > 1 ? 1 : (slices + G - 1) / G;
+  const float mma = kb_per * (n_unit > 64 ? 0.17f : 0.127f);
+  const float stream = (float)n_unit * kb_per * DL_BK * 2 / 80e3f;
+  const float floor_all = (float)N * K * 2 / 5.5e6f;
+  const float epi = 1.0f + 0.02f * n_unit * (1.0f + 0.5f * (split - 1));
+  return std::max(waves * std::max(mma, stream), floor_all) + waves * epi + (split > 1 ? 0.6f : 0.f);
 }
 
 }  // namespace kd
@@ -741,7 +898,7 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   KD_REQUIRE(attn->ndim == 2 && w_o->ndim == 2 && w_gate_up->ndim == 2 && w_down->ndim == 2, "operands must be 2-D");
   const int64_t Mb = attn->shape[0], Ko = attn->shape[1], H = w_o->shape[0], I2 = w_gate_up->shape[0], I = I2 / 2;
   Context& c = ctx();
-  const int G = c.sm_count;
+  int G = c.sm_count;
   KD_REQUIRE(Mb >= 1 && Mb <= 128, "%lld sequences; this path handles 1..128", (long long)Mb);
   KD_REQUIRE(Mb <= G, "more sequences than SMs");
   KD_REQUIRE(H % 16 == 0, "hidden size %lld must be a multiple of 16", (long long)H);
@@ -832,28 +989,94 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   struct Op { const void* w; int N, K, step; } ops[4] = {
       {p_wo, (int)H, (int)Ko, 16}, {p_wgu, (int)I2, (int)H, 32}, {p_wd, (int)H, (int)I, 16}, {p_wq, (int)Nq, (int)H, 128}};
   const int n_gemms = has_qkv ? 4 : 3;
-  for (int i = 0; i < n_gemms; ++i) {
-    DlGemm& g = p.g[i];
-    g.N = ops[i].N; g.K = ops[i].K;
-    g.n_unit = i == 3 ? 128 : dl_unit_rows(g.N, g.K, G, ops[i].step);
-    {   // experiment hook: KD_DL_N0 / KD_DL_N1 / KD_DL_N2 override the unit width of a phase
-      const char* names[3] = {"KD_DL_N0", "KD_DL_N1", "KD_DL_N2"};
-      const char* e = i < 3 ? getenv(names[i]) : nullptr;
-      if (e && atoi(e) >= ops[i].step && atoi(e) <= 128 && atoi(e) % ops[i].step == 0) g.n_unit = atoi(e);
-    }
-    g.units = (g.N + g.n_unit - 1) / g.n_unit;
-    if (tensor_parallel && (i == 0 || i == 2)) {
-      // one exchange flag per unit: at most P2P_MAX_ROWS units in the phases that exchange partial sums
-      // (widths are powers of two there: the epilogue reduces a row's sum of squares over adjacent lanes)
-      int w2 = 16;
-      while (w2 < g.n_unit) w2 *= 2;
-      g.n_unit = w2 > 128 ? 128 : w2;
-      while (g.n_unit < 128 && (g.N + g.n_unit - 1) / g.n_unit > P2P_MAX_ROWS) g.n_unit *= 2;
-      g.units = (g.N + g.n_unit - 1) / g.n_unit;
-      KD_REQUIRE(g.units <= P2P_MAX_ROWS, "hidden size %d needs %d exchange units (at most %d)", g.N, g.units, P2P_MAX_ROWS);
-    }
-    KD_REQUIRE(g.units <= DL_MAX_UNITS, "%d units in phase %d (at most %d)", g.units, i, DL_MAX_UNITS);
+  const int smem = DL_STAGES * DL_SLOT + 1024 + DL_RED_BYTES + 1024;
+  static bool configured[64] = {false};
+  if (!configured[dev]) {      // before the occupancy queries below, which need the shared memory to be allowed
+    KD_CUDA_CHECK(cudaFuncSetAttribute(decode_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    configured[dev] = true;
   }
+  const int x1 = p.x_box * DL_BK * 2;
+  static const bool no_groups = [] { const char* e = getenv("KD_DL_NO_GROUPS"); return e && e[0] == '1'; }();
+  auto grouped_of = [&](int K) { return K % DL_BK == 0 && !no_groups; };
+  auto kg_of = [&](int n_unit, int K) {
+    const int n_kb = (K + DL_BK - 1) / DL_BK;
+    return grouped_of(K) ? std::max(1, std::min(std::min(DL_X_AREA / x1, DL_W_AREA / (n_unit * DL_BK * 2)), std::min(n_kb, 16))) : 1;
+  };
+  // experiment hooks: KD_DL_CLUSTER = 1 | 2 | 4 fixes the cluster size, KD_DL_N0 / N1 / N2 the unit width of a phase
+  auto env_int = [](const char* name) { const char* e = getenv(name); return e ? atoi(e) : 0; };
+  const int want_cluster = env_int("KD_DL_CLUSTER");
+  const int want_n[3] = {env_int("KD_DL_N0"), env_int("KD_DL_N1"), env_int("KD_DL_N2")};
+  // Plan: for every cluster size that can be launched, the best unit width and K split of each phase
+  // by the cost model above; the cluster size with the lowest sum wins (the smaller one on a near tie).
+  int cluster = 0;
+  float best_total = 1e30f;
+  DlGemm plan[4] = {};
+  for (int cs = 1; cs <= 4; cs *= 2) {
+    if (want_cluster && cs != want_cluster) continue;
+    if (tensor_parallel && cs > 1) continue;          // K is already split over the ranks; the exchange replaces the cluster reduce
+    const int Gc = dl_cluster_grid(cs, smem);
+    if (Gc <= 0 || Mb > Gc) continue;
+    DlGemm cand[4] = {};
+    float total = 0.f;
+    bool feasible = true;
+    for (int i = 0; i < n_gemms && feasible; ++i) {
+      DlGemm& g = cand[i];
+      g.N = ops[i].N; g.K = ops[i].K;
+      const int n_kb = (g.K + DL_BK - 1) / DL_BK;
+      if (i == 1 || i == 3) {
+        g.split = 1;
+        g.kb_per = n_kb;
+        g.n_unit = 128;                 // phase 3: one head per unit
+        if (i == 1) {
+          float best1 = 1e30f;
+          for (int n = 32; n <= 128; n += 32) {
+            if (want_n[1] && n != want_n[1]) continue;
+            if ((g.N + n - 1) / n > DL_MAX_UNITS) continue;
+            const float cost = dl_phase_cost(g.N, g.K, n, 1, n_kb, Gc);
+            if (cost < best1 - 0.05f) { best1 = cost; g.n_unit = n; }
+          }
+        }
+        g.units = (g.N + g.n_unit - 1) / g.n_unit;
+        if (g.units > DL_MAX_UNITS) { feasible = false; break; }
+        total += dl_phase_cost(g.N, g.K, g.n_unit, 1, n_kb, Gc);
+        continue;
+      }
+      float best = 1e30f;
+      for (int n = 16; n <= 128; n += 16) {
+        if (want_n[i] && n != want_n[i]) continue;
+        if (tensor_parallel && (n & (n - 1))) continue;      // the exchange epilogue reduces over adjacent lanes: powers of two
+        const int slices = (g.N + n - 1) / n;
+        if (tensor_parallel && slices > P2P_MAX_ROWS) continue;   // one exchange flag per unit
+        if (slices > DL_MAX_UNITS) continue;
+        const int kg = kg_of(n, g.K);
+        for (int S = 1; S <= cs; S *= 2) {
+          int kb_per = n_kb;
+          if (S > 1) {
+            if (!grouped_of(g.K) || slices > Gc / S || (size_t)(S - 1) * Mb * n * sizeof(float) > (size_t)DL_RED_BYTES) continue;
+            const int q = (kg % 2) ? 2 * kg : kg;                  // ranges start at even k-blocks and at whole groups
+            kb_per = ((n_kb + S - 1) / S + q - 1) / q * q;
+            if (kb_per * (S - 1) >= n_kb) continue;                // somebody's range would be empty
+          }
+          const float cost = dl_phase_cost(g.N, g.K, n, S, kb_per, Gc);
+          if (cost < best - 0.05f) {
+            best = cost;
+            g.n_unit = n; g.units = slices; g.split = S; g.kb_per = kb_per;
+          }
+        }
+      }
+      if (best > 1e29f) feasible = false;
+      total += best;
+    }
+    if (!feasible) continue;
+    if (total < best_total - 0.3f) {
+      best_total = total;
+      cluster = cs;
+      for (int i = 0; i < 4; ++i) plan[i] = cand[i];
+    }
+  }
+  KD_REQUIRE(cluster > 0, "no launch configuration for these shapes (hidden %lld, %lld sequences)", (long long)H, (long long)Mb);
+  G = dl_cluster_grid(cluster, smem);
+  for (int i = 0; i < n_gemms; ++i) p.g[i] = plan[i];
   if (tensor_parallel) {
     P2pPeers peers;
     KD_TRY(p2p_peers(&peers));
@@ -885,7 +1108,7 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   p.g[0].rot = 0;
   p.g[1].rot = (G - p.g[1].units % G) % G;
   p.g[2].rot = 0;
-  p.g[3].rot = p.g[2].units % G;
+  p.g[3].rot = (p.g[2].units * p.g[2].split) % G;
   p.resid_in = static_cast<const float*>(p_ri);
   p.resid_out = static_cast<float*>(p_ro);
   p.w_post = static_cast<const __nv_bfloat16*>(p_pn);
@@ -907,13 +1130,11 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   static DlMaps maps;   // large: keep it off the stack
   const void* xs[4] = {p_attn, p.x1, p.act, p.x2};
   const int64_t ldx[4] = {attn->strides[0], H, I, H};
-  const int x1 = p.x_box * DL_BK * 2;
-  static const bool no_groups = [] { const char* e = getenv("KD_DL_NO_GROUPS"); return e && e[0] == '1'; }();
   for (int i = 0; i < n_gemms; ++i) {
     DlGemm& g = p.g[i];
     const int n_kb = (g.K + DL_BK - 1) / DL_BK;
-    g.grouped = (g.K % DL_BK == 0 && !no_groups) ? 1 : 0;
-    g.kg = g.grouped ? std::max(1, std::min(std::min(DL_X_AREA / x1, DL_W_AREA / (g.n_unit * DL_BK * 2)), std::min(n_kb, 16))) : 1;
+    g.grouped = grouped_of(g.K) ? 1 : 0;
+    g.kg = kg_of(g.n_unit, g.K);
     if (g.grouped) {
       // [k-block, row, 64]: the k-blocks of a row are 128 bytes apart, rows a whole row apart
       int rc = dl_tmap3(&maps.w[i], ops[i].w, DL_BK, (uint64_t)g.N, (uint64_t)n_kb, (uint64_t)g.K * 2, 128, (uint32_t)g.n_unit, (uint32_t)g.kg);
@@ -926,26 +1147,27 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
     }
   }
   if (n_gemms < 4) { maps.w[3] = maps.w[0]; maps.x[3] = maps.x[0]; }
-  const int smem = DL_STAGES * DL_SLOT + 1024 + 1024;
-  static bool configured[64] = {false};
-  if (!configured[dev]) {
-    KD_CUDA_CHECK(cudaFuncSetAttribute(decode_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    configured[dev] = true;
-  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(G);
   cfg.blockDim = dim3(DL_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = c.stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[3];
   attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident, or the launch fails
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster > 1) {
+    attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[cfg.numAttrs].val.clusterDim.x = cluster;
+    attr[cfg.numAttrs].val.clusterDim.y = 1;
+    attr[cfg.numAttrs].val.clusterDim.z = 1;
+    ++cfg.numAttrs;
+  }
   if (c.pdl) {
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.numAttrs = 2;
+    attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++cfg.numAttrs;
   }
   KD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, decode_layer_kernel, maps, p));
   return after_launch("decode_layer_kernel");
