@@ -10,14 +10,23 @@
 //     the causal mask, or be absent at the end of the sequence).
 // so every K/V tile fetched into shared memory feeds two S = QK^T and two O += PV products.
 //
-//   warp 0      TMA producer: both Q tiles once, then K/V tiles through a 4-slot ring
-//   warp 1      tcgen05.mma issuer, order  QK_A(0) QK_B(0) | PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1) | ...
+//   warps 0-3   softmax + epilogue of sub-tile A (one query row per thread)
+//   warps 4-7   the same for sub-tile B
+//   warp 8      TMA producer: both Q tiles once, then K/V tiles through a 4-slot ring
+//   warp 9      tcgen05.mma issuer, order  QK_A(0) QK_B(0) | PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1) | ...
 //               so the tensor pipe works on one sub-tile while the other's softmax runs
-//   warps 2-5   softmax + epilogue of sub-tile A (one query row per thread)
-//   warps 6-9   the same for sub-tile B
+//   warps 10-11 idle: they complete the third warpgroup, which hands most of its registers to the
+//               softmax warpgroups (setmaxnreg: 56 against 224 per thread)
 // TMEM (512 columns): S_A, S_B (fp32, overwritten in place by P as packed bf16), O_A, O_B.
-// The softmax makes two passes over the S row in tensor memory (maximum, then exponentials) so that
-// it never holds 128 scores in registers.  Mathematics as in attention_tcgen05.cu / the reference
+// The softmax reads its S row (128 scores) from tensor memory ONCE and keeps it in registers for the
+// maximum and the exponentials; P is handed to the MMA warp in two halves of 64 keys, so that the
+// first four k-steps of P V run while the second half is still being exponentiated.  The softmax
+// warps are bound by the instructions they issue (the special-function unit, at 16 exponentials per
+// clock and SM, would allow slightly more), so the arithmetic around the exponential is packed:
+// three-input maxima, two-wide fused multiply-adds and adds (max.f32 with three operands,
+// fma.rn.f32x2, add.rn.f32x2): 3 instructions per score instead of 4.5.  Computing a quarter of the
+// exponentials on the FMA pipe instead (round-to-nearest split, cubic polynomial, exponent added
+// with integer arithmetic) was measured and made the kernel 7 % slower: more instructions.  Mathematics as in attention_tcgen05.cu / the reference
 // shader (packages/backend-webgpu/src/kernels/attention/builder.ts:138-329).
 #include "common.cuh"
 #include "kernels.cuh"
@@ -33,6 +42,23 @@ __device__ __forceinline__ float fa2_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float fa2_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (x0, x1) = (a0, a1) * s + m
+__device__ __forceinline__ void fa2_fma2(float& x0, float& x1, float a0, float a1, float s, float m) {
+  asm("{\n\t.reg .b64 a, b, c, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tmov.b64 c, {%5, %5};\n\t"
+      "fma.rn.f32x2 d, a, b, c;\n\tmov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(x0), "=f"(x1) : "f"(a0), "f"(a1), "f"(s), "f"(m));
+}
+// (s0, s1) += (a0, a1)
+__device__ __forceinline__ void fa2_add2(float& s0, float& s1, float a0, float a1) {
+  asm("{\n\t.reg .b64 a, b, d;\n\tmov.b64 a, {%0, %1};\n\tmov.b64 b, {%2, %3};\n\tadd.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
+      : "+f"(s0), "+f"(s1) : "f"(a0), "f"(a1));
+}
+
 struct Fa2Params {
   int B, Hq, Hkv, Sq, Skv;
   int causal;
@@ -44,7 +70,7 @@ struct Fa2Params {
   int* err;
 };
 
-constexpr int FA2_BQ = 128, FA2_BKV = 128, FA2_THREADS = 320, FA2_NSLOT = 4;
+constexpr int FA2_BQ = 128, FA2_BKV = 128, FA2_THREADS = 384, FA2_NSLOT = 4;
 
 template <int D>
 __global__ void __launch_bounds__(FA2_THREADS, 1)
@@ -68,9 +94,9 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
   uint64_t* t_full = bars + 1;      // 4
   uint64_t* t_empty = bars + 5;     // 4
   uint64_t* s_full = bars + 9;      // 2 (per sub-tile)
-  uint64_t* p_ready = bars + 11;    // 2
-  uint64_t* o_done = bars + 13;     // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* p_ready = bars + 11;    // 4: [sub-tile][half of the keys]
+  uint64_t* o_done = bars + 15;     // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,14 +126,15 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < FA2_NSLOT; ++s) { mbar_init(&t_full[s], 1); mbar_init(&t_empty[s], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 4); mbar_init(&o_done[t], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&o_done[t], 1); }
+    for (int t = 0; t < 4; ++t) mbar_init(&p_ready[t], 4);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
   }
-  if (warp == 1) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -115,8 +142,9 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp == 8) {
     if (lane == 0) {
       // an absent second sub-tile still gets a (zero-filled, out-of-range) load so that the byte count is fixed
       mbar_arrive_expect_tx(q_full, 2 * Q_BYTES);
@@ -140,7 +168,7 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
           tma_load_4d(ring + sv * KV_BYTES + s * SLAB_BYTES, &tmap_v, &t_full[sv], s * 64, j * FA2_BKV, hk, b);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, 403);
       // S_t(j) = Q_t K(j)^T.  The K tile is waited for once per block (by whichever sub-tile comes first).
@@ -164,14 +192,17 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
       auto release_k = [&](int j) { umma_commit(&t_empty[(2 * j) % FA2_NSLOT]); };
       auto issue_pv = [&](int t, int j, bool wait_v) -> bool {
         const int stage = (2 * j + 1) % FA2_NSLOT;
-        if (!mbar_wait(&p_ready[t], (uint32_t)(j & 1), abort_flag, p.err, 405)) return false;
         if (wait_v && !mbar_wait(&t_full[stage], (uint32_t)(((2 * j + 1) / FA2_NSLOT) & 1), abort_flag, p.err, 406)) return false;
-        tc_fence_after();
         const uint32_t v_addr = smem_u32(ring + stage * KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < FA2_BKV / 16; ++k) {
-          const uint64_t vdesc = make_smem_desc_sw128(v_addr + (uint32_t)(k * 2048), SLAB_BYTES, 1024);
-          umma_ts(tmem_base + (uint32_t)(256 + t * D), tmem_base + (uint32_t)(t * 128 + k * 8), vdesc, IDESC_PV, (j | k) != 0 ? 1u : 0u);
+        for (int half = 0; half < 2; ++half) {
+          if (!mbar_wait(&p_ready[2 * t + half], (uint32_t)(j & 1), abort_flag, p.err, 405)) return false;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 4 * half; k < 4 * half + 4; ++k) {
+            const uint64_t vdesc = make_smem_desc_sw128(v_addr + (uint32_t)(k * 2048), SLAB_BYTES, 1024);
+            umma_ts(tmem_base + (uint32_t)(256 + t * D), tmem_base + (uint32_t)(t * 128 + k * 8), vdesc, IDESC_PV, (j | k) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(&o_done[t]);
         return true;
@@ -193,8 +224,10 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
         if (ok && (a_next || b_next)) release_k(j + 1);
       }
     }
+  }
   } else {
-    const int t = (warp - 2) >> 2;          // sub-tile of this warpgroup
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    const int t = warp >> 2;                // sub-tile of this warpgroup
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     const int my_q0 = t ? q0[1] : q0[0], my_head = t ? head[1] : head[0];
@@ -213,27 +246,27 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
       tc_fence_after();
       const int kv0 = j * FA2_BKV;
       const bool masked = (kv0 + FA2_BKV > my_kv_end) || (p.causal && kv0 + FA2_BKV - 1 > my_q0);
-      // pass 1: row maximum
-      float mx0 = -1e30f, mx1 = -1e30f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_wait_ld();
-        if (masked) {
+      // the whole S row of this thread, once
+      uint32_t r[128];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = kv0 + c * 32 + i;
-            if (col >= p.Skv || (p.causal && col > row)) r[i] = __float_as_uint(-1e30f);
-          }
-        }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, r + c * 32);
+      tmem_wait_ld();
+      if (masked) {
+        // key kv0 + i is visible to this row iff i <= lim
+        const int lim = (p.causal ? min(p.Skv - 1, row) : p.Skv - 1) - kv0;
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          mx0 = fmaxf(mx0, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
-          mx1 = fmaxf(mx1, fmaxf(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
-        }
+        for (int i = 0; i < 128; ++i)
+          if (i > lim) r[i] = __float_as_uint(-1e30f);
       }
-      const float m_blk = fmaxf(mx0, mx1) * p.scale_log2;
+      float mx0 = -1e30f, mx1 = -1e30f, mx2 = -1e30f, mx3 = -1e30f;
+#pragma unroll
+      for (int i = 0; i < 128; i += 8) {
+        mx0 = fa2_max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        mx1 = fa2_max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        mx2 = fa2_max3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+        mx3 = fa2_max3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+      }
+      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
       float alpha = 1.f;
       bool rescale = false;
       if (j == 0) {
@@ -249,53 +282,39 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t orr[32];
-          tmem_ld_32x32(o_addr + c * 32, orr);
+        for (int c = 0; c < D / 16; ++c) {      // narrow chunks: the 128 scores stay in registers meanwhile
+          uint32_t orr[16];
+          tmem_ld_32x16(o_addr + c * 16, orr);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-          tmem_st_32x32(o_addr + c * 32, orr);
+          for (int i = 0; i < 16; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+          tmem_st_32x16(o_addr + c * 16, orr);
         }
         l *= alpha;
       }
-      // pass 2: P = exp2(s*c - m) as packed bf16 over the first 64 columns of S.  Packed column k holds
-      // elements 2k, 2k+1, so chunk c (elements 32c..32c+31) lands in packed columns 16c..16c+15, which
-      // only overlap S columns that have already been consumed (16c+15 < 32(c+1)).
+      // P = exp2(s*c - m) as packed bf16 over the first 64 columns of S (packed column k holds keys
+      // 2k, 2k+1), written and handed over in two halves of 64 keys.  The packed values replace the
+      // scores in r[] from the front (r[i] <- keys 2i, 2i+1: never ahead of what is still to be read).
       float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; c += 2) {
-        uint32_t r0[32], r1[32], pk[32];
-        tmem_ld_32x32(s_addr + c * 32, r0);
-        tmem_ld_32x32(s_addr + (c + 1) * 32, r1);
-        tmem_wait_ld();
-        if (masked) {
+      const float neg_m = -m_used;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = kv0 + c * 32 + i;
-            if (col >= p.Skv || (p.causal && col > row)) r0[i] = __float_as_uint(-1e30f);
-            if (col + 32 >= p.Skv || (p.causal && col + 32 > row)) r1[i] = __float_as_uint(-1e30f);
-          }
-        }
+      for (int half = 0; half < 2; ++half) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float a0 = fa2_exp2(fmaf(__uint_as_float(r0[2 * i]), p.scale_log2, -m_used));
-          const float a1 = fa2_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), p.scale_log2, -m_used));
-          const float b0 = fa2_exp2(fmaf(__uint_as_float(r1[2 * i]), p.scale_log2, -m_used));
-          const float b1 = fa2_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), p.scale_log2, -m_used));
-          sum0 += a0 + b0;
-          sum1 += a1 + b1;
-          __nv_bfloat162 va = __floats2bfloat162_rn(a0, a1), vb = __floats2bfloat162_rn(b0, b1);
-          pk[i] = *reinterpret_cast<uint32_t*>(&va);
-          pk[16 + i] = *reinterpret_cast<uint32_t*>(&vb);
+        for (int i = 32 * half; i < 32 * half + 32; ++i) {
+          float x0, x1;
+          fa2_fma2(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m);
+          const float e0 = fa2_exp2(x0), e1 = fa2_exp2(x1);
+          fa2_add2(sum0, sum1, e0, e1);
+          __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
+          r[i] = *reinterpret_cast<uint32_t*>(&v);
         }
-        tmem_st_32x32(s_addr + c * 16, pk);
+        tmem_st_32x32(s_addr + half * 32, r + half * 32);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[2 * t + half]);
       }
       l += sum0 + sum1;
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[t]);
     }
     if (ok && nb > 0) {
       ok = mbar_wait(&o_done[t], (uint32_t)((nb - 1) & 1), abort_flag, p.err, 409);
@@ -330,7 +349,7 @@ flash_attention_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_q, cons
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 9) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
