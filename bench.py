@@ -14,8 +14,9 @@ are sharded, 32/N per rank, weights replicated, no data-path collective: STRONG 
   e2e     the same job through the public host API: each rank's prompt ids start in pinned host
           memory and are copied in every step; every decode step's token ids are read back to the
           host (as the reference's generation loop does).
-  parity_ok  (N > 1) the tokens the N ranks generated, gathered on rank 0, equal bit for bit the
-          tokens rank 0 generates alone for all 32 sequences in micro-batches of 32/N.
+  parity_ok  N > 1: the tokens the N ranks generated, gathered on rank 0, equal bit for bit the
+          tokens rank 0 generates alone for all 32 sequences in micro-batches of 32/N.  N = 1: the
+          timed run's tokens equal an eager re-run of the same job (no graph replay).
   roofline  the dominant kernel by time (split-KV decode attention, HBM-bound) timed alone with CUDA
           events at the mean context length; GEMM / attention / lm_head / chain figures ride along in
           `roofline_other`, each against the measured and the nominal ceiling.
@@ -430,6 +431,14 @@ def run_headline(bn: Bench) -> dict:
         else:
             parity = {"parity_ok": None, "note": f"{N_SEQ} sequences do not divide over {world} ranks evenly; not compared"}
         bn.sync_all()
+    else:
+        # one GPU: the tokens of the timed end-to-end run against the same job launched kernel by kernel
+        # (no graph replay); parity against the CPU oracle is what tests/test_full_configs_gpu.py checks
+        again = eng.generate(ids_all, T, use_graph=False)
+        got = np.asarray(tokens_mine)
+        parity = {"parity_ok": bool(np.array_equal(got, again)),
+                  "tokens_sha256": hashlib.sha256(np.ascontiguousarray(got).tobytes()).hexdigest()[:16],
+                  "reference_run": "the same sequences again with eager launches instead of the replayed decode graph"}
 
     tokens_all = N_SEQ * (S + T)
     per_layer_params = dims["hidden"] * ((dims["heads"] + 2 * dims["kv_heads"]) * dims["head_dim"]) + \
