@@ -338,7 +338,16 @@ int kd_increment_i32(const kd_tensor* scalar, int delta);
 /* CUDA-graph capture of everything enqueued between begin and end (no counterpart in the
  * reference, whose per-op host overhead is what this removes). */
 /* Enables programmatic dependent launch for the kernels of the decode step (they all begin with a
- * grid-dependency wait), so that each kernel's launch latency overlaps its predecessor. */
+ * grid-dependency wait), so that each kernel's launch latency overlaps its predecessor.
+ * enabled = 2 additionally lets kd_attention_decode[_paged/_noalloc] read the context length and
+ * fetch the K/V tiles that do not hold the LAST position (context length - 1) BEFORE its
+ * grid-dependency wait, while the kernel before it is still draining.  The caller then promises
+ * that, of everything the call reads, only the query and the cache rows of that last position
+ * were written by the launch directly before it; the context length, the block table and all
+ * earlier cache rows must date from launches that are separated from the call by at least one
+ * kernel of this library other than the fused layer kernel and the decode attention itself
+ * (every other kernel passes its grid-dependency wait before it lets its successor start).  A decode step that writes one new
+ * row per layer, as Qwen3Engine's does, satisfies this. */
 int kd_set_pdl(int enabled);
 int kd_graph_begin(void);
 int kd_graph_end(uint64_t* graph_out);

@@ -94,6 +94,7 @@ struct FaParams {
   float* part_ml;              // [B, Hkv, splits, group, 2] (running max in the log2 domain, sum)
   int direct;                  // splits == 1: write O/l as bf16 straight to `o` (no combine kernel)
   int colsplit;                // decode, group <= 8: each softmax warp handles a quarter of the key columns (see kernel)
+  int early_kv;                // decode: K/V tiles that do not hold the last position may be fetched before the grid-dependency wait
 };
 
 constexpr int FA_BQ = 128;
@@ -154,7 +155,10 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z;
   int h, hk, q0, kv_len, j_begin, j_end, kv_end;
-  if (DECODE) pdl_wait();   // the context length below is written by the previous step
+  // (early_kv: the caller guarantees that the context length and all cache rows but the last
+  // position's are older than the launch before this one; see kd_set_pdl)
+  if (DECODE && !p.early_kv) pdl_wait();
+  int n_early = 0;            // this CTA's leading key tiles that may be fetched before the wait
   if (DECODE) {
     hk = blockIdx.y;
     h = hk;                     // Q tensor map is indexed by (row-in-group, kv head, batch)
@@ -166,7 +170,11 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
     const int per_split = (n_total + p.splits - 1) / p.splits;
     j_begin = (int)blockIdx.x * per_split;
     j_end = min(n_total, j_begin + per_split);
+    // the ring takes three K/V tile pairs without anybody having to free a slot; the tile that holds
+    // position kv_len - 1 is the last one of the last split
+    if (p.early_kv) n_early = max(0, min(min(j_end, n_total - 1) - j_begin, NSLOT / 2));
     if (j_begin >= j_end) {     // nothing for this split: publish an empty partial and leave
+      if (p.early_kv) pdl_wait();
       if (p.direct) {
         // a single split without any key (context length 0 read from device memory): attention over
         // no keys is defined here as a zero row, so that `out` never keeps stale contents
@@ -217,10 +225,18 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, Q_BYTES);
+      auto load_q = [&]() {
+        mbar_arrive_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-      for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * Q_SLAB, &tmap_q, q_full, s * 64, q0, h, b);
+        for (int s = 0; s < SLABS; ++s) tma_load_4d(q_smem + s * Q_SLAB, &tmap_q, q_full, s * 64, q0, h, b);
+      };
+      if (!(DECODE && p.early_kv)) load_q();
       for (int jj = 0; jj < n_blocks; ++jj) {
+        if (DECODE && p.early_kv && jj == n_early) {
+          // everything else (the query, the newest cache row) was written by the launch before this one
+          pdl_wait();
+          load_q();
+        }
         // key-tile coordinates: rows j*BKV.. of sequence b, or the matching rows of the 128-row page
         // the block table names
         int row = (j_begin + jj) * BKV, outer = b;
@@ -240,6 +256,10 @@ flash_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
           tma_load_4d(ring + sv * KV_BYTES + s * SLAB_BYTES, &tmap_v, &t_full[sv], s * 64, row, hk, outer);
+      }
+      if (DECODE && p.early_kv && n_early >= n_blocks) {   // all of this CTA's tiles were early ones
+        pdl_wait();
+        load_q();
       }
     }
   } else if (warp == 1) {
@@ -841,6 +861,7 @@ int attention_decode(const kd_tensor* q, const kd_tensor* k, const kd_tensor* v,
   // column-split softmax: the Q tile is replicated into every 8-row group, so at most 8 query heads per KV head
   static const bool no_colsplit = [] { const char* e = getenv("KD_DECODE_NO_COLSPLIT"); return e && e[0] == '1'; }();
   p.colsplit = (group <= 8 && !no_colsplit) ? 1 : 0;
+  p.early_kv = ctx().pdl_early_kv ? 1 : 0;
   p.direct = (splits == 1 && (reinterpret_cast<uintptr_t>(po) & 15) == 0 && out->strides[0] % 8 == 0 && out->strides[1] % 8 == 0) ? 1 : 0;
   p.o = static_cast<__nv_bfloat16*>(po);
   p.so_b = out->strides[0]; p.so_h = out->strides[1]; p.so_s = out->strides[2];

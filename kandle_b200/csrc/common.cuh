@@ -55,6 +55,7 @@ struct Context {
   uint64_t launches = 0;
   int* error_flag = nullptr;  // device int, set by kernels that detect a problem
   bool pdl = false;           // launch kernels with programmatic dependent launch (kd_set_pdl)
+  bool pdl_early_kv = false;  // kd_set_pdl(2): decode attention may fetch K/V tiles of earlier positions before its grid-dependency wait
   void* workspace = nullptr;  // library-owned scratch, grown on demand
   uint64_t workspace_bytes = 0;
 };

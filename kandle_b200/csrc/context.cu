@@ -453,5 +453,6 @@ KD_API int kd_event_destroy(uint64_t event) {
 KD_API int kd_set_pdl(int enabled) {
   KD_TRY(require_init());
   ctx().pdl = enabled != 0;
+  ctx().pdl_early_kv = enabled == 2;
   return KD_OK;
 }

@@ -25,6 +25,7 @@ static workspace the simple choice.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 
 import numpy as np
@@ -130,6 +131,7 @@ class Qwen3Engine:
         self._decode = None
         self.pos = 0
         self.use_pdl = True
+        self.use_early_kv = os.environ.get("KD_EARLY_KV", "1") != "0"
         # decode: run o_proj .. next layer's QKV as one persistent kernel per layer (kd_decode_layer_chain);
         # tensor parallelism needs an all-reduce after o_proj and down_proj, so it keeps separate kernels
         self.use_chain = self.tp == 1 and self.H <= 4096
@@ -383,7 +385,10 @@ class Qwen3Engine:
 
     def _enqueue_decode_step(self, d: dict) -> None:
         """One decode step for d['ids'] at device position d['pos']; leaves the next ids in d['ids']."""
-        lib.call("kd_set_pdl", 1 if self.use_pdl else 0)   # every kernel below starts with a grid-dependency wait
+        # every kernel below starts with a grid-dependency wait; 2: the decode attention may fetch the K/V
+        # tiles of earlier positions before its wait (this step writes one new cache row per layer, and
+        # the context length dates from the previous step)
+        lib.call("kd_set_pdl", (2 if self.use_early_kv else 1) if self.use_pdl else 0)
         try:
             self._decode_step_kernels(d)
         finally:

@@ -176,3 +176,30 @@ def test_paged_engine_generates_the_tokens_of_the_contiguous_engine(backend, ora
                               num_attention_heads=4, num_key_value_heads=2, head_dim=128)
     ref = oracle.Qwen3Oracle(ocfg, w).greedy_generate(ids, 12, max_seq_len=256).astype(np.int64)
     assert (want == ref).mean() >= 0.8
+
+
+def test_early_kv_prefetch_gives_the_same_tokens(backend, oracle):
+    """kd_set_pdl(2): the decode attention fetches the K/V tiles of earlier positions before its
+    grid-dependency wait.  Nothing but the timing may change: tokens equal those of the plain
+    programmatic launches and of launches without them, for a context of several key tiles and
+    splits (prompt 300 + 40 steps crosses a 64-key tile boundary several times, so the tile that
+    holds the newest row keeps moving), contiguous and paged cache, graph replay and eager."""
+    dims = dict(vocab=1024, hidden=256, inter=512, layers=3, heads=4, kv_heads=2, head_dim=128)
+    w = {k: lib.round_to_bf16(v) for k, v in synth.qwen3_weights(std=0.05, **dims).items()}
+    cfg = Qwen3Config(vocabSize=1024, hiddenSize=256, intermediateSize=512, numHiddenLayers=3, numAttentionHeads=4,
+                      numKeyValueHeads=2, headDim=128, dtype="bfloat16")
+    ids = synth.token_ids("earlykv.ids", (5, 300), 1024)
+    for paged in (False, True):
+        eng = Qwen3Engine(cfg, w, 5, 384, paged=paged)
+        assert eng.use_pdl and eng.use_early_kv
+        got = eng.generate(ids, 40)
+        got_eager = eng.generate(ids, 40, use_graph=False)
+        eng.dispose()
+        eng.use_early_kv = False
+        want = eng.generate(ids, 40)
+        eng.dispose()
+        eng.use_pdl = False
+        plain = eng.generate(ids, 40)
+        eng.dispose()
+        assert np.array_equal(want, plain)
+        assert np.array_equal(got, want) and np.array_equal(got_eager, want)
