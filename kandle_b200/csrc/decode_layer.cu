@@ -326,6 +326,8 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 #define DL_RED (reinterpret_cast<float4*>(smem + DL_STAGES * DL_SLOT + 1024))
+  // phase 3: q-norm weights [128], k-norm weights [128], cos [64], sin [64] as fp32, staged once per CTA
+  float* head_c = reinterpret_cast<float*>(smem + DL_STAGES * DL_SLOT + 1024 + DL_RED_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
@@ -495,6 +497,14 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
       const bool has_unit = wk.first < g.units && wk.kb0 < wk.kb1;
       const bool leader = wk.sub == 0;          // of the group that shares a slice's K (always, when the phase is not split)
       float rs = 1.f;
+      if (has_unit && gi == 3) {
+        // (visible to the 128 threads after the barrier below)
+        const int t = (int)(threadIdx.x & 127);
+        head_c[t] = __bfloat162float(p.qw[t]);
+        head_c[128 + t] = __bfloat162float(p.kw[t]);
+        if (t < 64) head_c[256 + t] = p.cos_t[t];
+        else head_c[320 + (t - 64)] = p.sin_t[t - 64];
+      }
       if (has_unit && (gi == 1 || gi == 3)) {
         // 1/rms of this thread's sequence, from the sums of squares of the phase that produced x
         if ((threadIdx.x & 127) == 0) counter_wait(p.counters + (gi - 1), (unsigned)p.g[gi - 1].units, abort_flag, p.err, 526);
@@ -511,9 +521,16 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
         // the residual and the norm weights do not depend on the GEMM: fetch the first columns' worth
         // while the MMAs run (the first 16 columns; the later ones are loaded in the loop below, where
         // their latency hides behind the work on the columns before them)
+        // (the first 16 columns of the residual into registers; the unit's norm weights, which are the
+        // same for every sequence, into shared memory: the 128-thread barrier after the accumulator wait
+        // makes them visible)
         float pre_r[16];
-        if ((gi == 0 || gi == 2) && valid && n0 < g.N && p.tp == 1 && leader)
-          ld_f32x16((gi == 0 ? p.resid_in : p.resid_mid) + (int64_t)m * p.H + n0, pre_r);
+        float* w_s = head_c + 384;       // [n_unit]
+        if ((gi == 0 || gi == 2) && n0 < g.N && p.tp == 1 && leader) {
+          const int t = (int)(threadIdx.x & 127);
+          if (t < g.n_unit && n0 + t < g.N) w_s[t] = __bfloat162float((gi == 0 ? p.w_post : p.w_next)[n0 + t]);
+          if (valid) ld_f32x16((gi == 0 ? p.resid_in : p.resid_mid) + (int64_t)m * p.H + n0, pre_r);
+        }
         if (ok) ok = mbar_wait(&acc_full[buf], (uint32_t)(use & 1), abort_flag, p.err, 527);
         // the group's other CTAs have shipped their partial sums (a split phase is one unit per CTA, so
         // each of the two barriers completes once per launch)
@@ -628,8 +645,6 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
               }
             }
             if (valid && n0 + c0 < g.N) {
-              float w[16];
-              ld_bf16x16(wn + n0 + c0, w);
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
                 a[i] += r[i];
@@ -639,15 +654,17 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
 #pragma unroll
               for (int i = 0; i < 4; ++i) ho[i] = make_float4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
 #pragma unroll
-              for (int i = 0; i < 16; ++i) a[i] *= w[i];
+              for (int i = 0; i < 16; ++i) a[i] *= w_s[c0 + i];
               st_bf16x16(x_out + (int64_t)m * p.H + n0 + c0, a);
             }
           };
-          chunk(0, pre_r);
-          for (int c0 = 16; c0 < g.n_unit; c0 += 16) {
-            float a[16];
-            if (valid && n0 + c0 < g.N) ld_f32x16(resid + (int64_t)m * p.H + n0 + c0, a);
-            chunk(c0, a);
+          // the residual of the next 16 columns is requested before the current ones are worked on
+          for (int c0 = 0; c0 < g.n_unit; c0 += 16) {
+            float nxt[16];
+            if (c0 + 16 < g.n_unit && valid && n0 + c0 + 16 < g.N) ld_f32x16(resid + (int64_t)m * p.H + n0 + c0 + 16, nxt);
+            chunk(c0, pre_r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pre_r[i] = nxt[i];
           }
           if (valid) (gi == 0 ? p.ssq1 : p.ssq2)[u * p.Mb + m] = ss;
         } else if (gi == 1) {
@@ -696,7 +713,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
               dst = (is_k ? p.k_cache : p.v_cache) + outer * p.kc_b + (int64_t)hk * p.kc_h + row * p.kc_s;
             }
           }
-          const __nv_bfloat16* hw = is_q ? p.qw : p.kw;
+          const float* hw = is_q ? head_c : head_c + 128;
           for (int c0 = 0; c0 < 64; c0 += 16) {
             // elements d = c0..c0+15 and their rotation partners d + 64
             float y1[16], y2[16];
@@ -709,17 +726,13 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
                 y2[i] *= rs;
               }
               if (is_q || is_k) {
-                float w1[16], w2[16], cs[16], sn[16];
-                ld_bf16x16(hw + c0, w1);
-                ld_bf16x16(hw + 64 + c0, w2);
-                ld_f32x16(p.cos_t + c0, cs);
-                ld_f32x16(p.sin_t + c0, sn);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                  const float a = (y1[i] * sc) * w1[i], b = (y2[i] * sc) * w2[i];
+                  const float a = (y1[i] * sc) * hw[c0 + i], b = (y2[i] * sc) * hw[64 + c0 + i];
+                  const float cs = head_c[256 + c0 + i], sn = head_c[320 + c0 + i];
                   // out[i] = y[i] cos - y[i+64] sin ; out[i+64] = y[i+64] cos + y[i] sin
-                  y1[i] = a * cs[i] - b * sn[i];
-                  y2[i] = b * cs[i] + a * sn[i];
+                  y1[i] = a * cs - b * sn;
+                  y2[i] = b * cs + a * sn;
                 }
               }
               st_bf16x16(dst + c0, y1);
@@ -989,7 +1002,7 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   struct Op { const void* w; int N, K, step; } ops[4] = {
       {p_wo, (int)H, (int)Ko, 16}, {p_wgu, (int)I2, (int)H, 32}, {p_wd, (int)H, (int)I, 16}, {p_wq, (int)Nq, (int)H, 128}};
   const int n_gemms = has_qkv ? 4 : 3;
-  const int smem = DL_STAGES * DL_SLOT + 1024 + DL_RED_BYTES + 1024;
+  const int smem = DL_STAGES * DL_SLOT + 1024 + DL_RED_BYTES + 2048 + 1024;
   static bool configured[64] = {false};
   if (!configured[dev]) {      // before the occupancy queries below, which need the shared memory to be allowed
     KD_CUDA_CHECK(cudaFuncSetAttribute(decode_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
