@@ -515,10 +515,21 @@ def kernel_rooflines(bn: Bench, eng, B: int, S: int, T: int, dims: dict):
                     lib.call("kd_decode_layer_fused", r_(attn2d), r_(lw_["wo"]), r_(d["h"]), r_(lw_["post_norm"]), r_(lw_["wgu"]),
                              r_(lw_["wdown"]), r_(nl["in_norm"]), eps, r_(nl["wqkv"]), r_(nl["q_norm"]), r_(nl["k_norm"]), r_(d["cos"]),
                              r_(d["sin"]), r_(d["pos"]), r_(caches[li + 1][0]), r_(caches[li + 1][1]), None, r_(d["q"]), r_(d["h"]), None)
-            us_c = bn.timed_ms(layer_all, reps=5) * 1e3 / (n_l - 1)
+            # the launches of all layers captured once and replayed: an eager loop of this kernel is bound
+            # by the host (20 tensor arguments, 8 tensor maps and the launch plan per call) on a slow host
+            layer_all()
+            lib.call("kd_graph_begin")
+            try:
+                layer_all()
+            finally:
+                g_layers = ctypes.c_uint64(0)
+                lib.call("kd_graph_end", ctypes.byref(g_layers))
+            us_c = bn.timed_ms(lambda: lib.call("kd_graph_launch", g_layers), reps=5) * 1e3 / (n_l - 1)
+            bn.be.synchronize()
+            lib.call("kd_graph_destroy", g_layers)
             other["decode_layer_fused"] = roof("hbm", wbytes / (us_c * 1e-6) / 1e9, bn.peaks, us_per_launch=us_c, sequences=B,
                                                note="o_proj .. next layer's QKV + q/k-norm + RoPE + cache write in one launch; latency-bound "
-                                                    "(four dependent phases); eager launches, gaps included")
+                                                    "(four dependent phases); the launches of all layers replayed from a graph, gaps included")
         elif d.get("chain") and n_l > 1:
             def chain_all_layers():
                 for li in range(n_l - 1):

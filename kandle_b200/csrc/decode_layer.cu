@@ -794,6 +794,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
 
 // ----------------------------------------------------------------------------- host side
 static unsigned* g_dl_counters[64] = {nullptr};
+static bool g_dl_no_clusters[64] = {false};   // a clustered launch was refused on this device: plan without clusters
 static unsigned long long* g_dl_trace = nullptr;     // [sm_count][16], only with KD_DECODE_LAYER_TRACE=1
 
 // Called when a kernel reported an error: a launch that gave up leaves its counters dirty.
@@ -1027,6 +1028,7 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   DlGemm plan[4] = {};
   for (int cs = 1; cs <= 4; cs *= 2) {
     if (want_cluster && cs != want_cluster) continue;
+    if (cs > 1 && g_dl_no_clusters[dev]) continue;
     if (tensor_parallel && cs > 1) continue;          // K is already split over the ranks; the exchange replaces the cluster reduce
     const int Gc = dl_cluster_grid(cs, smem);
     if (Gc <= 0 || Mb > Gc) continue;
@@ -1199,7 +1201,16 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
     attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
     ++cfg.numAttrs;
   }
-  KD_CUDA_CHECK(cudaLaunchKernelEx(&cfg, decode_layer_kernel, maps, p));
+  const cudaError_t launched = cudaLaunchKernelEx(&cfg, decode_layer_kernel, maps, p);
+  if (launched != cudaSuccess && cluster > 1 && !want_cluster) {
+    // The clustered grid was refused (fewer SMs are available than the occupancy query promised, e.g.
+    // under a profiler that keeps some for itself): plan again without clusters, from now on.
+    cudaGetLastError();
+    g_dl_no_clusters[dev] = true;
+    return decode_layer_fused(tensor_parallel, attn, w_o, resid_in, post_norm_w, w_gate_up, w_down, next_norm_w, eps, w_qkv_next, q_norm_w,
+                              k_norm_w, cos, sin, pos, k_cache_next, v_cache_next, block_table, q_out, resid_out, x_final);
+  }
+  KD_CUDA_CHECK(launched);
   return after_launch("decode_layer_kernel");
 }
 
