@@ -66,6 +66,11 @@ typedef struct kd_tensor {
  * Device / context.  Replaces WebGPUBackend.create + WebGPUDeviceManager.init
  * (packages/backend-webgpu/src/index.ts:73-85, base/device.ts:95-176).
  * ------------------------------------------------------------------------------------------- */
+/* One process drives one GPU from one host thread: kd_init binds the device to the calling thread
+ * (the other entry points do not rebind it, so calls from another thread would reach that thread's
+ * current device), launch configurations and scratch are kept per process, and a second kd_init
+ * with another ordinal while the first context lives returns KD_ERR_UNSUPPORTED (kd_shutdown
+ * first).  For N GPUs start N processes. */
 int kd_init(int device_ordinal, unsigned flags);
 int kd_shutdown(void);
 int kd_synchronize(void);
