@@ -462,6 +462,14 @@ int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_
  * written into every peer's buffer, local polling, every wait bounded at about five seconds: error
  * code 531) and summed in rank order, so every rank holds the same residual bit for bit.  All ranks
  * must issue the same sequence of calls.  After an error 531 reconnect the peer buffers. */
+/* Test support: the launch plan (cluster size; per phase rows per unit, units, K split, k-blocks per
+ * CTA of a split group, k-blocks per bulk copy) that kd_decode_layer_fused[_tp] would use for these
+ * shapes when `grid_plain` / `grid_cluster2` / `grid_cluster4` CTAs can be resident together with
+ * clusters of 1 / 2 / 4 (0: not available).  Touches no device.  out: 29 ints, [0] = cluster size
+ * (0: no configuration), then 7 per phase: N, K, rows per unit, units, split, k-blocks per CTA, k-blocks
+ * per copy. */
+int kd_debug_decode_layer_plan(int sequences, int hidden, int attn_width, int inter, int qkv_rows, int tensor_parallel,
+                               int grid_plain, int grid_cluster2, int grid_cluster4, int* out, int out_len);
 int kd_decode_layer_fused_tp(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,
                              const kd_tensor* post_norm_w, const kd_tensor* w_gate_up, const kd_tensor* w_down,
                              const kd_tensor* next_norm_w, float eps, const kd_tensor* w_qkv_next,

@@ -876,6 +876,103 @@ static float dl_phase_cost(int N, int K, int n_unit, int split, int kb_per, int 
   return std::max(waves * std::max(mma, stream), floor_all) + waves * epi + (split > 1 ? 0.6f : 0.f);
 }
 
+
+// What the launch plan depends on, and nothing else (no device is touched: the plan can be checked on a CPU).
+struct DlPlanIn {
+  int Mb, x_box;              // sequences; rows of an activation tile (8 / 16 / 32 / 64 / 128)
+  int n_gemms;                // 4, or 3 after the last layer
+  int N[4], K[4];             // the weight matrices of the phases
+  int tensor_parallel;
+  int no_groups;              // experiment: one k-block per bulk copy
+  int want_n[3];              // experiment: fixed unit width of phases 0..2 (0: free)
+  int grid[5];                // [1], [2], [4]: CTAs that are resident together with clusters of that size (0: not available)
+};
+
+// The best unit width and K split of each phase by the cost model above, for every cluster size
+// that can be launched; the cluster size with the lowest sum wins (the smaller one on a near tie).
+// Returns the cluster size (0: no configuration) and fills plan[0 .. n_gemms).  Guarantees, for a
+// phase with split S > 1: the K ranges of the S CTAs start at even k-blocks and at whole groups of
+// k-blocks, none is empty, one wave of S-CTA groups covers all slices, and the partial sums of a
+// group fit DL_RED_BYTES.
+static int dl_make_plan(const DlPlanIn& in, DlGemm* plan) {
+  const int x1 = in.x_box * DL_BK * 2;
+  auto grouped_of = [&](int K) { return K % DL_BK == 0 && !in.no_groups; };
+  auto kg_of = [&](int n_unit, int K) {
+    const int n_kb = (K + DL_BK - 1) / DL_BK;
+    return grouped_of(K) ? std::max(1, std::min(std::min(DL_X_AREA / x1, DL_W_AREA / (n_unit * DL_BK * 2)), std::min(n_kb, 16))) : 1;
+  };
+  int cluster = 0;
+  float best_total = 1e30f;
+  for (int cs = 1; cs <= 4; cs *= 2) {
+    if (in.tensor_parallel && cs > 1) continue;       // K is already split over the ranks; the exchange replaces the cluster reduce
+    const int Gc = in.grid[cs];
+    if (Gc <= 0 || in.Mb > Gc) continue;
+    DlGemm cand[4] = {};
+    float total = 0.f;
+    bool feasible = true;
+    for (int i = 0; i < in.n_gemms && feasible; ++i) {
+      DlGemm& g = cand[i];
+      g.N = in.N[i]; g.K = in.K[i];
+      const int n_kb = (g.K + DL_BK - 1) / DL_BK;
+      if (i == 1 || i == 3) {
+        g.split = 1;
+        g.kb_per = n_kb;
+        g.n_unit = 128;                 // phase 3: one head per unit
+        if (i == 1) {
+          float best1 = 1e30f;
+          for (int n = 32; n <= 128; n += 32) {
+            if (in.want_n[1] && n != in.want_n[1]) continue;
+            if ((g.N + n - 1) / n > DL_MAX_UNITS) continue;
+            const float cost = dl_phase_cost(g.N, g.K, n, 1, n_kb, Gc);
+            if (cost < best1 - 0.05f) { best1 = cost; g.n_unit = n; }
+          }
+        }
+        g.units = (g.N + g.n_unit - 1) / g.n_unit;
+        if (g.units > DL_MAX_UNITS) { feasible = false; break; }
+        total += dl_phase_cost(g.N, g.K, g.n_unit, 1, n_kb, Gc);
+        continue;
+      }
+      float best = 1e30f;
+      for (int n = 16; n <= 128; n += 16) {
+        if (in.want_n[i] && n != in.want_n[i]) continue;
+        if (in.tensor_parallel && (n & (n - 1))) continue;      // the exchange epilogue reduces over adjacent lanes: powers of two
+        const int slices = (g.N + n - 1) / n;
+        if (in.tensor_parallel && slices > P2P_MAX_ROWS) continue;   // one exchange flag per unit
+        if (slices > DL_MAX_UNITS) continue;
+        const int kg = kg_of(n, g.K);
+        for (int S = 1; S <= cs; S *= 2) {
+          int kb_per = n_kb;
+          if (S > 1) {
+            if (!grouped_of(g.K) || slices > Gc / S || (size_t)(S - 1) * in.Mb * n * sizeof(float) > (size_t)DL_RED_BYTES) continue;
+            const int q = (kg % 2) ? 2 * kg : kg;                  // ranges start at even k-blocks and at whole groups
+            kb_per = ((n_kb + S - 1) / S + q - 1) / q * q;
+            if (kb_per * (S - 1) >= n_kb) continue;                // somebody's range would be empty
+          }
+          const float cost = dl_phase_cost(g.N, g.K, n, S, kb_per, Gc);
+          if (cost < best - 0.05f) {
+            best = cost;
+            g.n_unit = n; g.units = slices; g.split = S; g.kb_per = kb_per;
+          }
+        }
+      }
+      if (best > 1e29f) feasible = false;
+      total += best;
+    }
+    if (!feasible) continue;
+    if (total < best_total - 0.3f) {
+      best_total = total;
+      cluster = cs;
+      for (int i = 0; i < 4; ++i) plan[i] = cand[i];
+    }
+  }
+  // what the tensor maps and the kernel derive from the plan
+  for (int i = 0; cluster > 0 && i < in.n_gemms; ++i) {
+    plan[i].grouped = grouped_of(plan[i].K) ? 1 : 0;
+    plan[i].kg = kg_of(plan[i].n_unit, plan[i].K);
+  }
+  return cluster;
+}
+
 }  // namespace kd
 
 using namespace kd;
@@ -1021,75 +1118,17 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   auto env_int = [](const char* name) { const char* e = getenv(name); return e ? atoi(e) : 0; };
   const int want_cluster = env_int("KD_DL_CLUSTER");
   const int want_n[3] = {env_int("KD_DL_N0"), env_int("KD_DL_N1"), env_int("KD_DL_N2")};
-  // Plan: for every cluster size that can be launched, the best unit width and K split of each phase
-  // by the cost model above; the cluster size with the lowest sum wins (the smaller one on a near tie).
-  int cluster = 0;
-  float best_total = 1e30f;
-  DlGemm plan[4] = {};
+  DlPlanIn pin{};
+  pin.Mb = (int)Mb; pin.x_box = p.x_box; pin.n_gemms = n_gemms; pin.tensor_parallel = tensor_parallel ? 1 : 0;
+  pin.no_groups = no_groups ? 1 : 0;
+  for (int i = 0; i < 4; ++i) { pin.N[i] = ops[i].N; pin.K[i] = ops[i].K; }
+  for (int i = 0; i < 3; ++i) pin.want_n[i] = want_n[i];
   for (int cs = 1; cs <= 4; cs *= 2) {
-    if (want_cluster && cs != want_cluster) continue;
-    if (cs > 1 && g_dl_no_clusters[dev]) continue;
-    if (tensor_parallel && cs > 1) continue;          // K is already split over the ranks; the exchange replaces the cluster reduce
-    const int Gc = dl_cluster_grid(cs, smem);
-    if (Gc <= 0 || Mb > Gc) continue;
-    DlGemm cand[4] = {};
-    float total = 0.f;
-    bool feasible = true;
-    for (int i = 0; i < n_gemms && feasible; ++i) {
-      DlGemm& g = cand[i];
-      g.N = ops[i].N; g.K = ops[i].K;
-      const int n_kb = (g.K + DL_BK - 1) / DL_BK;
-      if (i == 1 || i == 3) {
-        g.split = 1;
-        g.kb_per = n_kb;
-        g.n_unit = 128;                 // phase 3: one head per unit
-        if (i == 1) {
-          float best1 = 1e30f;
-          for (int n = 32; n <= 128; n += 32) {
-            if (want_n[1] && n != want_n[1]) continue;
-            if ((g.N + n - 1) / n > DL_MAX_UNITS) continue;
-            const float cost = dl_phase_cost(g.N, g.K, n, 1, n_kb, Gc);
-            if (cost < best1 - 0.05f) { best1 = cost; g.n_unit = n; }
-          }
-        }
-        g.units = (g.N + g.n_unit - 1) / g.n_unit;
-        if (g.units > DL_MAX_UNITS) { feasible = false; break; }
-        total += dl_phase_cost(g.N, g.K, g.n_unit, 1, n_kb, Gc);
-        continue;
-      }
-      float best = 1e30f;
-      for (int n = 16; n <= 128; n += 16) {
-        if (want_n[i] && n != want_n[i]) continue;
-        if (tensor_parallel && (n & (n - 1))) continue;      // the exchange epilogue reduces over adjacent lanes: powers of two
-        const int slices = (g.N + n - 1) / n;
-        if (tensor_parallel && slices > P2P_MAX_ROWS) continue;   // one exchange flag per unit
-        if (slices > DL_MAX_UNITS) continue;
-        const int kg = kg_of(n, g.K);
-        for (int S = 1; S <= cs; S *= 2) {
-          int kb_per = n_kb;
-          if (S > 1) {
-            if (!grouped_of(g.K) || slices > Gc / S || (size_t)(S - 1) * Mb * n * sizeof(float) > (size_t)DL_RED_BYTES) continue;
-            const int q = (kg % 2) ? 2 * kg : kg;                  // ranges start at even k-blocks and at whole groups
-            kb_per = ((n_kb + S - 1) / S + q - 1) / q * q;
-            if (kb_per * (S - 1) >= n_kb) continue;                // somebody's range would be empty
-          }
-          const float cost = dl_phase_cost(g.N, g.K, n, S, kb_per, Gc);
-          if (cost < best - 0.05f) {
-            best = cost;
-            g.n_unit = n; g.units = slices; g.split = S; g.kb_per = kb_per;
-          }
-        }
-      }
-      if (best > 1e29f) feasible = false;
-      total += best;
-    }
-    if (!feasible) continue;
-    if (total < best_total - 0.3f) {
-      best_total = total;
-      cluster = cs;
-      for (int i = 0; i < 4; ++i) plan[i] = cand[i];
-    }
+    const bool allowed = !(want_cluster && cs != want_cluster) && !(cs > 1 && g_dl_no_clusters[dev]);
+    pin.grid[cs] = allowed ? dl_cluster_grid(cs, smem) : 0;
   }
+  DlGemm plan[4] = {};
+  const int cluster = dl_make_plan(pin, plan);
   KD_REQUIRE(cluster > 0, "no launch configuration for these shapes (hidden %lld, %lld sequences)", (long long)H, (long long)Mb);
   G = dl_cluster_grid(cluster, smem);
   for (int i = 0; i < n_gemms; ++i) p.g[i] = plan[i];
@@ -1212,6 +1251,33 @@ static int decode_layer_fused(bool tensor_parallel, const kd_tensor* attn, const
   }
   KD_CUDA_CHECK(launched);
   return after_launch("decode_layer_kernel");
+}
+
+// The launch plan of kd_decode_layer_fused[_tp] for given shapes and grid sizes, without touching a
+// device.  out: [0] cluster size (0: no configuration), then per phase 7 numbers: N, K, rows per
+// unit, units, K split, k-blocks per CTA of a split group, k-blocks per bulk copy.
+KD_API int kd_debug_decode_layer_plan(int sequences, int hidden, int attn_width, int inter, int qkv_rows, int tensor_parallel,
+                                      int grid_plain, int grid_cluster2, int grid_cluster4, int* out, int out_len) {
+  KD_REQUIRE(out && out_len >= 29, "out must hold 29 ints");
+  KD_REQUIRE(sequences >= 1 && sequences <= 128 && hidden > 0 && attn_width > 0 && inter > 0 && qkv_rows >= 0, "bad shape");
+  DlPlanIn in{};
+  in.Mb = sequences;
+  in.x_box = sequences <= 8 ? 8 : (sequences <= 16 ? 16 : (sequences <= 32 ? 32 : (sequences <= 64 ? 64 : 128)));
+  in.n_gemms = qkv_rows > 0 ? 4 : 3;
+  in.N[0] = hidden; in.K[0] = attn_width;
+  in.N[1] = 2 * inter; in.K[1] = hidden;
+  in.N[2] = hidden; in.K[2] = inter;
+  in.N[3] = qkv_rows; in.K[3] = hidden;
+  in.tensor_parallel = tensor_parallel ? 1 : 0;
+  in.grid[1] = grid_plain; in.grid[2] = grid_cluster2; in.grid[4] = grid_cluster4;
+  DlGemm plan[4] = {};
+  out[0] = dl_make_plan(in, plan);
+  for (int i = 0; i < 4; ++i) {
+    int* o = out + 1 + 7 * i;
+    o[0] = plan[i].N; o[1] = plan[i].K; o[2] = plan[i].n_unit; o[3] = plan[i].units; o[4] = plan[i].split; o[5] = plan[i].kb_per;
+    o[6] = plan[i].kg;
+  }
+  return KD_OK;
 }
 
 KD_API int kd_decode_layer_fused(const kd_tensor* attn, const kd_tensor* w_o, const kd_tensor* resid_in,

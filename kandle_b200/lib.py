@@ -153,6 +153,7 @@ _SIGNATURES = {
     "kd_decode_layer_chain": [_T, _T, _T, _T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T],
     "kd_decode_layer_fused": [_T, _T, _T, _T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T],
     "kd_decode_layer_fused_tp": [_T, _T, _T, _T, _T, _T, _T, ctypes.c_float, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _T],
+    "kd_debug_decode_layer_plan": [ctypes.c_int] * 9 + [ctypes.POINTER(ctypes.c_int), ctypes.c_int],
     "kd_debug_decode_layer_trace": [ctypes.POINTER(ctypes.c_uint64), ctypes.c_int],
     "kd_decode_layer_chain_splits": [ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)],
     "kd_set_pdl": [ctypes.c_int],
