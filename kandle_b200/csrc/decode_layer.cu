@@ -1,5 +1,8 @@
 // Everything a decoder layer does between two attention calls of a decode step, and the head of
-// the next layer, as ONE persistent kernel with FOUR dependent phases and no split-K:
+// the next layer, as ONE persistent kernel with FOUR dependent phases and no split-K through global
+// memory (where K is split, it is split inside a thread-block cluster and summed through
+// distributed shared memory; in the tensor-parallel form the ranks' partial sums cross NVLink
+// inside the epilogue, see DlParams):
 //
 //   P0  o_proj             h1 = h + attn Wo^T;  x1 = bf16(h1 * w_post);  per-unit sums of h1^2
 //   P1  gate/up            act = silu(rs1 (x1 Wg^T)) * (rs1 (x1 Wu^T)),  rs1 = 1/sqrt(mean(h1^2)+eps)
@@ -22,7 +25,7 @@
 // 128 whatever the batch, the unused rows read whatever follows the activation tile in shared
 // memory and produce rows nobody looks at), and a unit of work is a NARROW slice of weight rows
 // (16..128, the MMA's N) over the WHOLE of K.  So
-//   - there is no split-K and no partial sum anywhere: four hand-overs per layer;
+//   - there is no split-K phase and no partial sum in global memory: four hand-overs per layer;
 //   - a thread of the epilogue owns one sequence and sees a contiguous run of output features, so
 //     the residual add, the sums of squares RMSNorm needs, SiLU(gate)*up (gate and up rows are
 //     interleaved 16/16), a head's RMSNorm and its rotation are all plain per-thread loops with
@@ -33,8 +36,8 @@
 // sequences), which is why units are not made narrower than they need to be to occupy the SMs.
 //
 // warp 0 TMA producer (the weight tiles of a CTA's next unit are fetched while the activations they
-// meet are still being produced), warp 1 tcgen05.mma issuer (two accumulators in TMEM), warps 2-5
-// epilogues and counters.  One CTA per SM, all CTAs resident together (a cooperative launch, or a plain
+// meet are still being produced), warps 1 and 6 tcgen05.mma issuers (even / odd k-blocks into two
+// halves of each of the two accumulators in TMEM), warps 2-5 epilogues and counters.  One CTA per SM, all CTAs resident together (a cooperative launch, or a plain
 // one inside a decode step: see the launch code), every wait bounded (codes 521-531).
 // Results are bit-identical from launch to launch and do not depend on the number of sequences.
 // Roofline: HBM, the bytes of the four weight matrices; in practice latency.
