@@ -420,7 +420,7 @@ int kd_decode_layer_chain(const kd_tensor* attn, const kd_tensor* w_o, const kd_
                           const kd_tensor* resid_mid, const kd_tensor* resid_out, const kd_tensor* x_out,
                           const kd_tensor* act, const kd_tensor* qkv_partials);
 int kd_decode_layer_chain_splits(int64_t N, int64_t K, int* splits_out);
-/* The same stretch of a decode step in FOUR dependent phases and without split-K, and further: up
+/* The same stretch of a decode step in FOUR dependent phases and without split-K phases, and further: up
  * to and including the next layer's q_norm / k_norm, rotary embedding and KV-cache write
  * (packages/model-utils/src/attention/gqa.ts:274-322, rope.ts:546-644, kv-cache.ts:164-212), so that
  * a decode step is two launches per layer (this one and kd_attention_decode).
@@ -436,13 +436,17 @@ int kd_decode_layer_chain_splits(int64_t N, int64_t K, int* splits_out);
  *                                              [B,Hkv,maxS,128], or pools [pages,Hkv,128,128] addressed
  *                                              through block_table int32 [B,max_pages] when it is given)
  * The sequences are the rows of every accumulator and a unit of work is a narrow slice of weight
- * rows over the whole of K, so no partial sums exist and an epilogue thread owns one sequence.
+ * rows, so an epilogue thread owns one sequence; where o_proj or down_proj would leave most SMs
+ * idle, the K of a slice is split over the 2 or 4 CTAs of a thread-block cluster, which hand their
+ * partial sums to the first of them through distributed shared memory (no partial sum ever goes
+ * through global memory).
  * With w_qkv_next == NULL (after the last layer) the launch ends with
  * x_final = bf16(resid_out * rs2 * next_norm_w), the lm_head's input, and the arguments from
  * q_norm_w to q_out are ignored.  head_dim 128 only; 1 <= Mb <= 128; hidden size a multiple of 16;
  * resid_out may be resid_in.  A cache row outside [0, maxS) is not written and reports KD_ERR_DEVICE
- * code 102, a wait that runs out codes 521-528.  Results are bit-identical from launch to launch
- * and do not depend on how many sequences share the launch. */
+ * code 102, a wait that runs out codes 521-529.  Results are bit-identical from launch to launch;
+ * the launch plan (unit widths, K splits: kd_debug_decode_layer_plan), and with it the order of the
+ * sums, follows the shapes including the number of sequences. */
 /* Test / profiling support, no counterpart in the reference: device-side timestamps of the last
  * kd_decode_layer_fused launch, [SMs][16] nanoseconds (0: start; per phase g: 1+3g dependency seen,
  * 2+3g accumulator ready, 3+3g outputs published); only in a process started with
