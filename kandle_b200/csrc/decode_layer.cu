@@ -39,7 +39,8 @@
 // meet are still being produced), warps 1 and 6 tcgen05.mma issuers (even / odd k-blocks into two
 // halves of each of the two accumulators in TMEM), warps 2-5 epilogues and counters.  One CTA per SM, all CTAs resident together (a cooperative launch, or a plain
 // one inside a decode step: see the launch code), every wait bounded (codes 521-531).
-// Results are bit-identical from launch to launch and do not depend on the number of sequences.
+// Results are bit-identical from launch to launch; the launch plan (and with it the order of the
+// sums) follows the shapes, the number of sequences included.
 // Roofline: HBM, the bytes of the four weight matrices; in practice latency.
 #include <algorithm>
 
